@@ -1,0 +1,153 @@
+/*
+ * libvexact_b200: C ABI of the B200 (sm_100a) rollout-forward kernels.
+ *
+ * Every function
+ *   - takes raw device pointers, explicit sizes, element strides and a cudaStream_t
+ *     (passed as void*; NULL = the legacy default stream),
+ *   - launches on that stream, allocates nothing and does not synchronise
+ *     (b200_status_read excepted), so it can be captured in a CUDA graph,
+ *   - returns 0 when the work was launched and a negative code otherwise:
+ *       -1 invalid argument, -2 unsupported shape, -3 CUDA launch error,
+ *       -4 driver entry point (tensor-map encoder) unavailable.
+ * Nothing is reported from the device except through the status word read by
+ * b200_status_read (bounded waits that expired, out-of-range slot / expert ids).
+ *
+ * bf16 tensors are `__nv_bfloat16`, row-major with the innermost dimension
+ * contiguous unless a stride says otherwise.  Strides are in elements.
+ *
+ * Each declaration names the reference interface (path inside verl-project/vexact)
+ * that it stands in for.
+ */
+#ifndef VEXACT_B200_H
+#define VEXACT_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int b200_abi_version(void);
+
+/* Reads {code, detail, block, spare} of the device status word into host_out4 and clears it.
+ * Synchronises `stream`.  code: 0 ok, 1 a bounded wait expired, 2 an index was out of range. */
+int b200_status_read(int* host_out4, void* stream);
+
+/* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:159 matmul_persistent(a, b, bias),
+ *      :476 mm_batch_invariant, :480 addmm_batch_invariant.
+ * out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N] in fp32 before the cast).  `w` is the
+ * nn.Linear weight itself ([N, K], K contiguous): the reference receives weight.t().
+ * K and the row strides must be multiples of 8 elements; pointers 16-byte aligned.
+ * out_dtype: 0 = bf16, 1 = fp32. */
+int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
+                   long long x_row_stride, long long w_row_stride, long long out_row_stride, int out_dtype,
+                   void* stream);
+
+/* fp32 variant for the DeepSeek-V3 router (vexact/models/deepseek_v3/modeling_deepseek_v3.py:97-100,
+ * F.linear in fp32, reaching matmul_persistent with fp32 operands).  Exact fp32 FMA arithmetic. */
+int b200_gemm_f32(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
+                  long long x_row_stride, long long w_row_stride, long long out_row_stride, void* stream);
+
+/* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:728 batch_invariant_rms_norm (mode 0:
+ *      fp32 math, one rounding) and the HF eager RMSNorm the reference reaches through its
+ *      aten::mean.dim override, :619 mean_batch_invariant (mode 1: x*rsqrt(var+eps) rounded to
+ *      bf16, then multiplied by the weight). */
+int b200_rmsnorm(const void* x, const void* weight, void* out, long long rows, int n, long long x_row_stride,
+                 long long out_row_stride, float eps, int mode, void* stream);
+
+/* sum_out = bf16(residual + x); out = rmsnorm(sum_out).  All tensors [rows, n] contiguous.
+ * The decoder layer's "residual add, then norm" (HF Qwen3DecoderLayer.forward) in one pass. */
+int b200_add_rmsnorm(const void* x, const void* residual, const void* weight, void* sum_out, void* out,
+                     long long rows, int n, float eps, int mode, void* stream);
+
+/* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:385 mean_dim (last dimension only).
+ * dtype: 0 = fp32, 1 = bf16 (input and output). */
+int b200_mean_lastdim(const void* x, void* out, long long rows, int n, long long x_row_stride, int dtype,
+                      void* stream);
+
+/* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:295 log_softmax (fp32, last dim). */
+int b200_log_softmax_f32(const void* x, void* out, long long rows, int n, long long x_row_stride,
+                         long long out_row_stride, void* stream);
+
+/* ---- vexact/batch_invariant_ops/standalone_logprobs.py:28 logprobs_from_logits_flash_attn.
+ * out[r] = logits[r, labels[r]] - logsumexp(logits[r, :]) in fp32; 0 where labels[r] == ignore_index.
+ * labels are int64.  dtype of logits: 0 = fp32, 1 = bf16. */
+int b200_gather_logprob(const void* logits, const void* labels, void* out, long long rows, int n,
+                        long long row_stride, int dtype, long long ignore_index, void* stream);
+
+/* ---- vexact/batch_invariant_ops/kv_cache_context.py:294 store_kvcache.
+ * key [T, heads, dk], value [T, heads, dv] (token strides given, heads*dim contiguous);
+ * caches [blocks, page, heads, d] contiguous; slot_mapping int32 [T], -1 = skip.
+ * num_slots = blocks * page bounds the slot ids. */
+int b200_kv_store(const void* key, const void* value, void* k_cache, void* v_cache, const void* slot_mapping,
+                  long long num_tokens, int num_kv_heads, int k_head_dim, int v_head_dim,
+                  long long k_token_stride, long long v_token_stride, long long num_slots, void* stream);
+
+/* Fused per-head q/k RMSNorm (optional, HF formula) + rotary embedding + KV-cache store for
+ * head_dim 128: what HF Qwen3Attention / Qwen2Attention.forward does between the QKV
+ * projection and the attention call, followed by store_kvcache (kv_cache_context.py:294).
+ * qkv [T, (q_heads + 2 kv_heads) * 128] bf16; positions int64 [T]; inv_freq fp32 [64]. */
+int b200_qknorm_rope_store(const void* qkv, long long qkv_token_stride, const void* positions,
+                           const void* slot_mapping, const void* q_norm_weight, const void* k_norm_weight,
+                           const void* inv_freq, void* q_out, void* k_cache, void* v_cache,
+                           long long num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                           long long num_slots, float eps, void* stream);
+
+/* ---- vexact/batch_invariant_ops/triton_invariant_attention.py:905 flash_attn_varlen_func with a
+ *      page table (:605 _PagedFlashAttentionVarlen, kernel :434) and the FA3 / FA4 calls of
+ *      vexact/batch_invariant_ops/flash_attention.py:142-178.  Causal only.
+ * (dk, dv) in {(128,128), (192,128), (64,64)}; page_size a multiple of 8 that divides, or is a
+ * multiple of, 64; query heads per KV head <= 8 or a multiple of 8. */
+int b200_paged_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* out,
+                        const void* cu_seqlens_q, const void* seqused_k, const void* page_table, int num_seqs,
+                        int max_seqlen_q, int num_q_heads, int num_kv_heads, int dk, int dv, int num_blocks,
+                        int page_size, int max_pages, long long page_table_stride, long long q_tok_stride,
+                        long long q_head_stride, long long o_tok_stride, long long o_head_stride,
+                        long long kc_block_stride, long long kc_page_stride, long long kc_head_stride,
+                        long long vc_block_stride, long long vc_page_stride, long long vc_head_stride,
+                        float softmax_scale, void* stream);
+
+/* ---- vexact/models/qwen3_moe/modeling_qwen3_moe.py:128-134 (softmax, top-k, renormalise, cast).
+ * logits_dtype: 0 = fp32, 1 = bf16.  Any of the four outputs may be NULL except that one weight
+ * and one expert output are required. */
+int b200_moe_route_softmax_topk(const void* logits, int logits_dtype, long long row_stride, void* weights_bf16,
+                                void* weights_f32, void* experts_i32, void* experts_i64, long long T, int E,
+                                int topk, int renorm, void* stream);
+
+/* ---- vexact/models/deepseek_v3/modeling_deepseek_v3.py:185-208 route_tokens_to_experts. */
+int b200_moe_route_sigmoid_group_topk(const void* logits_f32, long long row_stride, const void* bias_f32,
+                                      void* weights_f32, void* experts_i32, void* experts_i64, long long T,
+                                      int E, int n_group, int topk_group, int topk, int renorm, float scale,
+                                      void* stream);
+
+/* ---- vexact/batch_invariant_ops/fused_moe.py:268 _build_moe_indices and
+ *      group_gemm/kernel/moe.py:304 moe_scatter.  Outputs are caller-provided scratch:
+ *      scatter_index [T*topk] i32, cu_seqlens [E+1] i32, x_perm [T*topk, H] bf16,
+ *      row_scale [T*topk] bf16, tile_table [max_tiles] int4, tile_count [1] i32. */
+int b200_moe_permute(const void* experts, int experts_dtype, const void* weights_bf16, const void* x,
+                     long long x_row_stride, void* scatter_index, void* cu_seqlens, void* x_perm,
+                     void* row_scale, void* tile_table, void* tile_count, long long T, int topk, int E, int H,
+                     int tile_rows, int max_tiles, void* stream);
+
+/* ---- vexact/batch_invariant_ops/fused_moe.py:319-339 (quack gemm with cu_seqlens_m) /
+ *      group_gemm/kernel/group_gemm.py:156 group_gemm_same_nk.
+ * mode 0: out[r, :] = x[r, :] @ w[g(r)]^T, w [G, n_out, K].
+ * mode 1: out[r, i] = silu(x.w[g, i]) * (x.w[g, n_out + i]) * row_scale[r], w [G, 2*n_out, K]
+ *         (gate rows first), each intermediate rounded to bf16 as in fused_moe.py:325-336. */
+int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, void* out,
+                          const void* tile_table, const void* tile_count, long long x_rows, int num_groups,
+                          int n_out, int K, long long out_row_stride, int max_tiles, int tile_rows_max, int mode,
+                          void* stream);
+
+/* ---- vexact/batch_invariant_ops/fused_moe.py:325-336 for split gate / up weights. */
+int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out, long long rows,
+                      int I, void* stream);
+
+/* ---- vexact/batch_invariant_ops/group_gemm/kernel/moe.py:131 moe_gather
+ *      (+ optional bf16 add of `addend` [T, H] afterwards, e.g. the shared experts'
+ *      output of modeling_deepseek_v3.py:217). */
+int b200_moe_unpermute_reduce(const void* y, const void* scatter_index, const void* addend, void* out,
+                              long long T, int topk, int H, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VEXACT_B200_H */

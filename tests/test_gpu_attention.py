@@ -1,0 +1,183 @@
+"""GPU parity: paged causal attention vs the reference kernel's golden outputs, the fp32 eager
+ground truth the reference tests use, and the bitwise invariance properties of
+tests/batch_invariant_ops/test_triton_attention_varlen.py:398-558 (batched == single sequence,
+prefill last token == decode, chunked == full prefill, MLA head dims)."""
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import ops
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def vb():
+    import vexact_b200 as vb
+
+    vb._lib.load()
+    return vb
+
+
+def _build(q_lens, kv_lens, hq, hkv, dk, dv, page, seed=0, extra_blocks=3):
+    g = torch.Generator().manual_seed(seed)
+    S = len(q_lens)
+    max_pages = max((kl + page - 1) // page for kl in kv_lens)
+    nblocks = S * max_pages + extra_blocks
+    perm = torch.randperm(nblocks, generator=g)
+    kc = (torch.randn(nblocks, page, hkv, dk, generator=g)).to(BF)
+    vc = (torch.randn(nblocks, page, hkv, dv, generator=g)).to(BF)
+    ptab = torch.full((S, max_pages), -1, dtype=torch.int32)
+    nxt = 0
+    for s in range(S):
+        for pg in range((kv_lens[s] + page - 1) // page):
+            ptab[s, pg] = perm[nxt]
+            nxt += 1
+    q = torch.randn(sum(q_lens), hq, dk, generator=g).to(BF)
+    cu = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
+    used = torch.tensor(kv_lens, dtype=torch.int32)
+    return q, kc, vc, cu, used, ptab
+
+
+def _run(vb, q, kc, vc, cu, used, ptab, scale, max_q):
+    out, none = vb.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cu_seqlens_q=cu.cuda(),
+                                          max_seqlen_q=max_q, seqused_k=used.cuda(), page_table=ptab.cuda(),
+                                          softmax_scale=scale, causal=True)
+    assert none is None
+    return out.cpu()
+
+
+def test_golden_reference_kernel(vb):
+    for c in load_golden("paged_attention"):
+        qlens = (c["cu_seqlens_q"][1:] - c["cu_seqlens_q"][:-1]).tolist()
+        out = _run(vb, c["q"], c["k_cache"], c["v_cache"], c["cu_seqlens_q"], c["seqused_k"], c["page_table"],
+                   c["scale"], max(qlens))
+        # reference tolerance, bf16 paged vs fp32 eager: atol 3e-3 on unit-variance inputs
+        # (test_triton_attention_varlen.py:415); outputs here reach |o| ~ 3, one bf16 ulp = 1.6e-2
+        torch.testing.assert_close(out.float(), c["out_triton_fp32"], rtol=2 ** -7, atol=3e-3)
+        torch.testing.assert_close(out.float(), c["out_eager_fp32"], rtol=2 ** -7, atol=3e-3)
+
+
+@pytest.mark.parametrize("hq,hkv,dk,dv,page", [(32, 4, 128, 128, 16), (16, 8, 128, 128, 16), (12, 2, 128, 128, 64),
+                                               (16, 8, 128, 128, 256), (16, 16, 192, 128, 16), (4, 4, 64, 64, 16),
+                                               (32, 2, 128, 128, 16)])
+def test_oracle_mixed_batch(vb, hq, hkv, dk, dv, page):
+    q_lens = [1, 5, 1, 17, 64, 1]
+    kv_lens = [1, 5, 130, 200, 64, 257]
+    q, kc, vc, cu, used, ptab = _build(q_lens, kv_lens, hq, hkv, dk, dv, page, seed=1)
+    scale = dk ** -0.5
+    out = _run(vb, q, kc, vc, cu, used, ptab, scale, max(q_lens))
+    ref = ops.paged_attention(q, kc, vc, cu, used, ptab, scale, block_n=64)
+    eager = ops.paged_attention(q, kc, vc, cu, used, ptab, scale)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2 ** -7, atol=3e-3)
+    torch.testing.assert_close(out.float(), eager.float(), rtol=2 ** -6, atol=6e-3)
+    assert (out == ref).float().mean() > 0.9
+
+
+def test_batched_equals_single_sequence_bitwise(vb):
+    q_lens = [1, 9, 1, 33]
+    kv_lens = [300, 9, 77, 140]
+    hq, hkv, d, page = 32, 4, 128, 16
+    q, kc, vc, cu, used, ptab = _build(q_lens, kv_lens, hq, hkv, d, d, page, seed=2)
+    scale = d ** -0.5
+    full = _run(vb, q, kc, vc, cu, used, ptab, scale, max(q_lens))
+    for s in range(len(q_lens)):
+        cu1 = torch.tensor([0, q_lens[s]], dtype=torch.int32)
+        one = _run(vb, q[cu[s]:cu[s + 1]], kc, vc, cu1, used[s:s + 1], ptab[s:s + 1], scale, q_lens[s])
+        assert torch.equal(one, full[cu[s]:cu[s + 1]]), f"sequence {s} differs when batched"
+
+
+@pytest.mark.parametrize("hq,hkv,dk,dv,page", [(16, 8, 128, 128, 256), (32, 4, 128, 128, 16), (16, 16, 192, 128, 16)])
+def test_prefill_chunked_decode_bitwise(vb, hq, hkv, dk, dv, page):
+    """Token p's output is the same bits whether it is computed in a full prefill, in a prefill
+    chunk, or as a single decode query over p cached tokens."""
+    L = 150
+    q, kc, vc, cu, used, ptab = _build([L], [L], hq, hkv, dk, dv, page, seed=3)
+    scale = dk ** -0.5
+    full = _run(vb, q, kc, vc, cu, used, ptab, scale, L)
+    # chunked: queries [0,70) over 70 keys, then [70,150) over 150 keys
+    c1 = _run(vb, q[:70], kc, vc, torch.tensor([0, 70], dtype=torch.int32), torch.tensor([70], dtype=torch.int32),
+              ptab, scale, 70)
+    c2 = _run(vb, q[70:], kc, vc, torch.tensor([0, 80], dtype=torch.int32), torch.tensor([150], dtype=torch.int32),
+              ptab, scale, 80)
+    assert torch.equal(torch.cat([c1, c2]), full)
+    # decode: every position as its own one-query sequence of a batch, all sharing the same pages
+    pos = [0, 1, 63, 64, 65, 127, 128, 149]
+    S = len(pos)
+    qd = torch.stack([q[p] for p in pos])
+    cu_d = torch.arange(S + 1, dtype=torch.int32)
+    used_d = torch.tensor([p + 1 for p in pos], dtype=torch.int32)
+    dec = _run(vb, qd, kc, vc, cu_d, used_d, ptab.expand(S, -1).contiguous(), scale, 1)
+    for i, p in enumerate(pos):
+        assert torch.equal(dec[i], full[p]), f"decode at position {p} differs from prefill"
+
+
+def test_padding_and_empty_sequences_are_noops(vb):
+    # CUDA-graph buckets pad with zero-length sequences (inferencer.py:318-324)
+    q_lens = [1, 0, 1, 0]
+    kv_lens = [40, 0, 17, 0]
+    hq, hkv, d, page = 8, 1, 128, 16
+    g = torch.Generator().manual_seed(4)
+    kc = torch.randn(8, page, hkv, d, generator=g).to(BF)
+    vc = torch.randn(8, page, hkv, d, generator=g).to(BF)
+    ptab = torch.tensor([[0, 1, 2], [-1, -1, -1], [3, 4, -1], [-1, -1, -1]], dtype=torch.int32)
+    q = torch.randn(2, hq, d, generator=g).to(BF)
+    cu = torch.tensor([0, 1, 1, 2, 2], dtype=torch.int32)
+    used = torch.tensor(kv_lens, dtype=torch.int32)
+    out = _run(vb, q, kc, vc, cu, used, ptab, d ** -0.5, 1)
+    ref = ops.paged_attention(q, kc, vc, cu, used, ptab, d ** -0.5, block_n=64)
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2 ** -7, atol=3e-3)
+
+
+def test_unwritten_cache_slots_do_not_leak(vb):
+    """Slots past the sequence end may hold anything, NaN bit patterns included."""
+    hq, hkv, d, page = 8, 1, 128, 16
+    q, kc, vc, cu, used, ptab = _build([1], [21], hq, hkv, d, d, page, seed=5)
+    out = _run(vb, q, kc, vc, cu, used, ptab, d ** -0.5, 1)
+    kc2, vc2 = kc.clone(), vc.clone()
+    blk = int(ptab[0, 1])
+    kc2[blk, 5:] = float("nan")
+    vc2[blk, 5:] = float("nan")
+    out2 = _run(vb, q, kc2, vc2, cu, used, ptab, d ** -0.5, 1)
+    assert torch.equal(out, out2)
+
+
+def test_hf_adapter_stores_then_attends(vb):
+    hq, hkv, d, page, L = 16, 8, 128, 16, 40
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(1, hq, L, d, generator=g).to(BF).cuda()
+    k = torch.randn(1, hkv, L, d, generator=g).to(BF).cuda()
+    v = torch.randn(1, hkv, L, d, generator=g).to(BF).cuda()
+    kc = {0: torch.zeros(4, page, hkv, d, dtype=BF).cuda()}
+    vc = {0: torch.zeros(4, page, hkv, d, dtype=BF).cuda()}
+    ptab = torch.tensor([[2, 0, 3]], dtype=torch.int32)
+    slots = torch.tensor(ops.slot_mapping([[2, 0, 3]], [0], [L], page))
+    vb.set_kv_cache_context(is_paged_attn=True, key_cache=kc, value_cache=vc, block_tables=ptab.cuda(),
+                            context_lens=torch.tensor([L], dtype=torch.int32).cuda(), slot_mapping=slots.cuda(),
+                            query_start_loc=torch.tensor([0, L], dtype=torch.int32).cuda(), max_seqlen_q=L)
+    mod = torch.nn.Module()
+    mod.layer_idx = 0
+    out, w = vb.flash_attention_forward(mod, q, k, v, None, scaling=d ** -0.5)
+    assert w is None and out.shape == (L, hq, d)
+    ref = ops.paged_attention(q[0].transpose(0, 1).cpu(), kc[0].cpu(), vc[0].cpu(), [0, L], [L], ptab, d ** -0.5,
+                              block_n=64)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=2 ** -7, atol=3e-3)
+
+
+def test_argument_errors(vb):
+    q, kc, vc, cu, used, ptab = _build([1], [5], 8, 1, 128, 128, 16)
+    with pytest.raises(NotImplementedError):
+        vb.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cu_seqlens_q=cu.cuda(), seqused_k=used.cuda(),
+                                  page_table=ptab.cuda(), causal=False)
+    with pytest.raises(ValueError):
+        vb.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cu_seqlens_q=cu.cuda(), seqused_k=used.cuda(),
+                                  page_table=ptab.cuda(), block_table=ptab.cuda(), causal=True)
+    with pytest.raises(ValueError):
+        vb.flash_attn_varlen_func(q.cuda(), kc.cuda(), vc.cuda(), cu_seqlens_q=cu.cuda(), seqused_k=used.cuda().long(),
+                                  page_table=ptab.cuda(), causal=True)
+
+
+def test_status_word_clean(vb):
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0

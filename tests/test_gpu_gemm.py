@@ -1,0 +1,113 @@
+"""GPU parity: tcgen05 weight-streaming GEMM vs the CPU oracle and the reference's golden
+fixtures, and bitwise row invariance across batch sizes
+(reference: tests/batch_invariant_ops/test_matmul.py:27-46, test_batch_invariance.py:30-128)."""
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import ops
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def vb():
+    import vexact_b200 as vb
+
+    vb._lib.load()
+    return vb
+
+
+def _seeded(*shape, seed=0, std=1.0, dtype=BF):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+
+def _close_bf16(got, want, k):
+    # stated tolerance: one bf16 ulp (rtol 2^-7) plus fp32 accumulation-order noise for results
+    # that cancel towards zero; and the vast majority of elements bit-identical
+    torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -7, atol=1e-6 * k ** 0.5 + 1e-5)
+    assert (got == want).float().mean() > 0.98
+
+
+def test_gemm_golden(vb):
+    for c in load_golden("matmul"):
+        a, w, bias = c["a"].cuda(), c["w"].cuda(), c["bias"].cuda()
+        _close_bf16(vb.matmul_persistent(a, w.t()).cpu(), c["out"], a.shape[1])
+        _close_bf16(vb.matmul_persistent(a, w.t(), bias).cpu(), c["out_bias"], a.shape[1])
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 2048, 6144), (7, 2048, 6144), (64, 2048, 6144), (256, 2048, 6144),
+                                   (300, 768, 2048), (512, 4096, 2048), (5, 72, 40), (129, 1536, 576)])
+def test_gemm_oracle(vb, M, K, N):
+    x = _seeded(M, K, seed=1)
+    w = _seeded(N, K, seed=2, std=0.02)
+    ref = ops.matmul(x, w.t())
+    out = vb.matmul_persistent(x.cuda(), w.cuda().t())
+    _close_bf16(out.cpu(), ref, K)
+    # row-major B ([K, N] contiguous) and fp32 output
+    out2 = vb.matmul_persistent(x.cuda(), w.t().contiguous().cuda())
+    assert torch.equal(out, out2)
+    out32 = vb.linear(x.cuda(), w.cuda(), out_dtype=torch.float32)
+    assert torch.equal(out32.to(BF), out)
+
+
+def test_gemm_bias_fp32_before_cast(vb):
+    x = _seeded(33, 1536, seed=3)
+    w = _seeded(256, 1536, seed=4, std=0.02)
+    b = _seeded(256, seed=5, std=0.5)
+    ref = ops.matmul(x, w.t(), b)
+    out = torch.addmm(b.cuda(), x.cuda(), w.cuda().t()) if False else vb.matmul_persistent(x.cuda(), w.cuda().t(), b.cuda())
+    _close_bf16(out.cpu(), ref, 1536)
+
+
+def test_gemm_row_invariance_sweep(vb):
+    """Row i of X @ W^T is bit-identical for every batch size 1..512 (BASELINE config 1)."""
+    K, N = 2048, 6144
+    x = _seeded(512, K, seed=6).cuda()
+    w = _seeded(N, K, seed=7, std=0.02).cuda()
+    full = vb.matmul_persistent(x, w.t())
+    sizes = sorted(set([1, 2, 3, 7, 8, 15, 16, 17, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 300, 384,
+                        511, 512] + list(range(1, 513, 37))))
+    for m in sizes:
+        part = vb.matmul_persistent(x[:m], w.t())
+        assert torch.equal(part, full[:m]), f"rows differ between batch {m} and batch 512"
+    # a row's result does not depend on its position in the batch either
+    perm = torch.randperm(512, generator=torch.Generator().manual_seed(0)).cuda()
+    assert torch.equal(vb.matmul_persistent(x[perm].contiguous(), w.t()), full[perm])
+
+
+def test_gemm_large_m_prefill_shape(vb):
+    x = _seeded(2048, 2048, seed=8)
+    w = _seeded(1024, 2048, seed=9, std=0.02)
+    out = vb.matmul_persistent(x.cuda(), w.cuda().t())
+    ref = ops.matmul(x, w.t())
+    _close_bf16(out.cpu(), ref, 2048)
+    assert torch.equal(vb.matmul_persistent(x[:5].cuda(), w.cuda().t()), out[:5])
+
+
+def test_aten_override_routes_linear(vb):
+    lin = torch.nn.Linear(512, 384, bias=True).to(BF).cuda()
+    x = _seeded(9, 512, seed=10).cuda()
+    with vb.set_batch_invariant_mode(True):
+        y = lin(x)
+        y1 = lin(x[:1])
+        lsm = torch.log_softmax(x.float(), dim=-1)
+    assert torch.equal(y[:1], y1)
+    _close_bf16(y.cpu(), ops.matmul(x.cpu(), lin.weight.detach().cpu().t(), lin.bias.detach().cpu()), 512)
+    torch.testing.assert_close(lsm.cpu(), ops.log_softmax(x.float().cpu()), rtol=0, atol=6e-6)
+    assert not vb.is_batch_invariant_mode_enabled()
+
+
+def test_gemm_f32_router(vb):
+    x = _seeded(40, 2048, seed=11, dtype=torch.float32)
+    w = _seeded(64, 2048, seed=12, std=0.02, dtype=torch.float32)
+    out = vb.matmul_persistent(x.cuda(), w.cuda().t())
+    torch.testing.assert_close(out.cpu(), x @ w.t(), rtol=1e-5, atol=1e-5)
+    assert torch.equal(vb.matmul_persistent(x[:3].cuda(), w.cuda().t()), out[:3])
+
+
+def test_status_word_clean(vb):
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0

@@ -1,0 +1,170 @@
+"""Paged causal attention behind the reference's two entry points.
+
+* `flash_attn_varlen_func`: the FlashAttention-compatible varlen interface of
+  vexact/batch_invariant_ops/triton_invariant_attention.py:905 (paged path only:
+  `page_table` / `block_table` and `seqused_k` / `cache_seqlens` aliases).
+* `flash_attention_forward`: the HF `ALL_ATTENTION_FUNCTIONS` adapter of
+  triton_invariant_attention.py:982 and flash_attention.py:26, which reads the
+  thread-local KV-cache context, stores K/V and calls the paged kernel.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import _lib
+from .kv_cache_context import get_kv_cache_context, store_kvcache
+
+ATTENTION_KEYS = ("fa-invariant", "fa-invariant-cute", "triton-invariant")
+
+
+def _require_cuda_int32(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dtype != torch.int32:
+        raise ValueError(f"{name} must be int32, got {t.dtype}")
+
+
+def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                    seqused_k: torch.Tensor, page_table: torch.Tensor, softmax_scale: float,
+                    max_seqlen_q: int) -> torch.Tensor:
+    """q (total_q, heads, dk) against caches (blocks, page, kv_heads, d); returns (total_q, heads, dv)."""
+    for name, t in (("q", q), ("k", k_cache), ("v", v_cache)):
+        if not t.is_cuda:
+            raise ValueError(f"{name} must be a CUDA tensor")
+    _require_cuda_int32("page_table", page_table)
+    _require_cuda_int32("cu_seqlens_q", cu_seqlens_q)
+    _require_cuda_int32("seqused_k", seqused_k)
+    if k_cache.ndim != 4 or v_cache.ndim != 4:
+        raise ValueError("paged flash_attn_varlen_func expects k/v with shape (num_blocks, page_size, heads, dim)")
+    if q.ndim != 3:
+        raise ValueError("paged flash_attn_varlen_func expects q with shape (total_q, heads, dim)")
+    if q.shape[-1] != k_cache.shape[-1]:
+        raise ValueError(f"q and k head_dim must match, got {q.shape[-1]} and {k_cache.shape[-1]}")
+    if q.shape[1] % k_cache.shape[2] != 0:
+        raise ValueError(f"query heads ({q.shape[1]}) must be divisible by KV heads ({k_cache.shape[2]})")
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise NotImplementedError("paged attention is implemented for bf16")
+    if q.stride(-1) != 1:
+        q = q.contiguous()
+    if k_cache.stride(-1) != 1 or v_cache.stride(-1) != 1 or page_table.stride(-1) != 1:
+        raise ValueError("caches and page_table must be contiguous in their last dimension")
+    if not cu_seqlens_q.is_contiguous():
+        cu_seqlens_q = cu_seqlens_q.contiguous()
+    if not seqused_k.is_contiguous():
+        seqused_k = seqused_k.contiguous()
+    out = torch.empty((q.shape[0], q.shape[1], v_cache.shape[-1]), device=q.device, dtype=q.dtype)
+    num_seqs = seqused_k.numel()
+    _lib.check(
+        _lib.load().b200_paged_attn_fwd(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_seqlens_q.data_ptr(),
+            seqused_k.data_ptr(), page_table.data_ptr(), num_seqs, int(max_seqlen_q), q.shape[1],
+            k_cache.shape[2], q.shape[-1], v_cache.shape[-1], k_cache.shape[0], k_cache.shape[1],
+            page_table.shape[1], page_table.stride(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1),
+            k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
+            v_cache.stride(2), float(softmax_scale), _lib.current_stream()),
+        "b200_paged_attn_fwd",
+    )
+    return out
+
+
+def flash_attn_varlen_func(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: Optional[torch.Tensor] = None,
+    max_seqlen_q: Optional[int] = None,
+    max_seqlen_k: Optional[int] = None,
+    dropout_p: float = 0.0,
+    softmax_scale: Optional[float] = None,
+    causal: bool = False,
+    window_size: Optional[tuple] = None,
+    softcap: Optional[float] = None,
+    alibi_slopes: Optional[torch.Tensor] = None,
+    deterministic: bool = False,
+    return_attn_probs: bool = False,
+    block_table: Optional[torch.Tensor] = None,
+    page_table: Optional[torch.Tensor] = None,
+    seqused_k: Optional[torch.Tensor] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    **kwargs,
+):
+    """FlashAttention-style varlen call; returns (out, None).  Paged KV only."""
+    del alibi_slopes, deterministic, return_attn_probs, kwargs, cu_seqlens_k, max_seqlen_k
+    if dropout_p != 0.0:
+        raise NotImplementedError("dropout is not supported")
+    if softcap not in (None, 0.0):
+        raise NotImplementedError("softcap is not supported")
+    if window_size not in (None, (-1, -1)):
+        raise NotImplementedError("sliding-window attention is not supported")
+    if page_table is not None and block_table is not None:
+        raise ValueError("pass only one of page_table or block_table")
+    table = page_table if page_table is not None else block_table
+    if table is None:
+        raise NotImplementedError(
+            "the packed (non-paged) varlen path is the training-side twin and is not part of this library")
+    lens = seqused_k if seqused_k is not None else cache_seqlens
+    if lens is None:
+        raise ValueError("seqused_k or cache_seqlens is required when page_table/block_table is provided")
+    if not causal:
+        raise NotImplementedError("paged flash_attn_varlen_func only supports causal=True")
+    scale = softmax_scale if softmax_scale is not None else q.shape[-1] ** -0.5
+    if max_seqlen_q is None or int(max_seqlen_q) <= 0:
+        # The reference kernel ignores max_seqlen_q; this one sizes its grid with it.
+        max_seqlen_q = q.shape[0]
+    return paged_attention(q, k, v, cu_seqlens_q, lens, table, scale, int(max_seqlen_q)), None
+
+
+def flash_attention_forward(
+    module: nn.Module,
+    query: torch.Tensor,
+    key: Optional[torch.Tensor],
+    value: Optional[torch.Tensor],
+    attention_mask: Optional[torch.Tensor],
+    scaling: float,
+    dropout: float = 0.0,
+    **kwargs,
+):
+    """HF attention-function adapter: (1, heads, T, d) in, (T', heads, dv) out, None for weights."""
+    del attention_mask
+    ctx = get_kv_cache_context()
+    if ctx is None or not ctx.is_paged_attn:
+        raise ValueError("a paged KV-cache context is required (set_kv_cache_context(is_paged_attn=True, ...))")
+    query = query.transpose(1, 2)
+    _, _, num_heads, head_dim = query.shape
+    layer_idx = int(kwargs["layer_idx"]) if "layer_idx" in kwargs else int(getattr(module, "layer_idx", 0))
+    k_cache = ctx.key_cache[layer_idx]
+    v_cache = ctx.value_cache[layer_idx]
+    if key is not None and value is not None:
+        key = key.transpose(1, 2)
+        value = value.transpose(1, 2)
+        kv_heads = key.shape[2]
+        key_flat = key.reshape(-1, kv_heads, head_dim)
+        value_flat = value.reshape(-1, kv_heads, value.shape[-1])
+        if key_flat.stride(1) != head_dim or key_flat.stride(2) != 1:
+            key_flat = key_flat.contiguous()
+        if value_flat.stride(1) != value.shape[-1] or value_flat.stride(2) != 1:
+            value_flat = value_flat.contiguous()
+        store_kvcache(key_flat, value_flat, k_cache, v_cache, ctx.slot_mapping)
+    q_flat = query.reshape(-1, num_heads, head_dim)
+    return flash_attn_varlen_func(
+        q_flat, k_cache, v_cache,
+        cu_seqlens_q=ctx.query_start_loc,
+        max_seqlen_q=ctx.max_seqlen_q,
+        seqused_k=ctx.context_lens,
+        page_table=ctx.block_tables,
+        dropout_p=dropout,
+        softmax_scale=scaling,
+        causal=True,
+    )
+
+
+def register_attention_functions() -> None:
+    """Install the adapter under the reference's attention keys (inferencer.py:51-55)."""
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+    for key in ATTENTION_KEYS:
+        ALL_ATTENTION_FUNCTIONS[key] = flash_attention_forward

@@ -1,0 +1,105 @@
+// Shared device/host helpers for the sm_100a rollout-forward kernels.
+//
+// Conventions used by every kernel in this directory:
+//   * every entry point launches on the caller's stream, allocates nothing and
+//     never synchronises, so it can be captured into a CUDA graph;
+//   * every reduction uses one fixed tree that depends only on the row length,
+//     never on the number of rows, so a row's result is bitwise independent of
+//     the batch it is computed in;
+//   * every spin-wait is bounded: on expiry the kernel writes a code into the
+//     device status word (see b200_status_read) and returns.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define B200_OK 0
+#define B200_ERR_ARG (-1)
+#define B200_ERR_SHAPE (-2)
+#define B200_ERR_LAUNCH (-3)
+#define B200_ERR_DRIVER (-4)
+
+// Codes a kernel may leave in the device status word.
+#define B200_STATUS_OK 0
+#define B200_STATUS_WAIT_EXPIRED 1
+#define B200_STATUS_BAD_INDEX 2
+
+namespace b200 {
+
+// Device status word: [0] = first non-zero code seen, [1] = detail (barrier id
+// or offending index), [2] = block id, [3] = spare.
+__device__ int g_status[4];  // one copy: all kernels are built as a single translation unit
+
+__device__ __forceinline__ void report_status(int code, int detail) {
+  if (atomicCAS(&g_status[0], 0, code) == 0) {
+    g_status[1] = detail;
+    g_status[2] = (int)blockIdx.x;
+  }
+}
+
+__device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16_rn(v); }
+// Round an fp32 value to bf16 precision and keep it in fp32 (models a bf16
+// tensor being materialised between two torch ops).
+__device__ __forceinline__ float round_bf(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ void unpack_bf2(uint32_t v, float& lo, float& hi) {
+  __nv_bfloat162 t = *reinterpret_cast<__nv_bfloat162*>(&v);
+  lo = __low2float(t);
+  hi = __high2float(t);
+}
+
+// Fixed butterfly reductions over a full warp.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed order: warp butterflies, then warp 0 folds the
+// per-warp partials with another butterfly.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+
+}  // namespace b200

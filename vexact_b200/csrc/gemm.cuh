@@ -1,0 +1,478 @@
+// Weight-streaming bf16 GEMM on tcgen05 tensor cores with TMA-staged tiles.
+// One kernel serves the dense projections (aten::mm / aten::addmm) and the
+// fused-MoE grouped GEMMs.
+//
+// Replaces vexact/batch_invariant_ops/batch_invariant_ops.py:54-229
+// (matmul_kernel_persistent / matmul_persistent: fp32 accumulation, sequential K
+// loop, no split-K, bias added in fp32 before the cast) and the grouped GEMMs of
+// vexact/batch_invariant_ops/fused_moe.py:319-339 (quack gemm with cu_seqlens_m)
+// / group_gemm/kernel/group_gemm.py:65-250 (group_gemm_same_nk).
+//
+// Orientation.  out[t, n] = sum_k X[t, k] * W[n, k] with W = nn.Linear.weight
+// ([N, K], K contiguous) and X = activations ([T, K], K contiguous).  The weight
+// rows sit on the UMMA M axis (always 128 rows per instruction) and the tokens on
+// the UMMA N axis, so decode batches stream each weight tile from HBM exactly
+// once and a one-token batch costs a 16-column instruction, not a 128-row one.
+//
+// Batch invariance.  A token's dot products are always computed by M=128, K=16
+// instructions walking K from 0 upward in 64-element stages with fp32
+// accumulation in tensor memory; there is no split-K and nothing depends on how
+// many tokens share the tile or where in the tile the token sits.
+//
+// Pipeline.  Persistent CTAs (one per SM) walk a static round-robin tile list.
+// Warp 0 issues TMA loads into a ring of shared-memory stages, warp 1 issues
+// tcgen05.mma into one of two tensor-memory accumulators, warps 2-5 drain the
+// other accumulator (tcgen05.ld), apply the epilogue and store.  All waits are
+// bounded (ptx::mbar_wait).
+//
+// Algorithmic bytes per launch: 2*(N*K + T*K + T*N); the weight term dominates
+// for decode shapes, so the roofline is HBM bandwidth.
+#pragma once
+#include <cuda.h>  // CUtensorMap and enums only: the encoder is looked up at run time, libcuda is not linked
+
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace b200 {
+
+constexpr int GEMM_BK = 64;             // K elements per stage = one 128-byte swizzle row
+constexpr int GEMM_WTILE = 128;         // weight rows per tile = UMMA M
+constexpr int GEMM_WBYTES = GEMM_WTILE * GEMM_BK * 2;
+constexpr int GEMM_THREADS = 192;       // producer warp, MMA warp, 4 epilogue warps
+constexpr int GEMM_MAX_STAGES = 12;
+constexpr int GEMM_SMEM_BUDGET = 227 * 1024;
+constexpr int GEMM_EXCH_PITCH = 256 + 8;  // bf16 elements per feature row in the SwiGLU exchange buffer
+
+struct GemmParams {
+  int n_w;               // output features per group (plain: N; SwiGLU: intermediate size I)
+  int k;                 // reduction length
+  int w_tiles;           // weight tiles per group
+  int w_rows_per_group;  // rows of the 2-D weight view per group (plain: N; SwiGLU: 2*I)
+  int up_offset;         // SwiGLU: row offset of the "up" half inside a group (= I)
+  // Token tiling.  Dense: tiles are computed from (t_rows, rows_per_tile).  Grouped:
+  // tile_table[i] = {group, first_row, n_rows, 0}, *tile_count entries are valid.
+  int t_rows;
+  int rows_per_tile;
+  int dense_t_tiles;
+  const int4* tile_table;
+  const int* tile_count;
+  int xbox;       // rows per activation TMA box (multiple of 16)
+  int xrows_max;  // largest token count of any tile (multiple of xbox, <= 256)
+  int stages;
+  int tmem_cols;  // power of two >= 2 * xrows_max
+  // Epilogue.
+  void* out;
+  long long ldo;
+  int out_f32;
+  const __nv_bfloat16* bias;       // [n_w] or null (plain mode)
+  const __nv_bfloat16* row_scale;  // [rows] or null (SwiGLU mode: routing weight of each permuted row)
+  uint64_t w_policy;
+};
+
+struct GemmTile {
+  int group, row0, n, wt;
+};
+
+__device__ __forceinline__ bool gemm_tile(const GemmParams& p, int t_tiles, long long linear, GemmTile& t) {
+  if (linear >= (long long)t_tiles * p.w_tiles) return false;
+  t.wt = (int)(linear / t_tiles);
+  const int tt = (int)(linear % t_tiles);
+  if (p.tile_table) {
+    const int4 e = p.tile_table[tt];
+    t.group = e.x;
+    t.row0 = e.y;
+    t.n = e.z;
+  } else {
+    t.group = 0;
+    t.row0 = tt * p.rows_per_tile;
+    t.n = min(p.rows_per_tile, p.t_rows - t.row0);
+  }
+  return true;
+}
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+               const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // Control block, then 1024-byte aligned stages (the 128-byte swizzle repeats every 1024 B).
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
+  const int S = p.stages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_raw + (2 * GEMM_MAX_STAGES + 4) * 8);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (2 * GEMM_MAX_STAGES + 4) * 8 + 8);
+  const uint32_t smem_base = ptx::smem_u32(smem_raw);
+  const uint32_t stage_base = (smem_base + 256 + 1023) & ~1023u;
+  const int stage_bytes = GEMM_WBYTES + p.xrows_max * (GEMM_BK * 2);
+  __nv_bfloat16* exch =
+      reinterpret_cast<__nv_bfloat16*>(smem_raw + (stage_base - smem_base) + (size_t)S * stage_bytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto full_bar = [&](int s) { return smem_base + 8u * s; };
+  auto empty_bar = [&](int s) { return smem_base + 8u * (S + s); };
+  auto tfull_bar = [&](int b) { return smem_base + 8u * (2 * S + b); };
+  auto tempty_bar = [&](int b) { return smem_base + 8u * (2 * S + 2 + b); };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(tfull_bar(b), 1);
+      ptx::mbar_init(tempty_bar(b), 128);
+    }
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_x);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
+  const int num_kb = (p.k + GEMM_BK - 1) / GEMM_BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;  // running stage counter across tiles
+      bool ok = true;
+      for (long long lin = blockIdx.x; ok; lin += gridDim.x) {
+        GemmTile t;
+        if (!gemm_tile(p, t_tiles, lin, t)) break;
+        const int nbox = (t.n + p.xbox - 1) / p.xbox;
+        const uint32_t tx = GEMM_WBYTES + (uint32_t)nbox * p.xbox * (GEMM_BK * 2);
+        const int wrow = t.group * p.w_rows_per_group + t.wt * (SWIGLU ? 64 : GEMM_WTILE);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag, 100 + s)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
+          const uint32_t sx = sw + GEMM_WBYTES;
+          ptx::mbar_expect_tx(full_bar(s), tx);
+          if (SWIGLU) {
+            ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
+            ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kb * GEMM_BK, wrow + p.up_offset,
+                             p.w_policy);
+          } else {
+            ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
+          }
+          for (int b = 0; b < nbox; ++b)
+            ptx::tma_load_2d(sx + (uint32_t)b * p.xbox * (GEMM_BK * 2), &tm_x, full_bar(s), kb * GEMM_BK,
+                             t.row0 + b * p.xbox, ptx::kEvictLast);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (long long lin = blockIdx.x; ok; lin += gridDim.x, ++tile_it) {
+        GemmTile t;
+        if (!gemm_tile(p, t_tiles, lin, t)) break;
+        const int buf = tile_it & 1;
+        const int nbox = (t.n + p.xbox - 1) / p.xbox;
+        const uint32_t idesc = ptx::umma_idesc_bf16_m128((uint32_t)(nbox * p.xbox));
+        if (!ptx::mbar_wait(tempty_bar(buf), ((tile_it >> 1) & 1) ^ 1, abort_flag, 200 + buf)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.xrows_max);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % S;
+          if (!ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag, 300 + s)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
+          const uint32_t sx = sw + GEMM_WBYTES;
+#pragma unroll
+          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+            const uint64_t da = ptx::umma_desc_k_sw128(sw + kk * 32);
+            const uint64_t db = ptx::umma_desc_k_sw128(sx + kk * 32);
+            ptx::umma_bf16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(s));  // stage is free once these MMAs have read it
+        }
+        if (ok) ptx::umma_commit(tfull_bar(buf));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;              // tensor-memory lane quadrant this warp may read
+    uint32_t tile_it = 0;
+    for (long long lin = blockIdx.x;; lin += gridDim.x, ++tile_it) {
+      GemmTile t;
+      if (!gemm_tile(p, t_tiles, lin, t)) break;
+      const int buf = tile_it & 1;
+      const bool ready = ptx::mbar_wait(tfull_bar(buf), (tile_it >> 1) & 1, abort_flag, 400 + buf);
+      if (!__all_sync(0xffffffffu, ready)) break;
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.xrows_max);
+      const int ncol = ((t.n + 15) / 16) * 16;
+      if (!SWIGLU) {
+        const int f = t.wt * GEMM_WTILE + q * 32 + lane;
+        const bool fvalid = f < p.n_w;
+        const float bias = (p.bias && fvalid) ? bf2f(p.bias[f]) : 0.f;
+        for (int c0 = 0; c0 < ncol; c0 += 16) {
+          uint32_t r[16];
+          ptx::tmem_ld16(taddr + c0, r);
+          ptx::tmem_ld_wait();
+          if (fvalid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int c = c0 + j;
+              if (c < t.n) {
+                const float v = __uint_as_float(r[j]) + bias;
+                const long long o = (long long)(t.row0 + c) * p.ldo + f;
+                if (p.out_f32)
+                  reinterpret_cast<float*>(p.out)[o] = v;
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[o] = f2bf(v);
+              }
+            }
+          }
+        }
+      } else {
+        // Lanes 0..63 hold the gate rows, lanes 64..127 the up rows of the same 64 features.
+        const int fi = (q & 1) * 32 + lane;
+        if (q >= 2) {
+          for (int c0 = 0; c0 < ncol; c0 += 16) {
+            uint32_t r[16];
+            ptx::tmem_ld16(taddr + c0, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) exch[fi * GEMM_EXCH_PITCH + c0 + j] = f2bf(__uint_as_float(r[j]));
+          }
+        }
+        ptx::named_barrier_sync(1, 128);
+        if (q < 2) {
+          const int f = t.wt * 64 + fi;
+          const bool fvalid = f < p.n_w;
+          for (int c0 = 0; c0 < ncol; c0 += 16) {
+            uint32_t r[16];
+            ptx::tmem_ld16(taddr + c0, r);
+            ptx::tmem_ld_wait();
+            if (fvalid) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int c = c0 + j;
+                if (c < t.n) {
+                  // Rounding points of fused_moe.py:319-336: each GEMM output, silu(), the
+                  // gate*up product and the routing-weight product are bf16 tensors.
+                  const float g = round_bf(__uint_as_float(r[j]));
+                  const float u = bf2f(exch[fi * GEMM_EXCH_PITCH + c]);
+                  const float sg = round_bf(g / (1.0f + expf(-g)));
+                  float h = round_bf(sg * u);
+                  if (p.row_scale) h = round_bf(h * bf2f(p.row_scale[t.row0 + c]));
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[(long long)(t.row0 + c) * p.ldo + f] = f2bf(h);
+                }
+              }
+            }
+          }
+        }
+        ptx::named_barrier_sync(1, 128);  // exchange buffer is reused by the next tile
+      }
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // Teardown.  On an aborted run give in-flight TMA copies time to land before the CTA exits.
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) {
+    }
+  }
+  ptx::tc_fence_after();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+
+// 2-D bf16 tensor [rows, cols] with `row_stride` elements between rows; box = 64 cols x box_rows,
+// 128-byte swizzle.  Out-of-range elements read as zero.
+inline int make_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                        uint32_t box_rows) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return B200_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride * 2) % 16 || box_rows == 0 || box_rows > 256)
+    return B200_ERR_ARG;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_stride * 2};
+  cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
+}
+
+inline int sm_count() {
+  static int n = []() {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+    return v;
+  }();
+  return n;
+}
+
+template <bool SWIGLU>
+inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams& p, long long max_tiles,
+                       cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_ws_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             GEMM_SMEM_BUDGET) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    attr_set = true;
+  }
+  const int stage_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
+  const int exch_bytes = SWIGLU ? 64 * GEMM_EXCH_PITCH * 2 : 0;
+  int stages = (GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes) / stage_bytes;
+  if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
+  if (stages < 2) return B200_ERR_SHAPE;
+  p.stages = stages;
+  int cols = 32;
+  while (cols < 2 * p.xrows_max) cols <<= 1;
+  if (cols > 512) return B200_ERR_SHAPE;
+  p.tmem_cols = cols;
+  const size_t smem = 256 + 1024 + (size_t)stages * stage_bytes + exch_bytes;
+  long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
+  if (grid <= 0) return B200_OK;
+  gemm_ws_kernel<SWIGLU><<<(unsigned)grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
+  return launch_status();
+}
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+}  // namespace b200
+
+namespace b200 {
+// fp32 GEMM for the DeepSeek-V3 router (modeling_deepseek_v3.py:97-100 runs F.linear in fp32):
+// one warp per output element, lanes stride over K, fixed butterfly.  Exact fp32 FMA arithmetic
+// (the reference's Triton path feeds tl.dot fp32 operands, i.e. TF32 inputs).
+__global__ void __launch_bounds__(256)
+gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                float* __restrict__ out, long long T, int N, int K, long long x_stride, long long w_stride,
+                long long out_stride) {
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= T * N) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = wid / N;
+  const int n = (int)(wid % N);
+  const float* xr = x + t * x_stride;
+  const float* wr = w + (long long)n * w_stride;
+  float acc = 0.f;
+  for (int k = lane; k < K; k += 32) acc = fmaf(xr[k], wr[k], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) out[t * out_stride + n] = acc + (bias ? bias[n] : 0.f);
+}
+}  // namespace b200
+
+extern "C" int b200_gemm_f32(const void* x, const void* w, const void* bias, void* out, long long T, int N,
+                             int K, long long x_row_stride, long long w_row_stride, long long out_row_stride,
+                             void* stream) {
+  using namespace b200;
+  if (!x || !w || !out || T < 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
+  if (T == 0) return B200_OK;
+  const long long warps = T * N;
+  gemm_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      (const float*)x, (const float*)w, (const float*)bias, (float*)out, T, N, K, x_row_stride, w_row_stride,
+      out_row_stride);
+  return launch_status();
+}
+
+// out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N], added in fp32 before the cast).
+// x rows are `x_row_stride` elements apart, w rows `w_row_stride`, out rows `out_row_stride`.
+extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, long long T, int N,
+                              int K, long long x_row_stride, long long w_row_stride, long long out_row_stride,
+                              int out_dtype /*0 = bf16, 1 = f32*/, void* stream) {
+  using namespace b200;
+  if (!x || !w || !out || T < 0 || N <= 0 || K <= 0 || (out_dtype != 0 && out_dtype != 1)) return B200_ERR_ARG;
+  if (K % 8 != 0 || x_row_stride % 8 != 0 || w_row_stride % 8 != 0) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  if (T > 0x7fffffffLL) return B200_ERR_SHAPE;
+  GemmParams p{};
+  p.n_w = N;
+  p.k = K;
+  p.w_tiles = (N + GEMM_WTILE - 1) / GEMM_WTILE;
+  p.w_rows_per_group = N;
+  p.up_offset = 0;
+  p.t_rows = (int)T;
+  p.dense_t_tiles = (int)((T + 255) / 256);
+  p.rows_per_tile = round_up((int)((T + p.dense_t_tiles - 1) / p.dense_t_tiles), 16);
+  p.tile_table = nullptr;
+  p.tile_count = nullptr;
+  p.xbox = p.rows_per_tile;
+  p.xrows_max = p.rows_per_tile;
+  p.out = out;
+  p.ldo = out_row_stride;
+  p.out_f32 = out_dtype;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.row_scale = nullptr;
+  p.w_policy = p.dense_t_tiles == 1 ? ptx::kEvictFirst : ptx::kEvictNormal;
+  CUtensorMap tw, tx;
+  int rc = make_tmap_2d(&tw, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_row_stride, GEMM_WTILE);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, x, (uint64_t)T, (uint64_t)K, (uint64_t)x_row_stride, (uint32_t)p.xbox);
+  if (rc) return rc;
+  return gemm_launch<false>(tw, tx, p, (long long)p.w_tiles * p.dense_t_tiles, (cudaStream_t)stream);
+}
+
+// Grouped GEMM over expert-sorted rows.
+//   mode 0: out[r, n] = x[r, :] . w[g(r), n, :]                      (w: [G, N, K])
+//   mode 1: out[r, i] = silu(x . w[g, i, :]) * (x . w[g, I + i, :]) * row_scale[r]   (w: [G, 2I, K], n_out = I)
+// tile_table / tile_count come from b200_moe_permute: every tile lies inside one group.
+extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, void* out,
+                                     const void* tile_table, const void* tile_count, long long x_rows,
+                                     int num_groups, int n_out, int K, long long out_row_stride,
+                                     int max_tiles, int tile_rows_max, int mode, void* stream) {
+  using namespace b200;
+  if (!x || !w || !out || !tile_table || !tile_count || x_rows < 0 || num_groups <= 0 || n_out <= 0 || K <= 0 ||
+      max_tiles < 0 || (mode != 0 && mode != 1))
+    return B200_ERR_ARG;
+  if (K % 8 != 0 || tile_rows_max % 16 != 0 || tile_rows_max <= 0 || tile_rows_max > 256) return B200_ERR_SHAPE;
+  if (x_rows == 0 || max_tiles == 0) return B200_OK;
+  GemmParams p{};
+  p.n_w = n_out;
+  p.k = K;
+  p.w_tiles = mode == 1 ? (n_out + 63) / 64 : (n_out + GEMM_WTILE - 1) / GEMM_WTILE;
+  p.w_rows_per_group = mode == 1 ? 2 * n_out : n_out;
+  p.up_offset = mode == 1 ? n_out : 0;
+  p.t_rows = (int)x_rows;
+  p.rows_per_tile = 0;
+  p.dense_t_tiles = 0;
+  p.tile_table = (const int4*)tile_table;
+  p.tile_count = (const int*)tile_count;
+  p.xbox = 16;
+  p.xrows_max = tile_rows_max;
+  p.out = out;
+  p.ldo = out_row_stride;
+  p.out_f32 = 0;
+  p.bias = nullptr;
+  p.row_scale = (const __nv_bfloat16*)row_scale;
+  p.w_policy = ptx::kEvictFirst;
+  CUtensorMap tw, tx;
+  int rc = make_tmap_2d(&tw, w, (uint64_t)num_groups * p.w_rows_per_group, (uint64_t)K, (uint64_t)K,
+                        mode == 1 ? 64 : GEMM_WTILE);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, 16);
+  if (rc) return rc;
+  const long long tiles = (long long)max_tiles * p.w_tiles;
+  if (mode == 1) return gemm_launch<true>(tw, tx, p, tiles, (cudaStream_t)stream);
+  return gemm_launch<false>(tw, tx, p, tiles, (cudaStream_t)stream);
+}

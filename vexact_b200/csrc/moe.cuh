@@ -1,0 +1,450 @@
+// MoE routing, token permutation and the fixed-order top-k reduction.
+// Integer parts are bit-exact; the floating-point parts round where the
+// reference's torch ops materialise tensors.
+//
+// Replaces
+//   vexact/models/qwen3_moe/modeling_qwen3_moe.py:128-134   softmax -> topk -> renorm -> cast
+//   vexact/models/deepseek_v3/modeling_deepseek_v3.py:185-208 sigmoid + bias, group-limited top-k
+//   vexact/batch_invariant_ops/fused_moe.py:268-292          _build_moe_indices (stable argsort by
+//       expert, inverse permutation, histogram, cumulative sum)
+//   vexact/batch_invariant_ops/group_gemm/kernel/moe.py:28-78, 255-335 (histogram, scatter)
+//   vexact/batch_invariant_ops/group_gemm/kernel/moe.py:86-160 (moe_gather: fp32 sum over the k
+//       expert rows of a token in k order, then one cast)
+//   vexact/batch_invariant_ops/fused_moe.py:325-336           silu * up * routing weight
+//
+// Top-k ties are broken towards the lower expert index; selected experts are
+// returned in descending weight order (what torch.topk(sorted=True) returns).
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int MOE_MAX_EXPERTS = 256;
+constexpr int MOE_MAX_TOPK = 16;
+
+// One warp per token.  Each lane owns experts lane, lane + 32, ... (up to 8).
+template <typename TIn>
+__global__ void __launch_bounds__(256)
+moe_route_softmax_topk_kernel(const TIn* __restrict__ logits, long long row_stride,
+                              __nv_bfloat16* __restrict__ w_bf16, float* __restrict__ w_f32,
+                              int* __restrict__ idx_i32, long long* __restrict__ idx_i64, long long T, int E,
+                              int topk, int renorm) {
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= T) return;
+  const int lane = threadIdx.x & 31;
+  const TIn* row = logits + tok * row_stride;
+  constexpr int PER = MOE_MAX_EXPERTS / 32;
+  float v[PER];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? (float)row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? expf(v[i] - mx) : 0.f;
+    sum += v[i];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) v[i] = v[i] / sum;  // softmax probabilities (fp32)
+
+  float sel_w[MOE_MAX_TOPK];
+  int sel_e[MOE_MAX_TOPK];
+  for (int k = 0; k < topk; ++k) {
+    // lane-local best (lowest index on ties), then a butterfly with the same tie rule
+    float bv = -1.f;
+    int be = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && (v[i] > bv)) {
+        bv = v[i];
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    sel_w[k] = bv;
+    sel_e[k] = be;
+    if ((be & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i)
+        if (lane + 32 * i == be) v[i] = -2.f;  // remove from the candidate set
+    }
+  }
+  if (lane == 0) {
+    float denom = 1.f;
+    if (renorm) {
+      denom = 0.f;
+      for (int k = 0; k < topk; ++k) denom += sel_w[k];
+    }
+    for (int k = 0; k < topk; ++k) {
+      const float w = renorm ? sel_w[k] / denom : sel_w[k];
+      if (w_bf16) w_bf16[tok * topk + k] = f2bf(w);
+      if (w_f32) w_f32[tok * topk + k] = w;
+      if (idx_i32) idx_i32[tok * topk + k] = sel_e[k];
+      if (idx_i64) idx_i64[tok * topk + k] = sel_e[k];
+    }
+  }
+}
+
+// DeepSeek-V3 routing.  One warp per token; E <= 256.
+//   s = sigmoid(logit); c = s + bias; group score = sum of the group's top-2 c;
+//   keep the top `topk_group` groups, zero the rest (masked_fill 0.0), top-k over c;
+//   weights = s[selected] (/ (sum + 1e-20) if renorm) * scale.
+// torch.topk(sorted=False) leaves the order of the selected experts unspecified; this kernel
+// returns them in descending choice-score order, ties to the lower index.
+__global__ void __launch_bounds__(256)
+moe_route_sigmoid_group_topk_kernel(const float* __restrict__ logits, long long row_stride,
+                                    const float* __restrict__ bias, float* __restrict__ w_out,
+                                    int* __restrict__ idx_i32, long long* __restrict__ idx_i64, long long T,
+                                    int E, int n_group, int topk_group, int topk, int renorm, float scale) {
+  __shared__ float s_sig[8][MOE_MAX_EXPERTS];
+  __shared__ float s_choice[8][MOE_MAX_EXPERTS];
+  __shared__ float s_gscore[8][32];
+  const int wib = threadIdx.x >> 5;
+  const long long tok = (long long)blockIdx.x * 8 + wib;
+  if (tok >= T) return;
+  const int lane = threadIdx.x & 31;
+  const float* row = logits + tok * row_stride;
+  float* sig = s_sig[wib];
+  float* choice = s_choice[wib];
+  for (int e = lane; e < E; e += 32) {
+    const float s = 1.0f / (1.0f + expf(-row[e]));
+    sig[e] = s;
+    choice[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  const int gsize = E / n_group;
+  for (int gidx = lane; gidx < n_group; gidx += 32) {
+    float t1 = -INFINITY, t2 = -INFINITY;
+    for (int j = 0; j < gsize; ++j) {
+      const float c = choice[gidx * gsize + j];
+      if (c > t1) {
+        t2 = t1;
+        t1 = c;
+      } else if (c > t2) {
+        t2 = c;
+      }
+    }
+    s_gscore[wib][gidx] = t1 + t2;
+  }
+  __syncwarp();
+  // Select the top groups (lane 0, n_group <= 32), then mask the others to 0.0.
+  unsigned keep = 0;
+  if (lane == 0) {
+    for (int r = 0; r < topk_group; ++r) {
+      float bv = -INFINITY;
+      int bg = -1;
+      for (int gi = 0; gi < n_group; ++gi)
+        if (!((keep >> gi) & 1u) && s_gscore[wib][gi] > bv) {
+          bv = s_gscore[wib][gi];
+          bg = gi;
+        }
+      if (bg >= 0) keep |= 1u << bg;
+    }
+  }
+  keep = __shfl_sync(0xffffffffu, keep, 0);
+  for (int e = lane; e < E; e += 32)
+    if (!((keep >> (e / gsize)) & 1u)) choice[e] = 0.0f;
+  __syncwarp();
+  float sel_w[MOE_MAX_TOPK];
+  int sel_e[MOE_MAX_TOPK];
+  for (int k = 0; k < topk; ++k) {
+    float bv = -INFINITY;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float c = choice[e];
+      if (c > bv) {
+        bv = c;
+        be = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ov > bv || (ov == bv && oe < be)) {
+        bv = ov;
+        be = oe;
+      }
+    }
+    sel_e[k] = be;
+    sel_w[k] = sig[be];
+    __syncwarp();
+    if (lane == 0) choice[be] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane == 0) {
+    float denom = 1.f;
+    if (renorm) {
+      denom = 0.f;
+      for (int k = 0; k < topk; ++k) denom += sel_w[k];
+      denom += 1e-20f;
+    }
+    for (int k = 0; k < topk; ++k) {
+      float w = renorm ? sel_w[k] / denom : sel_w[k];
+      w = w * scale;
+      w_out[tok * topk + k] = w;
+      if (idx_i32) idx_i32[tok * topk + k] = sel_e[k];
+      if (idx_i64) idx_i64[tok * topk + k] = sel_e[k];
+    }
+  }
+}
+
+// Index build: one CTA of 1024 threads.  For flat index f = t * topk + k (the order
+// expert_index.flatten() has) computes its position in the stable sort by expert:
+//   scatter_index[f] = cu_seqlens[e_f] + #{f' < f : e_f' == e_f}
+// plus cu_seqlens[E + 1] and the token-tile table of the grouped GEMM (tiles of at most
+// `tile_rows` consecutive rows of one expert).
+template <typename TIdx>
+__global__ void __launch_bounds__(1024)
+moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_rows,
+                 int* __restrict__ scatter_index, int* __restrict__ cu_seqlens, int4* __restrict__ tile_table,
+                 int* __restrict__ tile_count, int max_tiles) {
+  __shared__ int hist[MOE_MAX_EXPERTS];
+  __shared__ int base[MOE_MAX_EXPERTS];
+  __shared__ int cnt[32][MOE_MAX_EXPERTS];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int e = tid; e < E; e += 1024) hist[e] = 0;
+  __syncthreads();
+  for (long long i = tid; i < n; i += 1024) {
+    const long long e = (long long)experts[i];
+    if (e >= 0 && e < E)
+      atomicAdd(&hist[(int)e], 1);
+    else
+      report_status(B200_STATUS_BAD_INDEX, (int)e);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0, nt = 0;
+    for (int e = 0; e < E; ++e) {
+      base[e] = run;
+      cu_seqlens[e] = run;
+      for (int r = 0; r < hist[e]; r += tile_rows) {
+        if (nt < max_tiles) tile_table[nt] = make_int4(e, run + r, min(tile_rows, hist[e] - r), 0);
+        ++nt;
+      }
+      run += hist[e];
+    }
+    cu_seqlens[E] = run;
+    *tile_count = min(nt, max_tiles);
+  }
+  __syncthreads();
+  for (long long c0 = 0; c0 < n; c0 += 1024) {
+    for (int i = tid; i < 32 * E; i += 1024) cnt[i / E][i % E] = 0;
+    __syncthreads();
+    const long long i = c0 + tid;
+    int e = -1;
+    if (i < n) {
+      const long long ev = (long long)experts[i];
+      if (ev >= 0 && ev < E) e = (int)ev;
+    }
+    const unsigned mask = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(mask & ((1u << lane) - 1u));
+    if (rank == 0 && e >= 0) cnt[warp][e] = __popc(mask);
+    __syncthreads();
+    if (tid < E) {
+      int run = base[tid];
+      for (int w = 0; w < 32; ++w) {
+        const int c = cnt[w][tid];
+        cnt[w][tid] = run;
+        run += c;
+      }
+      base[tid] = run;
+    }
+    __syncthreads();
+    if (i < n) scatter_index[i] = e >= 0 ? cnt[warp][e] + rank : -1;
+    __syncthreads();
+  }
+}
+
+// Row scatter: x_perm[scatter_index[f]] = x[f / topk]; row_scale[scatter_index[f]] = weights[f].
+__global__ void __launch_bounds__(128)
+moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
+                        const __nv_bfloat16* __restrict__ weights, const int* __restrict__ scatter_index,
+                        __nv_bfloat16* __restrict__ x_perm, __nv_bfloat16* __restrict__ row_scale, int H,
+                        int topk) {
+  const long long f = blockIdx.x;
+  const int pos = scatter_index[f];
+  if (pos < 0) return;
+  const __nv_bfloat16* src = x + (f / topk) * x_stride;
+  __nv_bfloat16* dst = x_perm + (long long)pos * H;
+  for (int i = threadIdx.x; i < (H >> 3); i += 128)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  if (threadIdx.x == 0 && row_scale && weights) row_scale[pos] = weights[f];
+}
+
+// out[t] = bf16( sum_k fp32(y[scatter_index[t, k]]) ), k ascending; optionally followed by
+// out[t] = bf16(fp32(out[t]) + fp32(addend[t])) (shared-expert or residual add as a separate bf16 op).
+__global__ void __launch_bounds__(128)
+moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ scatter_index,
+                            const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out, int H,
+                            int topk) {
+  const long long t = blockIdx.x;
+  for (int v = threadIdx.x; v < (H >> 3); v += 128) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      const int pos = scatter_index[t * topk + k];
+      if (pos < 0) continue;
+      const uint4 r = reinterpret_cast<const uint4*>(y + (long long)pos * H)[v];
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a, b;
+        unpack_bf2(rp[j], a, b);
+        acc[2 * j] += a;
+        acc[2 * j + 1] += b;
+      }
+    }
+    if (addend) {
+      const uint4 r = reinterpret_cast<const uint4*>(addend + t * H)[v];
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a, b;
+        unpack_bf2(rp[j], a, b);
+        acc[2 * j] = round_bf(acc[2 * j]) + a;
+        acc[2 * j + 1] = round_bf(acc[2 * j + 1]) + b;
+      }
+    }
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) op[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(out + t * H)[v] = o;
+  }
+}
+
+// h = bf16(bf16(bf16(silu(g)) * u) * s): the unfused tail of fc1 for split gate / up weights.
+__global__ void __launch_bounds__(256)
+swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+                    const __nv_bfloat16* __restrict__ row_scale, __nv_bfloat16* __restrict__ out, long long rows,
+                    int I) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= rows * I) return;
+  const float g = bf2f(gate[i]);
+  const float u = bf2f(up[i]);
+  const float sg = round_bf(g / (1.0f + expf(-g)));
+  float h = round_bf(sg * u);
+  if (row_scale) h = round_bf(h * bf2f(row_scale[i / I]));
+  out[i] = f2bf(h);
+}
+
+}  // namespace b200
+
+extern "C" int b200_moe_route_softmax_topk(const void* logits, int logits_dtype /*0 = f32, 1 = bf16*/,
+                                           long long row_stride, void* weights_bf16, void* weights_f32,
+                                           void* experts_i32, void* experts_i64, long long T, int E, int topk,
+                                           int renorm, void* stream) {
+  using namespace b200;
+  if (!logits || T < 0 || E <= 0 || topk <= 0 || (!experts_i32 && !experts_i64) || (!weights_bf16 && !weights_f32))
+    return B200_ERR_ARG;
+  if (E > MOE_MAX_EXPERTS || topk > MOE_MAX_TOPK || topk > E) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)((T + 7) / 8);
+  if (logits_dtype == 0)
+    moe_route_softmax_topk_kernel<float><<<grid, 256, 0, st>>>(
+        (const float*)logits, row_stride, (__nv_bfloat16*)weights_bf16, (float*)weights_f32, (int*)experts_i32,
+        (long long*)experts_i64, T, E, topk, renorm);
+  else if (logits_dtype == 1)
+    moe_route_softmax_topk_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)logits, row_stride, (__nv_bfloat16*)weights_bf16, (float*)weights_f32,
+        (int*)experts_i32, (long long*)experts_i64, T, E, topk, renorm);
+  else
+    return B200_ERR_ARG;
+  return launch_status();
+}
+
+extern "C" int b200_moe_route_sigmoid_group_topk(const void* logits_f32, long long row_stride,
+                                                 const void* bias_f32, void* weights_f32, void* experts_i32,
+                                                 void* experts_i64, long long T, int E, int n_group,
+                                                 int topk_group, int topk, int renorm, float scale,
+                                                 void* stream) {
+  using namespace b200;
+  if (!logits_f32 || !weights_f32 || (!experts_i32 && !experts_i64) || T < 0 || E <= 0 || n_group <= 0 ||
+      topk_group <= 0 || topk <= 0)
+    return B200_ERR_ARG;
+  if (E > MOE_MAX_EXPERTS || topk > MOE_MAX_TOPK || n_group > 32 || E % n_group != 0 || topk_group > n_group ||
+      E / n_group < 2)
+    return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  moe_route_sigmoid_group_topk_kernel<<<(unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      (const float*)logits_f32, row_stride, (const float*)bias_f32, (float*)weights_f32, (int*)experts_i32,
+      (long long*)experts_i64, T, E, n_group, topk_group, topk, renorm, scale);
+  return launch_status();
+}
+
+// Builds the permutation (scatter_index, cu_seqlens, tile table) and moves the rows.
+//   experts [T, topk] (int32 or int64), weights [T, topk] bf16 (may be null), x [T, H] bf16
+//   -> scatter_index [T * topk] i32, cu_seqlens [E + 1] i32, x_perm [T * topk, H] bf16,
+//      row_scale [T * topk] bf16 (if weights), tile_table [max_tiles] int4, tile_count [1] i32.
+extern "C" int b200_moe_permute(const void* experts, int experts_dtype /*0 = i32, 1 = i64*/,
+                                const void* weights_bf16, const void* x, long long x_row_stride,
+                                void* scatter_index, void* cu_seqlens, void* x_perm, void* row_scale,
+                                void* tile_table, void* tile_count, long long T, int topk, int E, int H,
+                                int tile_rows, int max_tiles, void* stream) {
+  using namespace b200;
+  if (!experts || !scatter_index || !cu_seqlens || !tile_table || !tile_count || T < 0 || topk <= 0 || E <= 0 ||
+      H <= 0 || tile_rows <= 0 || max_tiles <= 0)
+    return B200_ERR_ARG;
+  if (E > MOE_MAX_EXPERTS || H % 8 != 0 || x_row_stride % 8 != 0) return B200_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long n = T * topk;
+  if (experts_dtype == 0)
+    moe_index_kernel<int><<<1, 1024, 0, st>>>((const int*)experts, n, E, tile_rows, (int*)scatter_index,
+                                              (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles);
+  else if (experts_dtype == 1)
+    moe_index_kernel<long long><<<1, 1024, 0, st>>>((const long long*)experts, n, E, tile_rows,
+                                                    (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table,
+                                                    (int*)tile_count, max_tiles);
+  else
+    return B200_ERR_ARG;
+  int rc = launch_status();
+  if (rc || n == 0 || !x || !x_perm) return rc;
+  moe_scatter_rows_kernel<<<(unsigned)n, 128, 0, st>>>((const __nv_bfloat16*)x, x_row_stride,
+                                                       (const __nv_bfloat16*)weights_bf16,
+                                                       (const int*)scatter_index, (__nv_bfloat16*)x_perm,
+                                                       (__nv_bfloat16*)row_scale, H, topk);
+  return launch_status();
+}
+
+extern "C" int b200_moe_unpermute_reduce(const void* y, const void* scatter_index, const void* addend,
+                                         void* out, long long T, int topk, int H, void* stream) {
+  using namespace b200;
+  if (!y || !scatter_index || !out || T < 0 || topk <= 0 || H <= 0) return B200_ERR_ARG;
+  if (H % 8 != 0) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  moe_unpermute_reduce_kernel<<<(unsigned)T, 128, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, H,
+      topk);
+  return launch_status();
+}
+
+extern "C" int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out,
+                                 long long rows, int I, void* stream) {
+  using namespace b200;
+  if (!gate || !up || !out || rows < 0 || I <= 0) return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  const long long n = rows * I;
+  swiglu_scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (const __nv_bfloat16*)row_scale, (__nv_bfloat16*)out,
+      rows, I);
+  return launch_status();
+}

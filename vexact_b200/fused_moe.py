@@ -1,0 +1,198 @@
+"""Fused MoE forward: routing, permutation, grouped GEMMs, top-k reduction.
+
+Mirror of vexact/batch_invariant_ops/fused_moe.py:459 (`fused_moe_forward`, split
+fc1 signature) extended with the keyword form the model files use
+(`fc1_1_2_weight`, modeling_qwen3_moe.py:89-100, modeling_deepseek_v3.py:148-160),
+plus the two routing functions of the model definitions.
+
+Pipeline (all on the caller's stream, scratch from torch's caching allocator):
+  b200_moe_permute        stable sort positions, cu_seqlens, tile table, row gather
+  b200_moe_grouped_gemm   fc1 with fused SwiGLU * routing weight (fused gate_up weights), or
+                          two plain grouped GEMMs + b200_swiglu_scale (split weights)
+  b200_moe_grouped_gemm   fc2
+  b200_moe_unpermute_reduce  fp32 sum of a token's k rows in k order, one cast
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+TILE_ROWS = 128  # largest token tile of the grouped GEMM (rows of one expert per tile)
+
+
+def max_token_tiles(num_rows: int, num_experts: int, tile_rows: int = TILE_ROWS) -> int:
+    """Upper bound on expert token tiles: every expert may add one partial tile."""
+    return min(num_rows, num_experts) + num_rows // tile_rows
+
+
+def route_softmax_topk(router_logits: torch.Tensor, top_k: int, norm_topk_prob: bool = True,
+                       out_dtype: torch.dtype = torch.bfloat16):
+    """softmax(fp32) -> top-k -> renormalise -> cast (modeling_qwen3_moe.py:128-134).
+
+    Returns (routing_weights [T, k] out_dtype, selected_experts [T, k] int64), experts in
+    descending weight order, ties to the lower index.
+    """
+    if not router_logits.is_cuda:
+        raise ValueError("router_logits must be a CUDA tensor")
+    T, E = router_logits.shape
+    x = router_logits if router_logits.stride(-1) == 1 else router_logits.contiguous()
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError(f"router logits dtype {x.dtype}")
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError(f"routing weight dtype {out_dtype}")
+    w = torch.empty((T, top_k), device=x.device, dtype=out_dtype)
+    idx = torch.empty((T, top_k), device=x.device, dtype=torch.int64)
+    _lib.check(
+        _lib.load().b200_moe_route_softmax_topk(
+            x.data_ptr(), 0 if x.dtype == torch.float32 else 1, x.stride(0),
+            w.data_ptr() if out_dtype == torch.bfloat16 else None,
+            w.data_ptr() if out_dtype == torch.float32 else None,
+            None, idx.data_ptr(), T, E, top_k, 1 if norm_topk_prob else 0, _lib.current_stream()),
+        "b200_moe_route_softmax_topk",
+    )
+    return w, idx
+
+
+def route_sigmoid_group_topk(router_logits: torch.Tensor, e_score_correction_bias: Optional[torch.Tensor],
+                             n_group: int, topk_group: int, top_k: int, norm_topk_prob: bool,
+                             routed_scaling_factor: float):
+    """DeepSeek-V3 routing (modeling_deepseek_v3.py:185-208).  Returns (indices int64, weights fp32)."""
+    if not router_logits.is_cuda:
+        raise ValueError("router_logits must be a CUDA tensor")
+    x = router_logits.float()
+    x = x if x.stride(-1) == 1 else x.contiguous()
+    T, E = x.shape
+    bias = None if e_score_correction_bias is None else e_score_correction_bias.float().contiguous()
+    w = torch.empty((T, top_k), device=x.device, dtype=torch.float32)
+    idx = torch.empty((T, top_k), device=x.device, dtype=torch.int64)
+    _lib.check(
+        _lib.load().b200_moe_route_sigmoid_group_topk(
+            x.data_ptr(), x.stride(0), _lib.ptr(bias), w.data_ptr(), None, idx.data_ptr(), T, E, n_group,
+            topk_group, top_k, 1 if norm_topk_prob else 0, float(routed_scaling_factor), _lib.current_stream()),
+        "b200_moe_route_sigmoid_group_topk",
+    )
+    return idx, w
+
+
+def build_moe_indices(expert_index: torch.Tensor, num_experts: int):
+    """(cu_seqlens_m [E+1], A_idx [T*k], scatter_index [T, k]) as fused_moe.py:268 returns them."""
+    T, k = expert_index.shape
+    plan = _permute(expert_index, None, None, num_experts)
+    scatter = plan["scatter_index"].view(T, k)
+    n = T * k
+    a_idx = torch.empty(n, device=expert_index.device, dtype=torch.int32)
+    a_idx[scatter.flatten().long()] = torch.arange(n, device=expert_index.device, dtype=torch.int32) // k
+    return plan["cu_seqlens"], a_idx, scatter
+
+
+def _permute(expert_index: torch.Tensor, routing_weights: Optional[torch.Tensor],
+             hidden_states: Optional[torch.Tensor], num_experts: int):
+    dev = expert_index.device
+    T, k = expert_index.shape
+    n = T * k
+    if expert_index.dtype not in (torch.int32, torch.int64):
+        expert_index = expert_index.to(torch.int64)
+    expert_index = expert_index.contiguous()
+    max_tiles = max(1, max_token_tiles(n, num_experts))
+    scatter_index = torch.empty(n, device=dev, dtype=torch.int32)
+    cu_seqlens = torch.empty(num_experts + 1, device=dev, dtype=torch.int32)
+    tile_table = torch.empty((max_tiles, 4), device=dev, dtype=torch.int32)
+    tile_count = torch.empty(1, device=dev, dtype=torch.int32)
+    x_perm = row_scale = None
+    H = 8
+    x_stride = 8
+    if hidden_states is not None:
+        H = hidden_states.shape[-1]
+        x_stride = hidden_states.stride(0)
+        x_perm = torch.empty((n, H), device=dev, dtype=torch.bfloat16)
+        if routing_weights is not None:
+            row_scale = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    _lib.check(
+        _lib.load().b200_moe_permute(
+            expert_index.data_ptr(), 0 if expert_index.dtype == torch.int32 else 1, _lib.ptr(routing_weights),
+            _lib.ptr(hidden_states), x_stride, scatter_index.data_ptr(), cu_seqlens.data_ptr(),
+            _lib.ptr(x_perm), _lib.ptr(row_scale), tile_table.data_ptr(), tile_count.data_ptr(), T, k,
+            num_experts, H, TILE_ROWS, max_tiles, _lib.current_stream()),
+        "b200_moe_permute",
+    )
+    return dict(scatter_index=scatter_index, cu_seqlens=cu_seqlens, tile_table=tile_table,
+                tile_count=tile_count, x_perm=x_perm, row_scale=row_scale, max_tiles=max_tiles)
+
+
+def _grouped_gemm(x, w, row_scale, plan, n_out, mode):
+    rows, K = x.shape
+    out = torch.empty((rows, n_out), device=x.device, dtype=torch.bfloat16)
+    _lib.check(
+        _lib.load().b200_moe_grouped_gemm(
+            x.data_ptr(), w.data_ptr(), _lib.ptr(row_scale), out.data_ptr(), plan["tile_table"].data_ptr(),
+            plan["tile_count"].data_ptr(), rows, w.shape[0], n_out, K, out.stride(0), plan["max_tiles"],
+            TILE_ROWS, mode, _lib.current_stream()),
+        "b200_moe_grouped_gemm",
+    )
+    return out
+
+
+def fused_moe_forward(
+    num_experts: int,
+    routing_weights: torch.Tensor,
+    selected_experts: torch.Tensor,
+    hidden_states: torch.Tensor,
+    fc1_1_weight: Optional[torch.Tensor] = None,
+    fc1_2_weight: Optional[torch.Tensor] = None,
+    fc2_weight: Optional[torch.Tensor] = None,
+    fc1_1_2_weight: Optional[torch.Tensor] = None,
+    addend: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """sum_k w_k * fc2_e(silu(fc1_1_e x) * fc1_2_e x) for the selected experts e of each token.
+
+    Weights: fc1_1 / fc1_2 [E, I, H] (split) or fc1_1_2 [E, 2I, H] (gate rows first), fc2 [E, H, I].
+    The routing weight multiplies the activation before fc2 and every intermediate is a bf16
+    tensor, as in fused_moe.py:319-342.  `addend` [T, H] is added to the result as a separate
+    bf16 add (the shared-expert output of DeepSeek-V3).
+    """
+    if not hidden_states.is_cuda:
+        raise ValueError("hidden_states must be a CUDA tensor")
+    if fc2_weight is None:
+        raise ValueError("fc2_weight is required")
+    routing_weights = routing_weights.to(torch.bfloat16).contiguous()
+    orig_shape = hidden_states.shape
+    x = hidden_states.to(torch.bfloat16).reshape(-1, orig_shape[-1])
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    T, H = x.shape
+    k = selected_experts.shape[-1]
+    selected_experts = selected_experts.reshape(T, k)
+    plan = _permute(selected_experts, routing_weights.reshape(T, k), x, num_experts)
+    if fc1_1_2_weight is not None:
+        assert fc1_1_2_weight.dtype == torch.bfloat16 and fc1_1_2_weight.is_contiguous()
+        I = fc1_1_2_weight.shape[1] // 2
+        h = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, plan["row_scale"], plan, I, mode=1)
+    else:
+        if fc1_1_weight is None or fc1_2_weight is None:
+            raise ValueError("pass fc1_1_weight and fc1_2_weight, or fc1_1_2_weight")
+        fc1_1_weight = fc1_1_weight.to(torch.bfloat16).contiguous()
+        fc1_2_weight = fc1_2_weight.to(torch.bfloat16).contiguous()
+        I = fc1_1_weight.shape[1]
+        g = _grouped_gemm(plan["x_perm"], fc1_1_weight, None, plan, I, mode=0)
+        u = _grouped_gemm(plan["x_perm"], fc1_2_weight, None, plan, I, mode=0)
+        h = torch.empty_like(g)
+        _lib.check(
+            _lib.load().b200_swiglu_scale(g.data_ptr(), u.data_ptr(), plan["row_scale"].data_ptr(), h.data_ptr(),
+                                          g.shape[0], I, _lib.current_stream()),
+            "b200_swiglu_scale",
+        )
+    fc2_weight = fc2_weight if (fc2_weight.dtype == torch.bfloat16 and fc2_weight.is_contiguous()) \
+        else fc2_weight.to(torch.bfloat16).contiguous()
+    y = _grouped_gemm(h, fc2_weight, None, plan, H, mode=0)
+    out = torch.empty((T, H), device=x.device, dtype=torch.bfloat16)
+    if addend is not None:
+        addend = addend.to(torch.bfloat16).reshape(T, H).contiguous()
+    _lib.check(
+        _lib.load().b200_moe_unpermute_reduce(y.data_ptr(), plan["scatter_index"].data_ptr(), _lib.ptr(addend),
+                                              out.data_ptr(), T, k, H, _lib.current_stream()),
+        "b200_moe_unpermute_reduce",
+    )
+    return out.reshape(orig_shape)

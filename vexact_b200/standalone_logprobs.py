@@ -1,0 +1,37 @@
+"""Per-token log-probabilities from logits.
+
+Mirror of vexact/batch_invariant_ops/standalone_logprobs.py:28
+(`logprobs_from_logits_flash_attn`): logprob = logits[label] - logsumexp(logits),
+computed in fp32 by one streaming pass per row.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+IGNORE_INDEX = -100
+
+
+def logprobs_from_logits_flash_attn(logits: torch.Tensor, labels: torch.Tensor,
+                                    inplace_backward: bool = False) -> torch.Tensor:
+    del inplace_backward  # forward only
+    if not logits.is_cuda:
+        raise ValueError("logits must be a CUDA tensor")
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError(f"logits dtype {logits.dtype} is not supported")
+    batch_shape = logits.shape[:-1]
+    vocab = logits.shape[-1]
+    x = logits.reshape(-1, vocab)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    lab = labels.reshape(-1).to(torch.int64).contiguous()
+    assert lab.numel() == x.shape[0], "labels must have one entry per logits row"
+    out = torch.empty((x.shape[0],), device=logits.device, dtype=torch.float32)
+    _lib.check(
+        _lib.load().b200_gather_logprob(x.data_ptr(), lab.data_ptr(), out.data_ptr(), x.shape[0], vocab,
+                                        x.stride(0), 0 if x.dtype == torch.float32 else 1, IGNORE_INDEX,
+                                        _lib.current_stream()),
+        "b200_gather_logprob",
+    )
+    return out.reshape(batch_shape)
