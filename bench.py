@@ -1,0 +1,442 @@
+"""Decode throughput of the Qwen3-30B-A3B-shape MoE on the B200 kernels.
+
+    python bench.py --gpus N --steps K --warmup W            # our arm
+    python bench.py --impl reference --gpus N --steps K --warmup W   # CPU reference arm
+
+Workload (BASELINE.json configs[3]): 48 layers, hidden 2048, 32 q / 4 kv heads, head_dim 128,
+128 experts top-8 (renormalised softmax routing), expert FFN 768, vocab 151936; random init
+N(0, 0.02) bf16; decode at batch 512 with a 2048-token paged context (16-token pages, page
+table = seeded random permutation).  A "step" is one decode step of one 512-sequence batch:
+embedding -> 48 decoder layers -> final norm -> lm_head -> greedy token + its logprob.
+With N > 1 GPUs the layers are split evenly over N pipeline stages and N batches are in
+flight (one per stage), hidden states handed over with NCCL send/recv: per-GPU work is
+fixed, so scaling is "weak" and a step advances all N in-flight batches by one token.
+
+Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in HBM;
+`e2e` copies each step's inputs from pinned host memory and reads tokens/logprobs back.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    # development overrides (the default is the BASELINE workload)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=512)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+def workload_name(args, shape):
+    return (f"{shape.name} decode, batch {args.batch}, ctx {args.ctx}, page {args.page}, "
+            f"{shape.num_layers} layers")
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            sm = sorted(float(r[1]) for r in rows if len(r) >= 9)
+            if sm:
+                out["sm_mhz"] = sm[len(sm) // 2]
+                out["sm_max_mhz"] = float(rows[0][2])
+                out["power_w_max"] = max(float(r[3]) for r in rows if len(r) >= 9)
+                names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                seen = set()
+                for r in rows:
+                    for i, n in enumerate(names):
+                        if len(r) >= 9 and r[5 + i].strip().lower().startswith("active"):
+                            seen.add(n)
+                out["reasons"] = sorted(seen)
+                out["samples"] = len(sm)
+        except Exception:
+            pass
+        finally:
+            try:
+                os.unlink(self.path)
+            except OSError:
+                pass
+        return out
+
+
+# --------------------------------------------------------------------------- CPU reference arm
+class CpuSample:
+    """One decoder layer + the head on CPU for `seqs` sequences of the workload.
+
+    The per-layer time is multiplied by the layer count: layers are identical in shape and cost."""
+
+    def __init__(self, args, shape, seqs: int, threads: int):
+        torch.set_num_threads(threads)
+        g = torch.Generator().manual_seed(0)
+        BF = torch.bfloat16
+        H, D = shape.hidden, shape.head_dim
+        m = shape.moe
+        self.shape, self.seqs = shape, seqs
+
+        def rn(*s):
+            t = torch.empty(*s, dtype=BF)
+            t.normal_(0.0, 0.02, generator=g)
+            return t
+
+        self.lw = dict(input_norm=torch.ones(H, dtype=BF), post_norm=torch.ones(H, dtype=BF),
+                       qkv=rn(shape.qkv_out, H), q_norm=torch.ones(D, dtype=BF), k_norm=torch.ones(D, dtype=BF),
+                       o=rn(H, shape.num_q_heads * D), router=rn(m.num_experts, H),
+                       experts_gate_up=rn(m.num_experts, 2 * m.intermediate, H),
+                       experts_down=rn(m.num_experts, H, m.intermediate))
+        self.final_norm, self.lm_head = torch.ones(H, dtype=BF), rn(shape.vocab, H)
+        pages = (args.ctx + args.page - 1) // args.page
+        nblocks = seqs * pages
+        self.kc = torch.empty(nblocks, args.page, shape.num_kv_heads, D, dtype=BF).normal_(generator=g)
+        self.vc = torch.empty(nblocks, args.page, shape.num_kv_heads, D, dtype=BF).normal_(generator=g)
+        self.ptab = torch.randperm(nblocks, generator=g).view(seqs, pages).to(torch.int32)
+        self.h = torch.empty(seqs, H, dtype=BF).normal_(generator=g)
+        self.pos = torch.full((seqs,), args.ctx - 1, dtype=torch.int64)
+        self.slots = (self.ptab[:, (args.ctx - 1) // args.page].long() * args.page
+                      + (args.ctx - 1) % args.page).to(torch.int32)
+        self.cu = torch.arange(seqs + 1, dtype=torch.int32)
+        self.used = torch.full((seqs,), args.ctx, dtype=torch.int32)
+
+    def run(self) -> float:
+        """Seconds one decode step of `seqs` sequences would take (layer time x layers + head)."""
+        from oracle import cpu_model
+
+        t0 = time.perf_counter()
+        h2 = cpu_model.layer_forward(self.shape, self.lw, self.h, self.pos, self.slots, self.kc, self.vc, self.cu,
+                                     self.used, self.ptab)
+        t1 = time.perf_counter()
+        cpu_model.head_forward(self.shape, self.final_norm, self.lm_head, h2)
+        t2 = time.perf_counter()
+        return (t1 - t0) * self.shape.num_layers + (t2 - t1)
+
+
+def run_reference(args, shape, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    seqs = min(args.batch, 128)
+    sample = (f"1 of {shape.num_layers} decoder layers (time x {shape.num_layers}) + final norm/lm_head/logprob, "
+              f"{seqs} of {args.batch} sequences at ctx {args.ctx}, torch CPU ops, {threads} threads")
+    sam = CpuSample(args, shape, seqs, threads)
+    for _ in range(args.warmup):
+        sam.run()
+    t_tot = 0.0
+    for _ in range(args.steps):
+        t_tot += sam.run()
+    ms = t_tot / max(args.steps, 1) * 1e3
+    value = seqs / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(args, shape), "pipeline_stages": args.gpus},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def build_inputs(args, shape, seed, device):
+    """Pinned host inputs of one decode step and their static device copies."""
+    S, ctx, page = args.batch, args.ctx, args.page
+    pages = (ctx + page - 1) // page
+    g = torch.Generator().manual_seed(seed)
+    ptab = torch.randperm(S * pages, generator=g).view(S, pages).to(torch.int32)
+    host = dict(
+        input_ids=torch.randint(0, shape.vocab, (S,), generator=g),
+        positions=torch.full((S,), ctx - 1, dtype=torch.int64),
+        slot_mapping=(ptab[:, (ctx - 1) // page].long() * page + (ctx - 1) % page).to(torch.int32),
+        query_start_loc=torch.arange(S + 1, dtype=torch.int32),
+        context_lens=torch.full((S,), ctx, dtype=torch.int32),
+        block_tables=ptab,
+    )
+    host = {k: v.pin_memory() for k, v in host.items()}
+    dev = {k: v.to(device) for k, v in host.items()}
+    return host, dev, S * pages
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    from vexact_b200.inferencer import PRESETS, ModelShape
+
+    shape = PRESETS["qwen3-30b-a3b-shape"]
+    if args.layers:
+        shape = ModelShape(**{**shape.__dict__, "num_layers": args.layers})
+    if args.impl == "reference":
+        run_reference(args, shape, rank)
+        return
+
+    import torch.distributed as dist
+
+    import vexact_b200 as vb
+    from vexact_b200 import _lib
+    from vexact_b200.inferencer import StageRunner, StageWeights, StepInputs, allocate_kv_cache
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path for the product arm")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _lib.load()
+    pp = world
+    if pp > 1:
+        dist.init_process_group("nccl", device_id=device)
+    S, H = args.batch, shape.hidden
+
+    weights = StageWeights.random_init(shape, rank, pp, device=device, seed=0)
+    n_inflight = pp
+    runners, graphs, outs, dev_inputs, host_inputs, step_inputs = [], [], [], [], [], []
+    hidden_in = [torch.zeros((S, H), device=device, dtype=torch.bfloat16) for _ in range(n_inflight)]
+    for b in range(n_inflight):
+        host, dev, nblocks = build_inputs(args, shape, seed=100 + b, device=device)
+        kc, vc = allocate_kv_cache(shape, weights.start_layer, weights.end_layer, nblocks, args.page, device=device,
+                                   fill_std=1.0, seed=b)
+        r = StageRunner(weights, kc, vc, rank, pp)
+        inp = StepInputs(input_ids=dev["input_ids"], hidden_in=hidden_in[b], positions=dev["positions"],
+                         slot_mapping=dev["slot_mapping"], query_start_loc=dev["query_start_loc"],
+                         context_lens=dev["context_lens"], block_tables=dev["block_tables"], max_seqlen_q=1)
+        runners.append(r)
+        host_inputs.append(host)
+        dev_inputs.append(dev)
+        step_inputs.append(inp)
+    torch.cuda.synchronize()
+
+    # count our kernel launches in one eager step, then capture
+    _lib.reset_launch_count()
+    runners[0].step(step_inputs[0])
+    torch.cuda.synchronize()
+    launches_per_step = _lib.launch_count()
+    for b in range(n_inflight):
+        if args.no_graph:
+            graphs.append(None)
+            outs.append(None)
+        else:
+            gr, out = runners[b].capture(step_inputs[b])
+            graphs.append(gr)
+            outs.append(out)
+    status = _lib.read_status()
+    if status[0] != 0:
+        raise SystemExit(f"device status word reports {status}")
+
+    def run_stage(b):
+        if graphs[b] is not None:
+            graphs[b].replay()
+            return outs[b]
+        return runners[b].step(step_inputs[b])
+
+    recv_tok = torch.zeros(S, dtype=torch.int64, device=device)
+
+    def global_step():
+        """Advance every in-flight batch by one token through this rank's stage."""
+        for b in range(n_inflight):
+            if pp > 1:
+                if rank == 0:
+                    pass  # token feedback is received at the end of the previous step
+                else:
+                    dist.recv(hidden_in[b], src=rank - 1)
+            out = run_stage(b)
+            if pp > 1:
+                if rank < pp - 1:
+                    dist.send(out, dst=rank + 1)
+                else:
+                    dist.send(out[0], dst=0)  # sampled token ids close the ring
+        if pp > 1 and rank == 0:
+            for b in range(n_inflight):
+                dist.recv(recv_tok, src=pp - 1)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if pp > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        global_step()
+    sync_all()
+
+    # ---- device-timed run (inputs resident in HBM; weights + KV >> L2, so every step is cold)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        global_step()
+    ev1.record()
+    sync_all()
+    dev_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop()
+
+    # ---- end-to-end run: pinned host inputs in, tokens + logprobs out, every step
+    h2d = sum(v.numel() * v.element_size() for v in host_inputs[0].values()) if rank == 0 else 0
+    tok_host = torch.empty(S, dtype=torch.int64).pin_memory()
+    lp_host = torch.empty(S, dtype=torch.float32).pin_memory()
+    d2h = (tok_host.numel() * 8 + lp_host.numel() * 4) if rank == pp - 1 else 0
+
+    def e2e_step():
+        for b in range(n_inflight):
+            if rank == 0:
+                for k, v in host_inputs[b].items():
+                    dev_inputs[b][k].copy_(v, non_blocking=True)
+            elif pp > 1:
+                dist.recv(hidden_in[b], src=rank - 1)
+            out = run_stage(b)
+            if pp > 1 and rank < pp - 1:
+                dist.send(out, dst=rank + 1)
+            if rank == pp - 1:
+                tok_host.copy_(out[0], non_blocking=True)
+                lp_host.copy_(out[1], non_blocking=True)
+                if pp > 1:
+                    dist.send(out[0], dst=0)
+        if pp > 1 and rank == 0:
+            for b in range(n_inflight):
+                dist.recv(recv_tok, src=pp - 1)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    sync_all()
+    e2e_s = time.perf_counter() - t0
+
+    # ---- dominant kernel alone (paged decode attention over every local layer's cache)
+    att = {}
+    r0 = runners[0]
+    q = torch.randn(S, shape.num_q_heads, shape.head_dim, device=device).to(torch.bfloat16)
+    layers = list(range(weights.start_layer, weights.end_layer))
+    reps = max(2, min(args.steps, 5))
+
+    def attn_all():
+        for li in layers:
+            vb.paged_attention(q, r0.key_cache[li], r0.value_cache[li], step_inputs[0].query_start_loc,
+                               step_inputs[0].context_lens, step_inputs[0].block_tables, shape.head_dim ** -0.5, 1)
+
+    attn_all()
+    torch.cuda.synchronize()
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(reps):
+        attn_all()
+    a1.record()
+    torch.cuda.synchronize()
+    att_ms = a0.elapsed_time(a1) / (reps * len(layers))
+    kv_bytes = S * args.ctx * shape.num_kv_heads * 2 * shape.head_dim * 2
+    att_bytes = kv_bytes + 2 * S * shape.num_q_heads * shape.head_dim * 2 + 4 * S * (step_inputs[0].block_tables.shape[1] + 2)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    achieved = att_bytes / (att_ms * 1e-3) / 1e9
+    att = {"bound": "hbm", "kernel": "paged_attn_kernel<128,128>", "achieved": achieved, "peak": peak,
+           "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
+           "frac": achieved / peak, "traffic": None, "algorithmic_bytes_per_launch": att_bytes,
+           "ms_per_launch": att_ms}
+
+    # ---- gather timing across ranks (max), emit
+    t = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    if pp > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = t.tolist()
+    tokens_per_step = S * n_inflight
+    value = tokens_per_step * args.steps / (dev_ms * 1e-3)
+    e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)
+    step_bytes = weights.num_bytes() + len(layers) * kv_bytes
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload_name(args, shape), "pipeline_stages": pp, "batches_in_flight": n_inflight,
+                   "l2": "inputs (weights + KV, >100 GB per GPU) far exceed L2; no flush needed",
+                   "cuda_graph": not args.no_graph},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * n_inflight,
+                "d2h_bytes_per_step": d2h * n_inflight, "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": launches_per_step * n_inflight * args.steps,
+        "roofline": att,
+        "step_roofline": {"bytes_per_stage_step": step_bytes, "hbm_bound_ms": step_bytes / (peak * 1e9) * 1e3,
+                          "frac": (step_bytes / (peak * 1e9) * 1e3) / (dev_ms / args.steps / n_inflight)},
+    }
+    if rank == 0 and pp == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        seqs = min(S, 128)
+        sam = CpuSample(args, shape, seqs, threads)
+        sam.run()
+        secs = min(sam.run() for _ in range(2))
+        v = seqs / secs
+        line["cpu_baseline"] = {
+            "value": v, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": (f"1 of {shape.num_layers} decoder layers (time x {shape.num_layers}) + head, {seqs} of "
+                       f"{S} sequences at ctx {args.ctx}, torch CPU ops; extrapolated step {secs:.2f} s"),
+        }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if pp > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

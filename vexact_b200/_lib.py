@@ -76,9 +76,26 @@ def load() -> C.CDLL:
     return _lib
 
 
+# Kernels launched by one successful call of each entry point (for launch accounting).
+_KERNELS_PER_CALL = {"b200_moe_permute": 2, "b200_status_read": 0, "b200_abi_version": 0}
+_launches = 0
+
+
 def check(rc: int, what: str) -> None:
+    global _launches
     if rc != 0:
         raise B200Error(f"{what} failed: {_ERRORS.get(rc, rc)}")
+    _launches += _KERNELS_PER_CALL.get(what, 1)
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured) since the last reset."""
+    return _launches
 
 
 def ptr(t) -> int | None:
