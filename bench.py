@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--page", type=int, default=16)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="device-timed run only (for profiler captures)")
     return ap.parse_args()
 
 
@@ -80,7 +81,24 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def wait_first_sample(self, limit_s: float = 5.0):
+        t0 = time.time()
+        while self.proc is not None and time.time() - t0 < limit_s:
+            try:
+                if os.path.getsize(self.path) > 0:
+                    return
+            except OSError:
+                return
+            time.sleep(0.05)
+
+    def mark(self) -> int:
+        """Number of samples written so far (to cut the timed region out of the log)."""
+        try:
+            return sum(1 for _ in open(self.path))
+        except Exception:
+            return 0
+
+    def stop(self, first: int = 0):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
             return out
@@ -91,6 +109,7 @@ class ClockSampler:
             self.proc.kill()
         try:
             rows = [r.split(",") for r in open(self.path).read().strip().splitlines() if r.strip()]
+            rows = rows[first:] if len(rows) > first else rows[-1:]
             sm = sorted(float(r[1]) for r in rows if len(r) >= 9)
             if sm:
                 out["sm_mhz"] = sm[len(sm) // 2]
@@ -283,73 +302,85 @@ def main():
             return outs[b]
         return runners[b].step(step_inputs[b])
 
-    recv_tok = torch.zeros(S, dtype=torch.int64, device=device)
+    # Hidden states travel r -> r+1 on the default group; the sampled token ids close the ring
+    # (last -> first) on a second group, i.e. another communicator and stream, so a stage can send
+    # the next batch forward while the previous batch's tokens are still on their way back.
+    tok_host = torch.empty(S, dtype=torch.int64).pin_memory()
+    lp_host = torch.empty(S, dtype=torch.float32).pin_memory()
+    fb_group = dist.new_group(ranks=list(range(pp))) if pp > 1 else None
+    recv_tok = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(n_inflight)]
+    pending = [None] * n_inflight
 
-    def global_step():
+    def global_step(e2e=False):
         """Advance every in-flight batch by one token through this rank's stage."""
         for b in range(n_inflight):
-            if pp > 1:
-                if rank == 0:
-                    pass  # token feedback is received at the end of the previous step
-                else:
-                    dist.recv(hidden_in[b], src=rank - 1)
+            if rank == 0:
+                if pending[b] is not None:      # tokens of this batch's previous step
+                    pending[b].wait()
+                    pending[b] = None
+                if e2e:
+                    for k, v in host_inputs[b].items():
+                        dev_inputs[b][k].copy_(v, non_blocking=True)
+            else:
+                dist.recv(hidden_in[b], src=rank - 1)
             out = run_stage(b)
-            if pp > 1:
-                if rank < pp - 1:
-                    dist.send(out, dst=rank + 1)
-                else:
-                    dist.send(out[0], dst=0)  # sampled token ids close the ring
-        if pp > 1 and rank == 0:
-            for b in range(n_inflight):
-                dist.recv(recv_tok, src=pp - 1)
+            if rank < pp - 1:
+                dist.send(out, dst=rank + 1)
+            else:
+                if e2e:
+                    tok_host.copy_(out[0], non_blocking=True)
+                    lp_host.copy_(out[1], non_blocking=True)
+                if pp > 1:
+                    dist.isend(out[0], dst=0, group=fb_group)
+            if pp > 1 and rank == 0:
+                pending[b] = dist.irecv(recv_tok[b], src=pp - 1, group=fb_group)
+        if e2e:
+            torch.cuda.current_stream().synchronize()
+
+    def drain():
+        for b in range(n_inflight):
+            if pending[b] is not None:
+                pending[b].wait()
+                pending[b] = None
 
     def sync_all():
+        drain()
         torch.cuda.synchronize()
         if pp > 1:
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    sampler = ClockSampler(local_rank)
+    if not args.quick:
+        sampler.start()
+        sampler.wait_first_sample()
+    for _ in range(max(args.warmup, 3) if not args.quick else args.warmup):
         global_step()
     sync_all()
 
     # ---- device-timed run (inputs resident in HBM; weights + KV >> L2, so every step is cold)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_sample = sampler.mark()
     ev0.record()
     for _ in range(args.steps):
         global_step()
     ev1.record()
     sync_all()
     dev_ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop()
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"quick": True, "ms_per_step": dev_ms / args.steps,
+                              "value": S * n_inflight * args.steps / (dev_ms * 1e-3)}), flush=True)
+        if pp > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- end-to-end run: pinned host inputs in, tokens + logprobs out, every step
     h2d = sum(v.numel() * v.element_size() for v in host_inputs[0].values()) if rank == 0 else 0
-    tok_host = torch.empty(S, dtype=torch.int64).pin_memory()
-    lp_host = torch.empty(S, dtype=torch.float32).pin_memory()
     d2h = (tok_host.numel() * 8 + lp_host.numel() * 4) if rank == pp - 1 else 0
 
     def e2e_step():
-        for b in range(n_inflight):
-            if rank == 0:
-                for k, v in host_inputs[b].items():
-                    dev_inputs[b][k].copy_(v, non_blocking=True)
-            elif pp > 1:
-                dist.recv(hidden_in[b], src=rank - 1)
-            out = run_stage(b)
-            if pp > 1 and rank < pp - 1:
-                dist.send(out, dst=rank + 1)
-            if rank == pp - 1:
-                tok_host.copy_(out[0], non_blocking=True)
-                lp_host.copy_(out[1], non_blocking=True)
-                if pp > 1:
-                    dist.send(out[0], dst=0)
-        if pp > 1 and rank == 0:
-            for b in range(n_inflight):
-                dist.recv(recv_tok, src=pp - 1)
-        torch.cuda.current_stream().synchronize()
+        global_step(e2e=True)
 
     for _ in range(2):
         e2e_step()
@@ -359,6 +390,7 @@ def main():
         e2e_step()
     sync_all()
     e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop(first_sample)
 
     # ---- dominant kernel alone (paged decode attention over every local layer's cache)
     att = {}

@@ -61,23 +61,40 @@ def test_stage_forward_vs_cpu_model_and_invariance(moe):
     runner = StageRunner(w, kc, vc)
     tokens, logprobs, logits = runner.step(inp)
 
-    # CPU model with the same weights
-    kc_c = {i: torch.zeros_like(kc[i]).cpu() for i in kc}
-    vc_c = {i: torch.zeros_like(vc[i]).cpu() for i in vc}
-    h = w.embed.cpu()[host["input_ids"]]
-    for li, lw in enumerate(w.layers):
-        h = cpu_model.layer_forward(shape, _cpu_layer(lw), h, host["positions"], host["slot_mapping"], kc_c[li],
-                                    vc_c[li], host["query_start_loc"], host["context_lens"], host["block_tables"])
+    # CPU model with the same weights, teacher-forced layer by layer: each CPU layer gets the GPU
+    # runner's own input to that layer (single-layer stages chained as pipeline ranks), so errors do
+    # not compound and a routing flip (bf16 router logits tie often) stays confined to its layer.
     last = (host["query_start_loc"][1:] - 1).long()
-    tok_c, lp_c, logits_c = cpu_model.head_forward(shape, w.final_norm.cpu(), w.lm_head.cpu(), h[last])
-    # stated tolerance: bf16 logits of a 4-layer stack, max-abs delta reported and bounded
+    h_gpu = w.embed.index_select(0, inp.input_ids)
+    worst_tok_frac = 0.0
+    for li, lw in enumerate(w.layers):
+        ws = StageWeights(shape, li, li + 1, layers=[lw], inv_freq=w.inv_freq)
+        kcl, vcl = allocate_kv_cache(shape, li, li + 1, nblocks, page, device=dev)
+        rr = StageRunner(ws, kcl, vcl, pp_rank=1, pp_size=3)       # a middle stage: hidden in, hidden out
+        h_next = rr.step(dataclasses.replace(inp, hidden_in=h_gpu))
+        kc_c = torch.zeros_like(kcl[li]).cpu()
+        vc_c = torch.zeros_like(vcl[li]).cpu()
+        h_cpu = cpu_model.layer_forward(shape, _cpu_layer(lw), h_gpu.cpu(), host["positions"], host["slot_mapping"],
+                                        kc_c, vc_c, host["query_start_loc"], host["context_lens"],
+                                        host["block_tables"])
+        # K/V cache rows are roped projections of the same input: one bf16 ulp
+        torch.testing.assert_close(kcl[li].cpu().float(), kc_c.float(), rtol=2 ** -6, atol=2e-2)
+        torch.testing.assert_close(vcl[li].cpu().float(), vc_c.float(), rtol=2 ** -6, atol=2e-2)
+        assert torch.equal(kcl[li], kc[li]) and torch.equal(vcl[li], vc[li])   # same bits as the 4-layer run
+        err = (h_next.cpu().float() - h_cpu.float()).abs().amax(dim=1)
+        scale_ = h_cpu.float().abs().amax().item()
+        bad = (err > 2 ** -5 * scale_).float().mean().item()
+        worst_tok_frac = max(worst_tok_frac, bad)
+        h_gpu = h_next
+    # dense: every token within tolerance; MoE: tokens whose expert choice flipped may differ
+    print(f"moe={moe}: worst per-layer fraction of tokens beyond 2^-5 of max|h| = {worst_tok_frac:.3f}")
+    assert worst_tok_frac <= (0.15 if moe else 0.0)
+    tok_c, lp_c, logits_c = cpu_model.head_forward(shape, w.final_norm.cpu(), w.lm_head.cpu(), h_gpu.cpu()[last])
+    assert torch.equal(runner.select_tokens(h_gpu, inp)[2], logits)            # chained stages == one stage
     dlogit = (logits.cpu().float() - logits_c.float()).abs().max().item()
     dlp = (logprobs.cpu() - ops.gather_logprob(logits_c, tokens.cpu())).abs().max().item()
-    print(f"moe={moe}: max |dlogit| = {dlogit:.4f}, max |dlogprob| = {dlp:.4f}")
-    assert dlogit < 0.25 and dlp < 0.1
-    # the KV cache contents are pure copies of roped K / V: near-exact
-    for li in kc:
-        torch.testing.assert_close(kc[li].cpu().float(), kc_c[li].float(), rtol=2 ** -5, atol=0.1)
+    print(f"moe={moe}: head on the same hidden: max |dlogit| = {dlogit:.4f}, max |dlogprob| = {dlp:.4f}")
+    assert dlogit < 0.07 and dlp < 0.05
 
     # decode step for every sequence, batched vs one by one: bitwise
     ctx2 = [c + 1 for c in ctx_lens]
@@ -174,5 +191,6 @@ def test_hf_dropin_attention_and_aten_overrides():
     print(f"HF drop-in vs stage runner: max |dlogit| = {d:.5f}")
     assert d < 0.06
     for li in kc:
-        assert torch.equal(vc[li], vc2[li])
+        # the HF module normalises through the aten::mean.dim override (another summation tree)
+        torch.testing.assert_close(vc[li].float(), vc2[li].float(), rtol=2 ** -6, atol=2e-2)
         torch.testing.assert_close(kc[li].float(), kc2[li].float(), rtol=2 ** -6, atol=2e-2)
