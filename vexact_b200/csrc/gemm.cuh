@@ -28,6 +28,7 @@
 // Algorithmic bytes per launch: 2*(N*K + T*K + T*N); the weight term dominates
 // for decode shapes, so the roofline is HBM bandwidth.
 #pragma once
+#include <stdlib.h>
 #include <cuda.h>  // CUtensorMap and enums only: the encoder is looked up at run time, libcuda is not linked
 
 #include "ptx.cuh"
@@ -41,7 +42,7 @@ constexpr int GEMM_WBYTES = GEMM_WTILE * GEMM_BK * 2;
 constexpr int GEMM_THREADS = 192;       // producer warp, MMA warp, 4 epilogue warps
 constexpr int GEMM_MAX_STAGES = 12;
 constexpr int GEMM_SMEM_BUDGET = 227 * 1024;
-constexpr int GEMM_EXCH_PITCH = 256 + 8;  // bf16 elements per feature row in the SwiGLU exchange buffer
+constexpr int GEMM_EXCH_PAD = 8;  // the SwiGLU exchange buffer holds xrows_max + 8 bf16 per feature row
 
 struct GemmParams {
   int n_w;               // output features per group (plain: N; SwiGLU: intermediate size I)
@@ -67,6 +68,7 @@ struct GemmParams {
   const __nv_bfloat16* bias;       // [n_w] or null (plain mode)
   const __nv_bfloat16* row_scale;  // [rows] or null (SwiGLU mode: routing weight of each permuted row)
   uint64_t w_policy;
+  int dbg;  // timing experiments only (B200_GEMM_DBG); results are wrong when non-zero
 };
 
 struct GemmTile {
@@ -106,6 +108,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __nv_bfloat16* exch =
       reinterpret_cast<__nv_bfloat16*>(smem_raw + (stage_base - smem_base) + (size_t)S * stage_bytes);
 
+  const int exch_pitch = p.xrows_max + GEMM_EXCH_PAD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   auto full_bar = [&](int s) { return smem_base + 8u * s; };
   auto empty_bar = [&](int s) { return smem_base + 8u * (S + s); };
@@ -157,7 +160,11 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           }
           const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
           const uint32_t sx = sw + GEMM_WBYTES;
-          ptx::mbar_expect_tx(full_bar(s), tx);
+          if ((p.dbg & 2) && it >= (uint32_t)S) {
+            ptx::mbar_arrive(full_bar(s));
+            continue;
+          }
+          ptx::mbar_expect_tx(full_bar(s), ((p.dbg & 1) && it >= (uint32_t)S) ? GEMM_WBYTES : tx);
           if (SWIGLU) {
             ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
             ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kb * GEMM_BK, wrow + p.up_offset,
@@ -165,6 +172,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           } else {
             ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
           }
+          if ((p.dbg & 1) && it >= (uint32_t)S) continue;
           for (int b = 0; b < nbox; ++b)
             ptx::tma_load_2d(sx + (uint32_t)b * p.xbox * (GEMM_BK * 2), &tm_x, full_bar(s), kb * GEMM_BK,
                              t.row0 + b * p.xbox, ptx::kEvictLast);
@@ -195,7 +203,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
           const uint32_t sx = sw + GEMM_WBYTES;
 #pragma unroll
-          for (int kk = 0; kk < GEMM_BK / 16; ++kk) {
+          for (int kk = 0; kk < ((p.dbg & 4) ? 1 : GEMM_BK / 16); ++kk) {
             const uint64_t da = ptx::umma_desc_k_sw128(sw + kk * 32);
             const uint64_t db = ptx::umma_desc_k_sw128(sx + kk * 32);
             ptx::umma_bf16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
@@ -250,7 +258,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             ptx::tmem_ld16(taddr + c0, r);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) exch[fi * GEMM_EXCH_PITCH + c0 + j] = f2bf(__uint_as_float(r[j]));
+            for (int j = 0; j < 16; ++j) exch[fi * exch_pitch + c0 + j] = f2bf(__uint_as_float(r[j]));
           }
         }
         ptx::named_barrier_sync(1, 128);
@@ -269,7 +277,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                   // Rounding points of fused_moe.py:319-336: each GEMM output, silu(), the
                   // gate*up product and the routing-weight product are bf16 tensors.
                   const float g = round_bf(__uint_as_float(r[j]));
-                  const float u = bf2f(exch[fi * GEMM_EXCH_PITCH + c]);
+                  const float u = bf2f(exch[fi * exch_pitch + c]);
                   const float sg = round_bf(g / (1.0f + expf(-g)));
                   float h = round_bf(sg * u);
                   if (p.row_scale) h = round_bf(h * bf2f(p.row_scale[t.row0 + c]));
@@ -330,6 +338,15 @@ inline int sm_count() {
   return n;
 }
 
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+// Development knobs (unset in normal use): B200_GEMM_XBOX = rows per activation box of the grouped
+// GEMM (16, 32 or 64), B200_GEMM_STAGES = cap on pipeline stages.
+inline int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
 template <bool SWIGLU>
 inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams& p, long long max_tiles,
                        cudaStream_t st) {
@@ -341,11 +358,19 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
     attr_set = true;
   }
   const int stage_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
-  const int exch_bytes = SWIGLU ? 64 * GEMM_EXCH_PITCH * 2 : 0;
+  const int exch_bytes = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
   int stages = (GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
+  {
+    static const int cap = env_int("B200_GEMM_STAGES", GEMM_MAX_STAGES);
+    if (stages > cap) stages = cap;
+  }
   if (stages < 2) return B200_ERR_SHAPE;
   p.stages = stages;
+  {
+    static const int dbg = env_int("B200_GEMM_DBG", 0);
+    p.dbg = dbg;
+  }
   int cols = 32;
   while (cols < 2 * p.xrows_max) cols <<= 1;
   if (cols > 512) return B200_ERR_SHAPE;
@@ -356,8 +381,6 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   gemm_ws_kernel<SWIGLU><<<(unsigned)grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
   return launch_status();
 }
-
-inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 }  // namespace b200
 
@@ -413,8 +436,18 @@ extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, vo
   p.w_rows_per_group = N;
   p.up_offset = 0;
   p.t_rows = (int)T;
-  p.dense_t_tiles = (int)((T + 255) / 256);
-  p.rows_per_tile = round_up((int)((T + p.dense_t_tiles - 1) / p.dense_t_tiles), 16);
+  // Token tiling.  A token's result does not depend on the tile it lands in (tokens are independent
+  // UMMA columns), so the tile width is chosen for occupancy only: enough tiles to cover every SM
+  // about twice when the weight has few row tiles, at most 256 and at least 16 tokens per tile.
+  {
+    const int min_tiles = (int)((T + 255) / 256);
+    const int max_tiles = (int)((T + 15) / 16);
+    int want = (2 * sm_count() + p.w_tiles - 1) / p.w_tiles;
+    if (want < min_tiles) want = min_tiles;
+    if (want > max_tiles) want = max_tiles;
+    p.rows_per_tile = round_up((int)((T + want - 1) / want), 16);
+    p.dense_t_tiles = (int)((T + p.rows_per_tile - 1) / p.rows_per_tile);
+  }
   p.tile_table = nullptr;
   p.tile_count = nullptr;
   p.xbox = p.rows_per_tile;
@@ -458,7 +491,9 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* r
   p.dense_t_tiles = 0;
   p.tile_table = (const int4*)tile_table;
   p.tile_count = (const int*)tile_count;
-  p.xbox = 16;
+  // One activation box per stage when the tile height allows it (fewer TMA issues per stage).
+  static const int xbox_env = env_int("B200_GEMM_XBOX", 64);
+  p.xbox = (xbox_env == 16 || xbox_env == 32 || xbox_env == 64) && tile_rows_max % xbox_env == 0 ? xbox_env : 16;
   p.xrows_max = tile_rows_max;
   p.out = out;
   p.ldo = out_row_stride;
@@ -470,7 +505,7 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* r
   int rc = make_tmap_2d(&tw, w, (uint64_t)num_groups * p.w_rows_per_group, (uint64_t)K, (uint64_t)K,
                         mode == 1 ? 64 : GEMM_WTILE);
   if (rc) return rc;
-  rc = make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, 16);
+  rc = make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, (uint32_t)p.xbox);
   if (rc) return rc;
   const long long tiles = (long long)max_tiles * p.w_tiles;
   if (mode == 1) return gemm_launch<true>(tw, tx, p, tiles, (cudaStream_t)stream);

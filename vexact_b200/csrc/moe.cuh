@@ -210,65 +210,111 @@ moe_route_sigmoid_group_topk_kernel(const float* __restrict__ logits, long long 
 //   scatter_index[f] = cu_seqlens[e_f] + #{f' < f : e_f' == e_f}
 // plus cu_seqlens[E + 1] and the token-tile table of the grouped GEMM (tiles of at most
 // `tile_rows` consecutive rows of one expert).
+//
+// Warp w owns the contiguous segment [w * seg, (w + 1) * seg) of the flat array and walks it 32
+// entries at a time: __match_any_sync groups equal experts, the lowest lane of a group bumps the
+// warp's private per-expert counter, so every entry learns its rank among the warp's earlier
+// entries of the same expert.  A per-expert scan over the 32 warps and a scan over the experts
+// turn those ranks into global positions.  All of it is integer arithmetic: bit-exact.
 template <typename TIdx>
 __global__ void __launch_bounds__(1024)
 moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_rows,
                  int* __restrict__ scatter_index, int* __restrict__ cu_seqlens, int4* __restrict__ tile_table,
                  int* __restrict__ tile_count, int max_tiles) {
-  __shared__ int hist[MOE_MAX_EXPERTS];
-  __shared__ int base[MOE_MAX_EXPERTS];
-  __shared__ int cnt[32][MOE_MAX_EXPERTS];
+  __shared__ int cnt[32][MOE_MAX_EXPERTS];  // per-warp counts, then per-warp exclusive offsets
+  __shared__ int base[MOE_MAX_EXPERTS];     // expert totals, then exclusive prefix (cu_seqlens)
+  __shared__ int tbase[MOE_MAX_EXPERTS];    // first tile index of each expert
+  __shared__ int wsum[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int e = tid; e < E; e += 1024) hist[e] = 0;
+  for (int i = tid; i < 32 * MOE_MAX_EXPERTS; i += 1024) (&cnt[0][0])[i] = 0;
   __syncthreads();
-  for (long long i = tid; i < n; i += 1024) {
-    const long long e = (long long)experts[i];
-    if (e >= 0 && e < E)
-      atomicAdd(&hist[(int)e], 1);
-    else
-      report_status(B200_STATUS_BAD_INDEX, (int)e);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int run = 0, nt = 0;
-    for (int e = 0; e < E; ++e) {
-      base[e] = run;
-      cu_seqlens[e] = run;
-      for (int r = 0; r < hist[e]; r += tile_rows) {
-        if (nt < max_tiles) tile_table[nt] = make_int4(e, run + r, min(tile_rows, hist[e] - r), 0);
-        ++nt;
-      }
-      run += hist[e];
-    }
-    cu_seqlens[E] = run;
-    *tile_count = min(nt, max_tiles);
-  }
-  __syncthreads();
-  for (long long c0 = 0; c0 < n; c0 += 1024) {
-    for (int i = tid; i < 32 * E; i += 1024) cnt[i / E][i % E] = 0;
-    __syncthreads();
-    const long long i = c0 + tid;
+  const long long seg = ((n + 31) / 32 + 31) / 32 * 32;  // entries per warp, a multiple of 32
+  const long long w0 = warp * seg;
+  // pass 1: rank of every entry among the warp's earlier entries of the same expert
+  for (long long o = 0; o < seg; o += 32) {
+    const long long i = w0 + o + lane;
     int e = -1;
     if (i < n) {
       const long long ev = (long long)experts[i];
-      if (ev >= 0 && ev < E) e = (int)ev;
+      if (ev >= 0 && ev < E)
+        e = (int)ev;
+      else
+        report_status(B200_STATUS_BAD_INDEX, (int)ev);
     }
     const unsigned mask = __match_any_sync(0xffffffffu, e);
     const int rank = __popc(mask & ((1u << lane) - 1u));
-    if (rank == 0 && e >= 0) cnt[warp][e] = __popc(mask);
-    __syncthreads();
-    if (tid < E) {
-      int run = base[tid];
-      for (int w = 0; w < 32; ++w) {
-        const int c = cnt[w][tid];
-        cnt[w][tid] = run;
-        run += c;
-      }
-      base[tid] = run;
+    const int leader = __ffs(mask) - 1;
+    int old = 0;
+    if (rank == 0 && e >= 0) {
+      old = cnt[warp][e];
+      cnt[warp][e] = old + __popc(mask);
     }
-    __syncthreads();
-    if (i < n) scatter_index[i] = e >= 0 ? cnt[warp][e] + rank : -1;
-    __syncthreads();
+    old = __shfl_sync(0xffffffffu, old, leader);
+    if (i < n) scatter_index[i] = e >= 0 ? old + rank : -1;
+    __syncwarp();
+  }
+  __syncthreads();
+  // per expert: exclusive scan over the warps, total into base[]
+  if (tid < E) {
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) {
+      const int c = cnt[w][tid];
+      cnt[w][tid] = run;
+      run += c;
+    }
+    base[tid] = run;
+  }
+  __syncthreads();
+  // exclusive scans over the experts (rows and tiles), 256 threads = 8 warps
+  if (tid < MOE_MAX_EXPERTS) {
+    const int rows = tid < E ? base[tid] : 0;
+    const int tiles = (rows + tile_rows - 1) / tile_rows;
+    int r = rows, t = tiles;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r2 = __shfl_up_sync(0xffffffffu, r, o);
+      const int t2 = __shfl_up_sync(0xffffffffu, t, o);
+      if (lane >= o) {
+        r += r2;
+        t += t2;
+      }
+    }
+    if (lane == 31) {
+      wsum[warp] = r;
+      wsum[8 + warp] = t;
+    }
+    // (only warps 0..7 reach here; named barrier over their 256 threads)
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    int roff = 0, toff = 0;
+    for (int w = 0; w < warp; ++w) {
+      roff += wsum[w];
+      toff += wsum[8 + w];
+    }
+    const int rexcl = roff + r - rows;
+    const int texcl = toff + t - tiles;
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (tid < E) {
+      base[tid] = rexcl;
+      tbase[tid] = texcl;
+      cu_seqlens[tid] = rexcl;
+      for (int j = 0; j < tiles; ++j)
+        if (texcl + j < max_tiles)
+          tile_table[texcl + j] = make_int4(tid, rexcl + j * tile_rows, min(tile_rows, rows - j * tile_rows), 0);
+      if (tid == E - 1) {
+        cu_seqlens[E] = rexcl + rows;
+        *tile_count = min(texcl + tiles, max_tiles);
+      }
+    }
+  }
+  __syncthreads();
+  // pass 2: local rank -> global position
+  for (long long o = 0; o < seg; o += 32) {
+    const long long i = w0 + o + lane;
+    if (i < n) {
+      const long long ev = (long long)experts[i];
+      if (ev >= 0 && ev < E) scatter_index[i] += base[(int)ev] + cnt[warp][(int)ev];
+    }
   }
 }
 
@@ -290,12 +336,12 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
 
 // out[t] = bf16( sum_k fp32(y[scatter_index[t, k]]) ), k ascending; optionally followed by
 // out[t] = bf16(fp32(out[t]) + fp32(addend[t])) (shared-expert or residual add as a separate bf16 op).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ scatter_index,
                             const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out, int H,
                             int topk) {
   const long long t = blockIdx.x;
-  for (int v = threadIdx.x; v < (H >> 3); v += 128) {
+  for (int v = threadIdx.x; v < (H >> 3); v += 256) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -431,7 +477,7 @@ extern "C" int b200_moe_unpermute_reduce(const void* y, const void* scatter_inde
   if (!y || !scatter_index || !out || T < 0 || topk <= 0 || H <= 0) return B200_ERR_ARG;
   if (H % 8 != 0) return B200_ERR_SHAPE;
   if (T == 0) return B200_OK;
-  moe_unpermute_reduce_kernel<<<(unsigned)T, 128, 0, (cudaStream_t)stream>>>(
+  moe_unpermute_reduce_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, H,
       topk);
   return launch_status();

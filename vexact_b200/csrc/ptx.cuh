@@ -44,14 +44,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
-  uint32_t spins = 0;
-  while (true) {
+  // Fast path: no timer read (%globaltimer is slow) until the wait has spun for a long while.
+  uint64_t t0 = 0;
+  for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+    if ((spins & 63u) == 0 && *abort_flag) return false;
+    if ((spins & 4095u) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         report_status(B200_STATUS_WAIT_EXPIRED, id);
         return false;

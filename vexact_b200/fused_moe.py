@@ -20,7 +20,7 @@ import torch
 
 from . import _lib
 
-TILE_ROWS = 128  # largest token tile of the grouped GEMM (rows of one expert per tile)
+TILE_ROWS = 64  # largest token tile of the grouped GEMM (rows of one expert per tile)
 
 
 def max_token_tiles(num_rows: int, num_experts: int, tile_rows: int = TILE_ROWS) -> int:
