@@ -137,6 +137,18 @@ int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, v
                           int n_out, int K, long long out_row_stride, int max_tiles, int tile_rows_max, int mode,
                           void* stream);
 
+/* No counterpart in the reference.  b200_moe_grouped_gemm for callers that cannot allocate device
+ * memory (a C/C++ host with statically owned buffers, a thread barred from cudaMalloc while a
+ * stream capture is open, a service with a fixed memory budget): rows already sorted by group
+ * plus cu_seqlens [num_groups + 1] (int32, device), as quack's varlen GEMM takes them.  The token-
+ * tile table lives in a fixed ~64 KiB device array inside the library, shared by all calls (calls
+ * that overlap on the GPU race on it).  Limits: num_groups <= 1024 and
+ * num_groups + x_rows / 64 <= 4095; larger problems return -2.  The first call on a device looks
+ * up the array's address and should be made before any stream capture. */
+int b200_moe_grouped_gemm_noalloc(const void* x, const void* w, const void* row_scale, void* out,
+                                  const void* cu_seqlens, long long x_rows, int num_groups, int n_out, int K,
+                                  long long out_row_stride, int mode, void* stream);
+
 /* ---- vexact/batch_invariant_ops/fused_moe.py:325-336 for split gate / up weights. */
 int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out, long long rows,
                       int I, void* stream);

@@ -35,6 +35,7 @@ SIGNATURES = {
     "b200_moe_route_sigmoid_group_topk": [P, LL, P, P, P, P, LL, I, I, I, I, I, F, P],
     "b200_moe_permute": [P, I, P, P, LL, P, P, P, P, P, P, LL, I, I, I, I, I, P],
     "b200_moe_grouped_gemm": [P, P, P, P, P, P, LL, I, I, I, LL, I, I, I, P],
+    "b200_moe_grouped_gemm_noalloc": [P, P, P, P, P, LL, I, I, I, LL, I, P],
     "b200_swiglu_scale": [P, P, P, P, LL, I, P],
     "b200_moe_unpermute_reduce": [P, P, P, P, LL, I, I, P],
 }

@@ -6,6 +6,7 @@
 #include "gemm.cuh"
 #include "attn.cuh"
 #include "moe.cuh"
+#include "noalloc.cuh"
 
 // Copies the device status word ({code, detail, block, spare}) to host memory and clears it.
 // Synchronises the stream: call it outside graph capture, after the work of interest.
