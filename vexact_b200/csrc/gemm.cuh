@@ -60,6 +60,7 @@ struct GemmParams {
   int xbox;       // rows per activation TMA box (multiple of 16)
   int xrows_max;  // largest token count of any tile (multiple of xbox, <= 256)
   int stages;
+  int katoms;     // 64-element K atoms per pipeline stage (1, 2 or 4)
   int tmem_cols;  // power of two >= 2 * xrows_max
   // Epilogue.
   void* out;
@@ -68,7 +69,6 @@ struct GemmParams {
   const __nv_bfloat16* bias;       // [n_w] or null (plain mode)
   const __nv_bfloat16* row_scale;  // [rows] or null (SwiGLU mode: routing weight of each permuted row)
   uint64_t w_policy;
-  int dbg;  // timing experiments only (B200_GEMM_DBG); results are wrong when non-zero
 };
 
 struct GemmTile {
@@ -104,7 +104,9 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_raw + (2 * GEMM_MAX_STAGES + 4) * 8 + 8);
   const uint32_t smem_base = ptx::smem_u32(smem_raw);
   const uint32_t stage_base = (smem_base + 256 + 1023) & ~1023u;
-  const int stage_bytes = GEMM_WBYTES + p.xrows_max * (GEMM_BK * 2);
+  const int atom_bytes = GEMM_WBYTES + p.xrows_max * (GEMM_BK * 2);
+  const int KA = p.katoms;
+  const int stage_bytes = atom_bytes * KA;
   __nv_bfloat16* exch =
       reinterpret_cast<__nv_bfloat16*>(smem_raw + (stage_base - smem_base) + (size_t)S * stage_bytes);
 
@@ -139,12 +141,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
 
   const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
-  const int num_kb = (p.k + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb = (p.k + GEMM_BK * KA - 1) / (GEMM_BK * KA);  // K beyond the tensor reads as zero
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;  // running stage counter across tiles
+    if (ptx::elect_one()) {
+      uint32_t it = 0;   // running stage counter across tiles
+      int s = 0;         // ring slot of `it`
+      uint32_t ph = 0;   // parity of the slot's current use
       bool ok = true;
       for (long long lin = blockIdx.x; ok; lin += gridDim.x) {
         GemmTile t;
@@ -152,37 +156,34 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int nbox = (t.n + p.xbox - 1) / p.xbox;
         const uint32_t tx = GEMM_WBYTES + (uint32_t)nbox * p.xbox * (GEMM_BK * 2);
         const int wrow = t.group * p.w_rows_per_group + t.wt * (SWIGLU ? 64 : GEMM_WTILE);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % S;
-          if (!ptx::mbar_wait(empty_bar(s), ((it / S) & 1) ^ 1, abort_flag, 100 + s)) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+          if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 100 + s)) {
             ok = false;
             break;
           }
-          const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
-          const uint32_t sx = sw + GEMM_WBYTES;
-          if ((p.dbg & 2) && it >= (uint32_t)S) {
-            ptx::mbar_arrive(full_bar(s));
-            continue;
+          ptx::mbar_expect_tx(full_bar(s), tx * KA);
+          for (int a = 0; a < KA; ++a) {
+            const uint32_t sw = stage_base + (uint32_t)s * stage_bytes + (uint32_t)a * atom_bytes;
+            const uint32_t sx = sw + GEMM_WBYTES;
+            const int kcol = (kb * KA + a) * GEMM_BK;
+            if (SWIGLU) {
+              ptx::tma_load_2d(sw, &tm_w, full_bar(s), kcol, wrow, p.w_policy);
+              ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kcol, wrow + p.up_offset, p.w_policy);
+            } else {
+              ptx::tma_load_2d(sw, &tm_w, full_bar(s), kcol, wrow, p.w_policy);
+            }
+            for (int b = 0; b < nbox; ++b)
+              ptx::tma_load_2d(sx + (uint32_t)b * p.xbox * (GEMM_BK * 2), &tm_x, full_bar(s), kcol,
+                               t.row0 + b * p.xbox, ptx::kEvictLast);
           }
-          ptx::mbar_expect_tx(full_bar(s), ((p.dbg & 1) && it >= (uint32_t)S) ? GEMM_WBYTES : tx);
-          if (SWIGLU) {
-            ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
-            ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kb * GEMM_BK, wrow + p.up_offset,
-                             p.w_policy);
-          } else {
-            ptx::tma_load_2d(sw, &tm_w, full_bar(s), kb * GEMM_BK, wrow, p.w_policy);
-          }
-          if ((p.dbg & 1) && it >= (uint32_t)S) continue;
-          for (int b = 0; b < nbox; ++b)
-            ptx::tma_load_2d(sx + (uint32_t)b * p.xbox * (GEMM_BK * 2), &tm_x, full_bar(s), kb * GEMM_BK,
-                             t.row0 + b * p.xbox, ptx::kEvictLast);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      uint32_t it = 0, tile_it = 0;
+    if (ptx::elect_one()) {
+      uint32_t it = 0, tile_it = 0, ph = 0;
+      int s = 0;
       bool ok = true;
       for (long long lin = blockIdx.x; ok; lin += gridDim.x, ++tile_it) {
         GemmTile t;
@@ -193,20 +194,21 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (!ptx::mbar_wait(tempty_bar(buf), ((tile_it >> 1) & 1) ^ 1, abort_flag, 200 + buf)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.xrows_max);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % S;
-          if (!ptx::mbar_wait(full_bar(s), (it / S) & 1, abort_flag, 300 + s)) {
+        const uint64_t desc_hi = ptx::umma_desc_k_sw128(0) & 0xFFFFFFFF00000000ull;
+        for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+          if (!ptx::mbar_wait(full_bar(s), ph, abort_flag, 300 + s)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t sw = stage_base + (uint32_t)s * stage_bytes;
-          const uint32_t sx = sw + GEMM_WBYTES;
+          for (int a = 0; a < KA; ++a) {
+            const uint32_t sw = stage_base + (uint32_t)s * stage_bytes + (uint32_t)a * atom_bytes;
+            // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element K step
+            const uint64_t da = desc_hi | (uint64_t)(((sw & 0x3FFFFu) >> 4) | (1u << 16));
+            const uint64_t db = desc_hi | (uint64_t)((((sw + GEMM_WBYTES) & 0x3FFFFu) >> 4) | (1u << 16));
+            ptx::umma_bf16(d_tmem, da, db, idesc, (kb | a) != 0 ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < ((p.dbg & 4) ? 1 : GEMM_BK / 16); ++kk) {
-            const uint64_t da = ptx::umma_desc_k_sw128(sw + kk * 32);
-            const uint64_t db = ptx::umma_desc_k_sw128(sx + kk * 32);
-            ptx::umma_bf16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            for (int kk = 1; kk < GEMM_BK / 16; ++kk) ptx::umma_bf16_acc(d_tmem, da + 2 * kk, db + 2 * kk, idesc);
           }
           ptx::umma_commit(empty_bar(s));  // stage is free once these MMAs have read it
         }
@@ -357,7 +359,16 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
       return B200_ERR_LAUNCH;
     attr_set = true;
   }
-  const int stage_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
+  const int atom_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
+  const int exch_bytes_pre = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
+  // K atoms per stage: fewer, larger stages cut the per-stage barrier round trips; keep >= 3 stages.
+  static const int ka_env = env_int("B200_GEMM_KATOMS", 2);
+  int ka = (ka_env == 1 || ka_env == 2 || ka_env == 4) ? ka_env : 2;
+  while (ka > 1 && ((GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes_pre) / (atom_bytes * ka) < 3 ||
+                    (p.k + GEMM_BK - 1) / GEMM_BK < ka))
+    ka >>= 1;
+  p.katoms = ka;
+  const int stage_bytes = atom_bytes * ka;
   const int exch_bytes = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
   int stages = (GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
@@ -367,10 +378,6 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   }
   if (stages < 2) return B200_ERR_SHAPE;
   p.stages = stages;
-  {
-    static const int dbg = env_int("B200_GEMM_DBG", 0);
-    p.dbg = dbg;
-  }
   int cols = 32;
   while (cols < 2 * p.xrows_max) cols <<= 1;
   if (cols > 512) return B200_ERR_SHAPE;
@@ -437,16 +444,25 @@ extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, vo
   p.up_offset = 0;
   p.t_rows = (int)T;
   // Token tiling.  A token's result does not depend on the tile it lands in (tokens are independent
-  // UMMA columns), so the tile width is chosen for occupancy only: enough tiles to cover every SM
-  // about twice when the weight has few row tiles, at most 256 and at least 16 tokens per tile.
+  // UMMA columns), so the tile width is chosen for speed only.  Every tile streams K/64 stages of
+  // (16 KiB of weights + 128 B per token) into shared memory and the persistent CTAs work through
+  // the tiles in rounds, so the cost of a tiling is rounds x bytes per stage; take the cheapest.
   {
+    const int sms = sm_count();
     const int min_tiles = (int)((T + 255) / 256);
     const int max_tiles = (int)((T + 15) / 16);
-    int want = (2 * sm_count() + p.w_tiles - 1) / p.w_tiles;
-    if (want < min_tiles) want = min_tiles;
-    if (want > max_tiles) want = max_tiles;
-    p.rows_per_tile = round_up((int)((T + want - 1) / want), 16);
-    p.dense_t_tiles = (int)((T + p.rows_per_tile - 1) / p.rows_per_tile);
+    long long best_cost = -1;
+    for (int tt = min_tiles; tt <= max_tiles; ++tt) {
+      const int rows = round_up((int)((T + tt - 1) / tt), 16);
+      const int tiles_t = (int)((T + rows - 1) / rows);
+      const long long rounds = ((long long)tiles_t * p.w_tiles + sms - 1) / sms;
+      const long long cost = rounds * (GEMM_WBYTES + rows * GEMM_BK * 2);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        p.rows_per_tile = rows;
+        p.dense_t_tiles = tiles_t;
+      }
+    }
   }
   p.tile_table = nullptr;
   p.tile_count = nullptr;
