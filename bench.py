@@ -302,17 +302,27 @@ def main():
             return outs[b]
         return runners[b].step(step_inputs[b])
 
-    # Hidden states travel r -> r+1 on the default group; the sampled token ids close the ring
-    # (last -> first) on a second group, i.e. another communicator and stream, so a stage can send
-    # the next batch forward while the previous batch's tokens are still on their way back.
+    # Hidden states travel r -> r+1 on a group of their own per adjacent pair (as the reference's
+    # PPMessager builds them), and the sampled token ids close the ring (last -> first) on another
+    # group: every direction has its own communicator and stream, so a stage can receive the next
+    # batch, send the previous one and return tokens at the same time.  All transfers are
+    # asynchronous; a buffer's transfer is waited for only where the buffer is next touched.
     tok_host = torch.empty(S, dtype=torch.int64).pin_memory()
     lp_host = torch.empty(S, dtype=torch.float32).pin_memory()
+    pair_groups = [dist.new_group(ranks=[i, i + 1]) for i in range(pp - 1)] if pp > 1 else []
     fb_group = dist.new_group(ranks=list(range(pp))) if pp > 1 else None
+    g_prev = pair_groups[rank - 1] if rank > 0 else None
+    g_next = pair_groups[rank] if rank < pp - 1 else None
     recv_tok = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(n_inflight)]
-    pending = [None] * n_inflight
+    pending = [None] * n_inflight      # rank 0: token feedback of each batch's previous step
+    recv_h = [None] * n_inflight       # rank > 0: hidden-state receives of this step
+    send_h = [None] * n_inflight       # sends whose source buffer the next replay overwrites
 
     def global_step(e2e=False):
         """Advance every in-flight batch by one token through this rank's stage."""
+        if rank > 0:
+            for b in range(n_inflight):
+                recv_h[b] = dist.irecv(hidden_in[b], src=rank - 1, group=g_prev)
         for b in range(n_inflight):
             if rank == 0:
                 if pending[b] is not None:      # tokens of this batch's previous step
@@ -322,26 +332,31 @@ def main():
                     for k, v in host_inputs[b].items():
                         dev_inputs[b][k].copy_(v, non_blocking=True)
             else:
-                dist.recv(hidden_in[b], src=rank - 1)
+                recv_h[b].wait()
+                recv_h[b] = None
+            if send_h[b] is not None:           # the previous step's send reads this graph's output
+                send_h[b].wait()
+                send_h[b] = None
             out = run_stage(b)
             if rank < pp - 1:
-                dist.send(out, dst=rank + 1)
+                send_h[b] = dist.isend(out, dst=rank + 1, group=g_next)
             else:
                 if e2e:
                     tok_host.copy_(out[0], non_blocking=True)
                     lp_host.copy_(out[1], non_blocking=True)
                 if pp > 1:
-                    dist.isend(out[0], dst=0, group=fb_group)
+                    send_h[b] = dist.isend(out[0], dst=0, group=fb_group)
             if pp > 1 and rank == 0:
                 pending[b] = dist.irecv(recv_tok[b], src=pp - 1, group=fb_group)
         if e2e:
             torch.cuda.current_stream().synchronize()
 
     def drain():
-        for b in range(n_inflight):
-            if pending[b] is not None:
-                pending[b].wait()
-                pending[b] = None
+        for lst in (pending, send_h, recv_h):
+            for b in range(n_inflight):
+                if lst[b] is not None:
+                    lst[b].wait()
+                    lst[b] = None
 
     def sync_all():
         drain()
@@ -428,10 +443,11 @@ def main():
            "ms_per_launch": att_ms}
 
     # ---- gather timing across ranks (max), emit
-    t = torch.tensor([dev_ms, e2e_s * 1e3], device=device, dtype=torch.float64)
+    t = torch.tensor([dev_ms, e2e_s * 1e3, float(h2d), float(d2h)], device=device, dtype=torch.float64)
     if pp > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = t.tolist()
+    dev_ms, e2e_ms, h2d, d2h = t.tolist()
+    h2d, d2h = int(h2d), int(d2h)
     tokens_per_step = S * n_inflight
     value = tokens_per_step * args.steps / (dev_ms * 1e-3)
     e2e_value = tokens_per_step * args.steps / (e2e_ms * 1e-3)

@@ -102,11 +102,15 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const uint32_t tile_base = (ptx::smem_u32(smem_raw) + 1023) & ~1023u;
   uint8_t* tile_ptr = smem_raw + (tile_base - ptx::smem_u32(smem_raw));
 
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x;
   const int g = lane >> 2, t = lane & 3;
-  const int seq = blockIdx.y;
-  const int kvh = blockIdx.z / p.head_chunks;
-  const int hchunk = blockIdx.z % p.head_chunks;
+  // KV heads vary fastest in launch order, so the CTAs that walk the same sequence's pages (one
+  // per KV head) run at the same time and share DRAM pages and 256-byte L2 sectors.
+  const int seq = blockIdx.z;
+  const int kvh = blockIdx.y / p.head_chunks;
+  const int hchunk = blockIdx.y % p.head_chunks;
   const int heads_here = min(8, p.group - hchunk * 8);  // query heads of this KV head covered by the CTA
 
   const int q_start = p.cu_seqlens_q[seq];
@@ -363,7 +367,7 @@ inline int attn_launch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnP
       return B200_ERR_LAUNCH;
     attr_set = true;
   }
-  paged_attn_kernel<DK, DV, STAGES><<<grid, 32, smem, st>>>(tk, tv, p);
+  launch_k(paged_attn_kernel<DK, DV, STAGES>, grid, dim3(32), (size_t)smem, st, tk, tv, p);
   return launch_status();
 }
 
@@ -426,8 +430,8 @@ extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const voi
                        vc_head_stride, p.box_tokens);
   if (rc) return rc;
   const int q_tiles = (max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile;
-  dim3 grid((unsigned)q_tiles, (unsigned)num_seqs, (unsigned)(num_kv_heads * p.head_chunks));
-  if (num_seqs > 65535 || grid.z > 65535) return B200_ERR_SHAPE;
+  dim3 grid((unsigned)q_tiles, (unsigned)(num_kv_heads * p.head_chunks), (unsigned)num_seqs);
+  if (num_seqs > 65535 || grid.y > 65535) return B200_ERR_SHAPE;
   cudaStream_t st = (cudaStream_t)stream;
   if (dk == 128 && dv == 128) return attn_launch<128, 128, 3>(tk, tv, p, grid, st);
   if (dk == 192 && dv == 128) return attn_launch<192, 128, 2>(tk, tv, p, grid, st);

@@ -13,6 +13,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define B200_OK 0
 #define B200_ERR_ARG (-1)
@@ -95,6 +96,38 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
+}
+
+// Programmatic dependent launch.  Kernels of the per-layer chain are launched with the
+// programmatic-stream-serialization attribute: a kernel may start (and run its prologue) while
+// its predecessor drains, and touches global memory only after pdl_wait(), which returns once
+// the predecessor has completed and its writes are visible.  pdl_trigger() lets the successor
+// begin launching; every CTA calls it first thing, so a successor can become resident only
+// when every CTA of this kernel has started.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = []() {
+    const char* v = getenv("B200_PDL");  // off unless B200_PDL=1: measured neutral inside CUDA graphs
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 inline int launch_status() {

@@ -139,6 +139,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_trigger();
+  pdl_wait();  // everything above is set-up; inputs written by the previous kernel are read below
 
   const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
   const int num_kb = (p.k + GEMM_BK * KA - 1) / (GEMM_BK * KA);  // K beyond the tensor reads as zero
@@ -385,7 +387,7 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   const size_t smem = 256 + 1024 + (size_t)stages * stage_bytes + exch_bytes;
   long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid <= 0) return B200_OK;
-  gemm_ws_kernel<SWIGLU><<<(unsigned)grid, GEMM_THREADS, smem, st>>>(tw, tx, p);
+  launch_k(gemm_ws_kernel<SWIGLU>, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, st, tw, tx, p);
   return launch_status();
 }
 

@@ -22,6 +22,8 @@ kv_store_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
                 __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                 const int* __restrict__ slot_mapping, long long k_tok_stride, long long v_tok_stride,
                 int k_row, int v_row, long long num_slots) {
+  pdl_trigger();
+  pdl_wait();
   const long long tok = blockIdx.x;
   const long long slot = slot_mapping[tok];
   if (slot < 0) return;
@@ -57,6 +59,8 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
                          __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
                          int num_q_heads, int num_kv_heads, long long num_tokens, long long num_slots,
                          float eps) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int D = 128;
   const int heads_total = num_q_heads + 2 * num_kv_heads;
   const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -140,7 +144,7 @@ extern "C" int b200_kv_store(const void* key, const void* value, void* k_cache, 
       k_head_dim <= 0 || v_head_dim <= 0 || num_slots < 0)
     return B200_ERR_ARG;
   if (num_tokens == 0) return B200_OK;
-  kv_store_kernel<<<(unsigned)num_tokens, 128, 0, (cudaStream_t)stream>>>(
+  launch_k(kv_store_kernel, dim3((unsigned)num_tokens), dim3(128), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)key, (const __nv_bfloat16*)value, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
       (const int*)slot_mapping, k_token_stride, v_token_stride, num_kv_heads * k_head_dim,
       num_kv_heads * v_head_dim, num_slots);
@@ -162,7 +166,7 @@ extern "C" int b200_qknorm_rope_store(const void* qkv, long long qkv_token_strid
   if (qkv_token_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(qkv) & 7) != 0) return B200_ERR_ARG;
   if (num_tokens == 0) return B200_OK;
   const long long warps = num_tokens * (num_q_heads + 2 * num_kv_heads);
-  qknorm_rope_store_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  launch_k(qknorm_rope_store_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)qkv, qkv_token_stride, (const long long*)positions, (const int*)slot_mapping,
       (const __nv_bfloat16*)q_norm_weight, (const __nv_bfloat16*)k_norm_weight, (const float*)inv_freq,
       (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_q_heads, num_kv_heads,

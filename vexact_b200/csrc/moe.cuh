@@ -29,6 +29,8 @@ moe_route_softmax_topk_kernel(const TIn* __restrict__ logits, long long row_stri
                               __nv_bfloat16* __restrict__ w_bf16, float* __restrict__ w_f32,
                               int* __restrict__ idx_i32, long long* __restrict__ idx_i64, long long T, int E,
                               int topk, int renorm) {
+  pdl_trigger();
+  pdl_wait();
   const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (tok >= T) return;
   const int lane = threadIdx.x & 31;
@@ -112,6 +114,8 @@ moe_route_sigmoid_group_topk_kernel(const float* __restrict__ logits, long long 
                                     const float* __restrict__ bias, float* __restrict__ w_out,
                                     int* __restrict__ idx_i32, long long* __restrict__ idx_i64, long long T,
                                     int E, int n_group, int topk_group, int topk, int renorm, float scale) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float s_sig[8][MOE_MAX_EXPERTS];
   __shared__ float s_choice[8][MOE_MAX_EXPERTS];
   __shared__ float s_gscore[8][32];
@@ -221,6 +225,8 @@ __global__ void __launch_bounds__(1024)
 moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_rows,
                  int* __restrict__ scatter_index, int* __restrict__ cu_seqlens, int4* __restrict__ tile_table,
                  int* __restrict__ tile_count, int max_tiles) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int cnt[32][MOE_MAX_EXPERTS];  // per-warp counts, then per-warp exclusive offsets
   __shared__ int base[MOE_MAX_EXPERTS];     // expert totals, then exclusive prefix (cu_seqlens)
   __shared__ int tbase[MOE_MAX_EXPERTS];    // first tile index of each expert
@@ -324,6 +330,8 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
                         const __nv_bfloat16* __restrict__ weights, const int* __restrict__ scatter_index,
                         __nv_bfloat16* __restrict__ x_perm, __nv_bfloat16* __restrict__ row_scale, int H,
                         int topk) {
+  pdl_trigger();
+  pdl_wait();
   const long long f = blockIdx.x;
   const int pos = scatter_index[f];
   if (pos < 0) return;
@@ -340,6 +348,8 @@ __global__ void __launch_bounds__(256)
 moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ scatter_index,
                             const __nv_bfloat16* __restrict__ addend, __nv_bfloat16* __restrict__ out, int H,
                             int topk) {
+  pdl_trigger();
+  pdl_wait();
   const long long t = blockIdx.x;
   for (int v = threadIdx.x; v < (H >> 3); v += 256) {
     float acc[8];
@@ -382,6 +392,8 @@ __global__ void __launch_bounds__(256)
 swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                     const __nv_bfloat16* __restrict__ row_scale, __nv_bfloat16* __restrict__ out, long long rows,
                     int I) {
+  pdl_trigger();
+  pdl_wait();
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= rows * I) return;
   const float g = bf2f(gate[i]);
@@ -406,11 +418,11 @@ extern "C" int b200_moe_route_softmax_topk(const void* logits, int logits_dtype 
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)((T + 7) / 8);
   if (logits_dtype == 0)
-    moe_route_softmax_topk_kernel<float><<<grid, 256, 0, st>>>(
+    launch_k(moe_route_softmax_topk_kernel<float>, dim3(grid), dim3(256), 0, st, 
         (const float*)logits, row_stride, (__nv_bfloat16*)weights_bf16, (float*)weights_f32, (int*)experts_i32,
         (long long*)experts_i64, T, E, topk, renorm);
   else if (logits_dtype == 1)
-    moe_route_softmax_topk_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+    launch_k(moe_route_softmax_topk_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, 
         (const __nv_bfloat16*)logits, row_stride, (__nv_bfloat16*)weights_bf16, (float*)weights_f32,
         (int*)experts_i32, (long long*)experts_i64, T, E, topk, renorm);
   else
@@ -431,7 +443,7 @@ extern "C" int b200_moe_route_sigmoid_group_topk(const void* logits_f32, long lo
       E / n_group < 2)
     return B200_ERR_SHAPE;
   if (T == 0) return B200_OK;
-  moe_route_sigmoid_group_topk_kernel<<<(unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  launch_k(moe_route_sigmoid_group_topk_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (const float*)logits_f32, row_stride, (const float*)bias_f32, (float*)weights_f32, (int*)experts_i32,
       (long long*)experts_i64, T, E, n_group, topk_group, topk, renorm, scale);
   return launch_status();
@@ -454,17 +466,17 @@ extern "C" int b200_moe_permute(const void* experts, int experts_dtype /*0 = i32
   cudaStream_t st = (cudaStream_t)stream;
   const long long n = T * topk;
   if (experts_dtype == 0)
-    moe_index_kernel<int><<<1, 1024, 0, st>>>((const int*)experts, n, E, tile_rows, (int*)scatter_index,
+    launch_k(moe_index_kernel<int>, dim3(1), dim3(1024), 0, st, (const int*)experts, n, E, tile_rows, (int*)scatter_index,
                                               (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles);
   else if (experts_dtype == 1)
-    moe_index_kernel<long long><<<1, 1024, 0, st>>>((const long long*)experts, n, E, tile_rows,
+    launch_k(moe_index_kernel<long long>, dim3(1), dim3(1024), 0, st, (const long long*)experts, n, E, tile_rows,
                                                     (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table,
                                                     (int*)tile_count, max_tiles);
   else
     return B200_ERR_ARG;
   int rc = launch_status();
   if (rc || n == 0 || !x || !x_perm) return rc;
-  moe_scatter_rows_kernel<<<(unsigned)n, 128, 0, st>>>((const __nv_bfloat16*)x, x_row_stride,
+  launch_k(moe_scatter_rows_kernel, dim3((unsigned)n), dim3(128), 0, st, (const __nv_bfloat16*)x, x_row_stride,
                                                        (const __nv_bfloat16*)weights_bf16,
                                                        (const int*)scatter_index, (__nv_bfloat16*)x_perm,
                                                        (__nv_bfloat16*)row_scale, H, topk);
@@ -477,7 +489,7 @@ extern "C" int b200_moe_unpermute_reduce(const void* y, const void* scatter_inde
   if (!y || !scatter_index || !out || T < 0 || topk <= 0 || H <= 0) return B200_ERR_ARG;
   if (H % 8 != 0) return B200_ERR_SHAPE;
   if (T == 0) return B200_OK;
-  moe_unpermute_reduce_kernel<<<(unsigned)T, 256, 0, (cudaStream_t)stream>>>(
+  launch_k(moe_unpermute_reduce_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, H,
       topk);
   return launch_status();
@@ -489,7 +501,7 @@ extern "C" int b200_swiglu_scale(const void* gate, const void* up, const void* r
   if (!gate || !up || !out || rows < 0 || I <= 0) return B200_ERR_ARG;
   if (rows == 0) return B200_OK;
   const long long n = rows * I;
-  swiglu_scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+  launch_k(swiglu_scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (const __nv_bfloat16*)row_scale, (__nv_bfloat16*)out,
       rows, I);
   return launch_status();

@@ -107,6 +107,8 @@ rmsnorm_cta_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
                    __nv_bfloat16* __restrict__ sum_out, long long x_stride, long long res_stride,
                    long long out_stride, long long sum_stride, int n, float eps, int mode) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
   rmsnorm_row<128, 8, ADD_RESIDUAL>(x + row * x_stride, ADD_RESIDUAL ? res + row * res_stride : nullptr, w,
@@ -123,6 +125,8 @@ rmsnorm_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
                     __nv_bfloat16* __restrict__ sum_out, long long x_stride, long long res_stride,
                     long long out_stride, long long sum_stride, long long rows, int n, float eps,
                     int mode) {
+  pdl_trigger();
+  pdl_wait();
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   rmsnorm_row<32, 4, ADD_RESIDUAL>(x + row * x_stride, ADD_RESIDUAL ? res + row * res_stride : nullptr, w,
@@ -137,6 +141,8 @@ rmsnorm_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
                        __nv_bfloat16* __restrict__ sum_out, long long x_stride, long long res_stride,
                        long long out_stride, long long sum_stride, int n, float eps, int mode) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float scratch[32];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * x_stride;
@@ -164,6 +170,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 mean_lastdim_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows, int n,
                     long long x_stride) {
+  pdl_trigger();
+  pdl_wait();
   const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -191,13 +199,13 @@ extern "C" int b200_rmsnorm(const void* x, const void* weight, void* out, long l
   const bool vec = (n % 8 == 0) && aligned16(x) && aligned16(weight) && aligned16(out) &&
                    (x_row_stride % 8 == 0) && (out_row_stride % 8 == 0);
   if (vec && n <= 1024) {
-    rmsnorm_warp_kernel<false><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+    launch_k(rmsnorm_warp_kernel<false>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, 
         X, nullptr, W, O, nullptr, x_row_stride, 0, out_row_stride, 0, rows, n, eps, mode);
   } else if (vec && n <= 8192) {
-    rmsnorm_cta_kernel<false><<<(unsigned)rows, 128, 0, st>>>(X, nullptr, W, O, nullptr, x_row_stride, 0,
+    launch_k(rmsnorm_cta_kernel<false>, dim3((unsigned)rows), dim3(128), 0, st, X, nullptr, W, O, nullptr, x_row_stride, 0,
                                                                out_row_stride, 0, n, eps, mode);
   } else {
-    rmsnorm_generic_kernel<<<(unsigned)rows, 128, 0, st>>>(X, nullptr, W, O, nullptr, x_row_stride, 0,
+    launch_k(rmsnorm_generic_kernel, dim3((unsigned)rows), dim3(128), 0, st, X, nullptr, W, O, nullptr, x_row_stride, 0,
                                                             out_row_stride, 0, n, eps, mode);
   }
   return launch_status();
@@ -218,12 +226,12 @@ extern "C" int b200_add_rmsnorm(const void* x, const void* residual, const void*
   const bool vec = (n % 8 == 0) && aligned16(x) && aligned16(residual) && aligned16(weight) &&
                    aligned16(out) && aligned16(sum_out);
   if (vec && n <= 1024) {
-    rmsnorm_warp_kernel<true><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(X, R, W, O, S, n, n, n, n, rows, n,
+    launch_k(rmsnorm_warp_kernel<true>, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, st, X, R, W, O, S, n, n, n, n, rows, n,
                                                                           eps, mode);
   } else if (vec && n <= 8192) {
-    rmsnorm_cta_kernel<true><<<(unsigned)rows, 128, 0, st>>>(X, R, W, O, S, n, n, n, n, n, eps, mode);
+    launch_k(rmsnorm_cta_kernel<true>, dim3((unsigned)rows), dim3(128), 0, st, X, R, W, O, S, n, n, n, n, n, eps, mode);
   } else {
-    rmsnorm_generic_kernel<<<(unsigned)rows, 128, 0, st>>>(X, R, W, O, S, n, n, n, n, n, eps, mode);
+    launch_k(rmsnorm_generic_kernel, dim3((unsigned)rows), dim3(128), 0, st, X, R, W, O, S, n, n, n, n, n, eps, mode);
   }
   return launch_status();
 }
@@ -236,10 +244,9 @@ extern "C" int b200_mean_lastdim(const void* x, void* out, long long rows, int n
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)((rows + 7) / 8);
   if (dtype == 0) {
-    mean_lastdim_kernel<float><<<grid, 256, 0, st>>>((const float*)x, (float*)out, rows, n, x_row_stride);
+    launch_k(mean_lastdim_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)x, (float*)out, rows, n, x_row_stride);
   } else if (dtype == 1) {
-    mean_lastdim_kernel<__nv_bfloat16>
-        <<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, n, x_row_stride);
+    launch_k(mean_lastdim_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, n, x_row_stride);
   } else {
     return B200_ERR_ARG;
   }

@@ -131,6 +131,8 @@ __device__ __forceinline__ MaxSum row_max_sum(const T* __restrict__ row, int n, 
 __global__ void __launch_bounds__(1024)
 log_softmax_f32_kernel(const float* __restrict__ x, float* __restrict__ out, int n, long long x_stride,
                        long long out_stride, bool vec) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sm[32], ss[32];
   const float* row = x + (long long)blockIdx.x * x_stride;
   float* orow = out + (long long)blockIdx.x * out_stride;
@@ -158,6 +160,8 @@ __global__ void __launch_bounds__(1024)
 gather_logprob_kernel(const T* __restrict__ x, const long long* __restrict__ labels,
                       float* __restrict__ out, int n, long long x_stride, long long ignore_index,
                       bool vec) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sm[32], ss[32];
   const T* row = x + (long long)blockIdx.x * x_stride;
   const long long label = labels[blockIdx.x];
@@ -181,7 +185,7 @@ extern "C" int b200_log_softmax_f32(const void* x, void* out, long long rows, in
   if (rows == 0) return B200_OK;
   const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                    x_row_stride % 4 == 0 && out_row_stride % 4 == 0;
-  log_softmax_f32_kernel<<<(unsigned)rows, 1024, 0, (cudaStream_t)stream>>>(
+  launch_k(log_softmax_f32_kernel, dim3((unsigned)rows), dim3(1024), 0, (cudaStream_t)stream, 
       (const float*)x, (float*)out, n, x_row_stride, out_row_stride, vec);
   return launch_status();
 }
@@ -195,11 +199,11 @@ extern "C" int b200_gather_logprob(const void* logits, const void* labels, void*
   cudaStream_t st = (cudaStream_t)stream;
   const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
   if (dtype == 0) {
-    gather_logprob_kernel<float><<<(unsigned)rows, 1024, 0, st>>>(
+    launch_k(gather_logprob_kernel<float>, dim3((unsigned)rows), dim3(1024), 0, st, 
         (const float*)logits, (const long long*)labels, (float*)out, n, row_stride, ignore_index,
         aligned && row_stride % 4 == 0);
   } else if (dtype == 1) {
-    gather_logprob_kernel<__nv_bfloat16><<<(unsigned)rows, 1024, 0, st>>>(
+    launch_k(gather_logprob_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(1024), 0, st, 
         (const __nv_bfloat16*)logits, (const long long*)labels, (float*)out, n, row_stride, ignore_index,
         aligned && row_stride % 8 == 0);
   } else {
