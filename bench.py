@@ -314,30 +314,35 @@ def main():
     g_prev = pair_groups[rank - 1] if rank > 0 else None
     g_next = pair_groups[rank] if rank < pp - 1 else None
     recv_tok = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(n_inflight)]
-    pending = [None] * n_inflight      # rank 0: token feedback of each batch's previous step
-    recv_h = [None] * n_inflight       # rank > 0: hidden-state receives of this step
+    pending = [False] * n_inflight     # rank 0: a token message of the batch's previous step is outstanding
     send_h = [None] * n_inflight       # sends whose source buffer the next replay overwrites
+
+    trace = [] if os.environ.get("B200_BENCH_TRACE") else None
 
     def global_step(e2e=False):
         """Advance every in-flight batch by one token through this rank's stage."""
-        if rank > 0:
-            for b in range(n_inflight):
-                recv_h[b] = dist.irecv(hidden_in[b], src=rank - 1, group=g_prev)
         for b in range(n_inflight):
             if rank == 0:
-                if pending[b] is not None:      # tokens of this batch's previous step
-                    pending[b].wait()
-                    pending[b] = None
+                if pp > 1 and pending[b]:       # tokens of this batch's previous step, received only now:
+                    # a receive posted earlier would poll on the GPU all through the stages in between
+                    dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
+                    pending[b] = False
                 if e2e:
                     for k, v in host_inputs[b].items():
                         dev_inputs[b][k].copy_(v, non_blocking=True)
             else:
-                recv_h[b].wait()
-                recv_h[b] = None
+                # posted only now: the receive kernel starts when the previous stage ends, so it does
+                # not sit on the GPU polling while that stage computes
+                dist.irecv(hidden_in[b], src=rank - 1, group=g_prev).wait()
             if send_h[b] is not None:           # the previous step's send reads this graph's output
                 send_h[b].wait()
                 send_h[b] = None
+            if trace is not None:
+                trace.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+                trace[-1][0].record()
             out = run_stage(b)
+            if trace is not None:
+                trace[-1][1].record()
             if rank < pp - 1:
                 send_h[b] = dist.isend(out, dst=rank + 1, group=g_next)
             else:
@@ -347,16 +352,18 @@ def main():
                 if pp > 1:
                     send_h[b] = dist.isend(out[0], dst=0, group=fb_group)
             if pp > 1 and rank == 0:
-                pending[b] = dist.irecv(recv_tok[b], src=pp - 1, group=fb_group)
+                pending[b] = True               # one token message is now owed to this batch
         if e2e:
             torch.cuda.current_stream().synchronize()
 
     def drain():
-        for lst in (pending, send_h, recv_h):
-            for b in range(n_inflight):
-                if lst[b] is not None:
-                    lst[b].wait()
-                    lst[b] = None
+        for b in range(n_inflight):
+            if pp > 1 and rank == 0 and pending[b]:
+                dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
+                pending[b] = False
+            if send_h[b] is not None:
+                send_h[b].wait()
+                send_h[b] = None
 
     def sync_all():
         drain()
@@ -382,6 +389,15 @@ def main():
     ev1.record()
     sync_all()
     dev_ms = ev0.elapsed_time(ev1)
+    if trace is not None:
+        tail = trace[-args.steps * n_inflight:]
+        st = [a.elapsed_time(b) for a, b in tail]
+        gaps = [tail[i][1].elapsed_time(tail[i + 1][0]) for i in range(len(tail) - 1)]
+        print(f"[trace rank {rank}] stage ms mean {sum(st) / len(st):.3f} max {max(st):.3f}; "
+              f"gap ms mean {sum(gaps) / max(len(gaps), 1):.3f} max {max(gaps) if gaps else 0:.3f}; "
+              f"step {dev_ms / args.steps:.3f}", file=sys.stderr, flush=True)
+        trace.clear()
+        trace = None
     if args.quick:
         if rank == 0:
             print(json.dumps({"quick": True, "ms_per_step": dev_ms / args.steps,
