@@ -91,6 +91,17 @@ int b200_qknorm_rope_store(const void* qkv, long long qkv_token_stride, const vo
                            long long num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
                            long long num_slots, float eps, void* stream);
 
+/* ---- vexact/models/deepseek_v3/modeling_deepseek_v3.py:225-283 deepseek_v3_attention_forward, the part
+ *      between the projections and the attention call (split nope / rope, interleaved rotary embedding
+ *      with the deterministic cos/sin of :409-436, k_rot expanded to every head, concat) followed by
+ *      store_kvcache.  q [T, heads, nope + 64]; kvb [T, heads, nope + dv] (kv_b_proj output);
+ *      k_rot [T, 64]; positions int64; inv_freq fp32 [32]; caches [blocks, page, heads, nope + 64 | dv]. */
+int b200_mla_rope_store(const void* q, long long q_token_stride, const void* kvb, long long kvb_token_stride,
+                        const void* k_rot, long long k_rot_token_stride, const void* positions,
+                        const void* slot_mapping, const void* inv_freq, void* q_out, void* k_cache,
+                        void* v_cache, long long num_tokens, int num_heads, int qk_nope_dim, int qk_rope_dim,
+                        int v_dim, long long num_slots, void* stream);
+
 /* ---- vexact/batch_invariant_ops/triton_invariant_attention.py:905 flash_attn_varlen_func with a
  *      page table (:605 _PagedFlashAttentionVarlen, kernel :434) and the FA3 / FA4 calls of
  *      vexact/batch_invariant_ops/flash_attention.py:142-178.  Causal only.

@@ -12,9 +12,13 @@ pytestmark = pytest.mark.gpu
 BF = torch.bfloat16
 
 
-def _tiny(moe: bool):
-    from vexact_b200.inferencer import ModelShape, MoEShape
+def _tiny(moe):
+    from vexact_b200.inferencer import MLAShape, ModelShape, MoEShape
 
+    if moe == "dsv3":   # DeepSeek-V3 / Moonlight layout: MLA, dense first layer, sigmoid-group routing, shared expert
+        return ModelShape("tiny-dsv3", 3, 512, 4, 4, 192, 1024, ffn=256, qk_norm=False, rope_theta=50000.0,
+                          mla=MLAShape(128, 128, 64, 128), first_k_dense=1, norm_single_round=True,
+                          moe=MoEShape(8, 2, 128, True, "sigmoid_group", 2, 1, 2.5, 1))
     if moe:
         return ModelShape("tiny-moe", 4, 512, 8, 2, 128, 1024, moe=MoEShape(16, 4, 128))
     return ModelShape("tiny-dense", 4, 512, 4, 2, 128, 1024, ffn=768, qk_norm=False, qkv_bias=True)
@@ -47,7 +51,7 @@ def _inputs(shape, q_lens, ctx_lens, page, device, seed=0):
     return host, inp, S * pages
 
 
-@pytest.mark.parametrize("moe", [False, True])
+@pytest.mark.parametrize("moe", [False, True, "dsv3"])
 def test_stage_forward_vs_cpu_model_and_invariance(moe):
     from vexact_b200.inferencer import StageRunner, StageWeights, allocate_kv_cache
 

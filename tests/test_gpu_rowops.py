@@ -163,6 +163,46 @@ def test_qknorm_rope_store(vb, with_norm):
         assert (got == want).float().mean() > 0.99
 
 
+def test_mla_rope_store(vb):
+    """Interleaved rotary embedding + K/V assembly of DeepSeek-V3 attention vs the oracle
+    (reference: modeling_deepseek_v3.py:240-261; HF apply_rotary_pos_emb_interleave)."""
+    from oracle import cpu_model
+    from vexact_b200 import _lib
+
+    T, heads, nope, rope, dv, blocks, page = 11, 4, 128, 64, 128, 4, 16
+    q = _seeded(T, heads * (nope + rope), seed=20, dtype=BF)
+    kvb = _seeded(T, heads * (nope + dv), seed=21, dtype=BF)
+    ckv = _seeded(T, 96 + rope, seed=22, dtype=BF)          # k_rot is a column slice of a wider tensor
+    pos = torch.tensor([0, 1, 2, 3, 17, 100, 1023, 2047, 4095, 8191, 5])
+    slots = torch.randperm(blocks * page, generator=torch.Generator().manual_seed(5))[:T].to(torch.int32)
+    slots[4] = -1
+    cos, sin, inv_freq = ops.rope_cos_sin(pos, rope, 50000.0)
+    qv = q.view(T, heads, nope + rope)
+    q_ref = torch.cat((qv[..., :nope], cpu_model.rope_interleave(qv[..., nope:].contiguous(), cos, sin)), -1)
+    kv = kvb.view(T, heads, nope + dv)
+    k_rot = cpu_model.rope_interleave(ckv[:, 96:].reshape(T, 1, rope).contiguous(), cos, sin).expand(T, heads, rope)
+    k_ref = torch.cat((kv[..., :nope], k_rot), -1).contiguous()
+    v_ref = kv[..., nope:].contiguous()
+    kc_ref = torch.zeros(blocks, page, heads, nope + rope, dtype=BF)
+    vc_ref = torch.zeros(blocks, page, heads, dv, dtype=BF)
+    ops.kv_store(k_ref, v_ref, kc_ref, vc_ref, slots)
+    qg, kvbg, ckvg = q.cuda(), kvb.cuda(), ckv.cuda()
+    krg = ckvg[:, 96:]
+    q_out = torch.empty(T, heads, nope + rope, dtype=BF).cuda()
+    kc = torch.zeros_like(kc_ref).cuda()
+    vc = torch.zeros_like(vc_ref).cuda()
+    pg, sg, fg = pos.cuda(), slots.cuda(), inv_freq.cuda()
+    _lib.check(_lib.load().b200_mla_rope_store(
+        qg.data_ptr(), qg.stride(0), kvbg.data_ptr(), kvbg.stride(0), krg.data_ptr(), krg.stride(0), pg.data_ptr(),
+        sg.data_ptr(), fg.data_ptr(), q_out.data_ptr(), kc.data_ptr(), vc.data_ptr(), T, heads, nope, rope, dv,
+        blocks * page, _lib.current_stream()), "b200_mla_rope_store")
+    assert torch.equal(vc.cpu(), vc_ref)
+    assert torch.equal(q_out.cpu()[..., :nope], q_ref[..., :nope]) and torch.equal(kc.cpu()[..., :nope], kc_ref[..., :nope])
+    for got, want in ((q_out.cpu(), q_ref), (kc.cpu(), kc_ref)):
+        torch.testing.assert_close(got.float(), want.float(), rtol=2 ** -6, atol=5e-2)
+        assert (got == want).float().mean() > 0.99
+
+
 def test_status_word_clean(vb):
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0

@@ -153,3 +153,43 @@ def test_pp_indices_exact():
 def test_slot_mapping_formula():
     slots = ops.slot_mapping([[3, 1], [2]], [14, 0], [4, 2], 16)
     assert slots.tolist() == [3 * 16 + 14, 3 * 16 + 15, 16, 17, 32, 33]
+
+
+def test_mla_projection_and_rope_match_hf_deepseek_modules():
+    """The oracle's MLA q/k/v (the restatement of modeling_deepseek_v3.py:234-261) equals the HF
+    DeepseekV3 modules and helpers that the reference's forward calls, bit for bit."""
+    from transformers import DeepseekV3Config
+    from transformers.models.deepseek_v3 import modeling_deepseek_v3 as m
+
+    from oracle import cpu_model
+    from vexact_b200.inferencer import MLAShape, ModelShape
+
+    torch.manual_seed(0)
+    cfg = DeepseekV3Config(hidden_size=256, num_attention_heads=2, num_key_value_heads=2, kv_lora_rank=64,
+                           q_lora_rank=None, qk_nope_head_dim=32, qk_rope_head_dim=64, v_head_dim=32,
+                           num_hidden_layers=1, intermediate_size=128, moe_intermediate_size=64, n_routed_experts=8,
+                           num_experts_per_tok=2, n_shared_experts=1, n_group=1, topk_group=1, vocab_size=64,
+                           rope_theta=50000.0, first_k_dense_replace=1, rope_interleave=True)
+    att = m.DeepseekV3Attention(cfg, 0).to(BF).eval()
+    rot = m.DeepseekV3RotaryEmbedding(cfg)
+    T = 7
+    x = torch.randn(1, T, 256).to(BF)
+    pos = torch.tensor([[0, 1, 5, 17, 100, 1000, 4095]])
+    cos, sin = rot(x, pos)
+    with torch.no_grad():
+        q = att.q_proj(x).view(1, T, -1, 96).transpose(1, 2)
+        q_pass, q_rot = torch.split(q, [32, 64], -1)
+        ckv = att.kv_a_proj_with_mqa(x)
+        k_pass, k_rot = torch.split(ckv, [64, 64], -1)
+        k_pass = att.kv_b_proj(att.kv_a_layernorm(k_pass)).view(1, T, -1, 64).transpose(1, 2)
+        k_pass, v = torch.split(k_pass, [32, 32], -1)
+        q_rot, k_rot = m.apply_rotary_pos_emb_interleave(q_rot, k_rot.view(1, 1, T, 64), cos, sin)
+        Q = torch.cat((q_pass, q_rot), -1)
+        K = torch.cat((k_pass, k_rot.expand(*k_pass.shape[:-1], -1)), -1)
+    shape = ModelShape("t", 1, 256, 2, 2, 96, 64, mla=MLAShape(64, 32, 64, 32), rope_theta=50000.0,
+                       rms_eps=cfg.rms_norm_eps, norm_single_round=True)
+    lw = dict(qkv=att.q_proj.weight.data, kv_a=att.kv_a_proj_with_mqa.weight.data,
+              kv_a_norm=att.kv_a_layernorm.weight.data, kv_b=att.kv_b_proj.weight.data)
+    q2, k2, v2 = cpu_model.mla_qkv(shape, lw, x[0], pos[0])
+    assert torch.equal(q2, Q[0].transpose(0, 1)) and torch.equal(k2, K[0].transpose(0, 1))
+    assert torch.equal(v2, v[0].transpose(0, 1))

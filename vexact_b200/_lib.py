@@ -29,6 +29,7 @@ SIGNATURES = {
     "b200_gather_logprob": [P, P, P, LL, I, LL, I, LL, P],
     "b200_kv_store": [P, P, P, P, P, LL, I, I, I, LL, LL, LL, P],
     "b200_qknorm_rope_store": [P, LL, P, P, P, P, P, P, P, P, LL, I, I, I, LL, F, P],
+    "b200_mla_rope_store": [P, LL, P, LL, P, LL, P, P, P, P, P, P, LL, I, I, I, I, LL, P],
     "b200_paged_attn_fwd": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL,
                             LL, LL, F, P],
     "b200_moe_route_softmax_topk": [P, I, LL, P, P, P, P, LL, I, I, I, P],

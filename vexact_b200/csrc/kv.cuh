@@ -133,6 +133,76 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
   }
 }
 
+// Multi-head latent attention (DeepSeek-V3 / Moonlight): what deepseek_v3_attention_forward
+// (vexact/models/deepseek_v3/modeling_deepseek_v3.py:225-283) does between its projections and the
+// attention call.  One warp per (token, head):
+//   q  [T, heads, nope + rope]  : nope part copied, rope part rotated        -> q_out [T, heads, nope + rope]
+//   kvb[T, heads, nope + dv]    : k_nope | value (output of kv_b_proj)
+//   kr [T, rope]                : the shared rotary key (last columns of kv_a_proj_with_mqa)
+//   K cache row = cat(k_nope[h], rot(kr)) (the rotated shared key is repeated for every head, as the
+//   reference's k_rot.expand does), V cache row = value[h].
+// Rotary embedding is HF's apply_rotary_pos_emb_interleave: pairs (x[2j], x[2j+1]) are first
+// de-interleaved to (first half, second half), then rotate_half is applied with bf16 cos/sin and bf16
+// products, and the result stays in the de-interleaved order.  rope dim is 64: lane j owns pair j.
+__global__ void __launch_bounds__(256)
+mla_rope_store_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride,
+                      const __nv_bfloat16* __restrict__ kvb, long long kvb_stride,
+                      const __nv_bfloat16* __restrict__ kr, long long kr_stride,
+                      const long long* __restrict__ positions, const int* __restrict__ slot_mapping,
+                      const float* __restrict__ inv_freq, __nv_bfloat16* __restrict__ q_out,
+                      __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int heads,
+                      int nope, int dv, long long num_tokens, long long num_slots) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int ROPE = 64;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (wid >= num_tokens * heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long tok = wid / heads;
+  const int head = (int)(wid % heads);
+  const int dq = nope + ROPE;
+  const float pos = (float)positions[tok];
+  const float ang = pos * inv_freq[lane];
+  const float c = round_bf(cosf(ang)), sn = round_bf(sinf(ang));
+  auto rotate = [&](uint32_t pair, float& first, float& second) {
+    float xe, xo;  // x[2j], x[2j+1]
+    unpack_bf2(pair, xe, xo);
+    first = round_bf(round_bf(xe * c) + round_bf(-xo * sn));   // (q*cos) + (rotate_half(q)*sin), first half
+    second = round_bf(round_bf(xo * c) + round_bf(xe * sn));   // second half
+  };
+  // ---- query
+  const __nv_bfloat16* qs = q + tok * q_stride + (long long)head * dq;
+  __nv_bfloat16* qd = q_out + (tok * heads + head) * dq;
+  for (int i = lane; i < (nope >> 1); i += 32)
+    reinterpret_cast<uint32_t*>(qd)[i] = reinterpret_cast<const uint32_t*>(qs)[i];
+  {
+    float f, s2;
+    rotate(reinterpret_cast<const uint32_t*>(qs + nope)[lane], f, s2);
+    qd[nope + lane] = f2bf(f);
+    qd[nope + 32 + lane] = f2bf(s2);
+  }
+  // ---- key / value into the paged caches
+  const long long slot = slot_mapping[tok];
+  if (slot < 0) return;
+  if (slot >= num_slots) {
+    if (lane == 0) report_status(B200_STATUS_BAD_INDEX, (int)slot);
+    return;
+  }
+  const __nv_bfloat16* ks = kvb + tok * kvb_stride + (long long)head * (nope + dv);
+  __nv_bfloat16* kd = k_cache + (slot * heads + head) * dq;
+  __nv_bfloat16* vd = v_cache + (slot * heads + head) * dv;
+  for (int i = lane; i < (nope >> 1); i += 32)
+    reinterpret_cast<uint32_t*>(kd)[i] = reinterpret_cast<const uint32_t*>(ks)[i];
+  for (int i = lane; i < (dv >> 1); i += 32)
+    reinterpret_cast<uint32_t*>(vd)[i] = reinterpret_cast<const uint32_t*>(ks + nope)[i];
+  {
+    float f, s2;
+    rotate(reinterpret_cast<const uint32_t*>(kr + tok * kr_stride)[lane], f, s2);
+    kd[nope + lane] = f2bf(f);
+    kd[nope + 32 + lane] = f2bf(s2);
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_kv_store(const void* key, const void* value, void* k_cache, void* v_cache,
@@ -171,5 +241,29 @@ extern "C" int b200_qknorm_rope_store(const void* qkv, long long qkv_token_strid
       (const __nv_bfloat16*)q_norm_weight, (const __nv_bfloat16*)k_norm_weight, (const float*)inv_freq,
       (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_q_heads, num_kv_heads,
       num_tokens, num_slots, eps);
+  return launch_status();
+}
+
+extern "C" int b200_mla_rope_store(const void* q, long long q_token_stride, const void* kvb,
+                                   long long kvb_token_stride, const void* k_rot, long long k_rot_token_stride,
+                                   const void* positions, const void* slot_mapping, const void* inv_freq,
+                                   void* q_out, void* k_cache, void* v_cache, long long num_tokens, int num_heads,
+                                   int qk_nope_dim, int qk_rope_dim, int v_dim, long long num_slots,
+                                   void* stream) {
+  using namespace b200;
+  if (!q || !kvb || !k_rot || !positions || !slot_mapping || !inv_freq || !q_out || !k_cache || !v_cache ||
+      num_tokens < 0 || num_heads <= 0)
+    return B200_ERR_ARG;
+  if (qk_rope_dim != 64 || qk_nope_dim % 2 || v_dim % 2 || qk_nope_dim <= 0 || v_dim <= 0) return B200_ERR_SHAPE;
+  if (q_token_stride % 2 || kvb_token_stride % 2 || k_rot_token_stride % 2 ||
+      ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kvb) | reinterpret_cast<uintptr_t>(k_rot)) & 3))
+    return B200_ERR_ARG;
+  if (num_tokens == 0) return B200_OK;
+  const long long warps = num_tokens * num_heads;
+  launch_k(mla_rope_store_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+           (const __nv_bfloat16*)q, q_token_stride, (const __nv_bfloat16*)kvb, kvb_token_stride,
+           (const __nv_bfloat16*)k_rot, k_rot_token_stride, (const long long*)positions,
+           (const int*)slot_mapping, (const float*)inv_freq, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+           (__nv_bfloat16*)v_cache, num_heads, qk_nope_dim, v_dim, num_tokens, num_slots);
   return launch_status();
 }

@@ -22,8 +22,9 @@ import torch
 
 from . import _lib
 from .attention import paged_attention
-from .batch_invariant_ops import add_rms_norm, hf_rms_norm, linear
-from .fused_moe import TILE_ROWS, _grouped_gemm, fused_moe_forward, route_softmax_topk
+from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
+from .fused_moe import (TILE_ROWS, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
+                        route_softmax_topk)
 from .standalone_logprobs import logprobs_from_logits_flash_attn
 
 BF = torch.bfloat16
@@ -35,6 +36,22 @@ class MoEShape:
     top_k: int
     intermediate: int
     norm_topk_prob: bool = True
+    # DeepSeek-V3 style routing (modeling_deepseek_v3.py:185-208) when scoring == "sigmoid_group"
+    scoring: str = "softmax"
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    n_shared_experts: int = 0
+
+
+@dataclass(frozen=True)
+class MLAShape:
+    """Multi-head latent attention dims (DeepSeek-V3 / Moonlight), q_lora_rank = None."""
+
+    kv_lora_rank: int = 512
+    qk_nope: int = 128
+    qk_rope: int = 64
+    v_head: int = 128
 
 
 @dataclass(frozen=True)
@@ -54,16 +71,36 @@ class ModelShape:
     qkv_bias: bool = False
     rope_theta: float = 1e6
     rms_eps: float = 1e-6
+    mla: Optional[MLAShape] = None
+    first_k_dense: int = 0            # leading layers with a dense FFN in an MoE model
+    norm_single_round: bool = False   # DeepSeek-V3: every RMSNorm is batch_invariant_rms_norm
 
     @property
     def qkv_out(self) -> int:
         return (self.num_q_heads + 2 * self.num_kv_heads) * self.head_dim
 
+    @property
+    def k_dim(self) -> int:
+        return self.mla.qk_nope + self.mla.qk_rope if self.mla else self.head_dim
+
+    @property
+    def v_dim(self) -> int:
+        return self.mla.v_head if self.mla else self.head_dim
+
+    def layer_is_moe(self, layer_idx: int) -> bool:
+        return self.moe is not None and layer_idx >= self.first_k_dense
+
 
 QWEN3_1P7B = ModelShape("qwen3-1.7b-shape", 28, 2048, 16, 8, 128, 151936, ffn=6144)
 QWEN2_1P5B = ModelShape("qwen2-1.5b-shape", 28, 1536, 12, 2, 128, 151936, ffn=8960, qk_norm=False, qkv_bias=True)
 QWEN3_30B_A3B = ModelShape("qwen3-30b-a3b-shape", 48, 2048, 32, 4, 128, 151936, moe=MoEShape(128, 8, 768))
-PRESETS = {m.name: m for m in (QWEN3_1P7B, QWEN2_1P5B, QWEN3_30B_A3B)}
+# Moonlight-16B-A3B (DeepSeek-V3 architecture).  n_group / topk_group / scaling are not fixed by the
+# benchmark description: 1 / 1 / 2.446 (Moonlight's published config) are used.
+MOONLIGHT_16B_A3B = ModelShape(
+    "moonlight-16b-a3b-shape", 27, 2048, 16, 16, 192, 163840, ffn=11264, qk_norm=False, rope_theta=50000.0,
+    rms_eps=1e-5, mla=MLAShape(), first_k_dense=1, norm_single_round=True,
+    moe=MoEShape(64, 6, 1408, True, "sigmoid_group", 1, 1, 2.446, 2))
+PRESETS = {m.name: m for m in (QWEN3_1P7B, QWEN2_1P5B, QWEN3_30B_A3B, MOONLIGHT_16B_A3B)}
 
 
 def get_pp_indices(num_hidden_layers: int, pp_rank: int, pp_size: int) -> tuple[int, int]:
@@ -97,6 +134,12 @@ class LayerWeights:
     router: Optional[torch.Tensor] = None    # moe: [E, hidden]
     experts_gate_up: Optional[torch.Tensor] = None  # moe: [E, 2I, hidden]
     experts_down: Optional[torch.Tensor] = None     # moe: [E, hidden, I]
+    router_bias: Optional[torch.Tensor] = None      # DeepSeek-V3 e_score_correction_bias [E] fp32
+    shared_gate_up: Optional[torch.Tensor] = None   # shared experts: [2 * I * n_shared, hidden]
+    shared_down: Optional[torch.Tensor] = None      # [hidden, I * n_shared]
+    kv_a: Optional[torch.Tensor] = None             # MLA: kv_a_proj_with_mqa [kv_lora + rope, hidden]
+    kv_a_norm: Optional[torch.Tensor] = None        # MLA: [kv_lora]
+    kv_b: Optional[torch.Tensor] = None             # MLA: [heads * (nope + v), kv_lora]
 
 
 @dataclass
@@ -125,21 +168,42 @@ class StageWeights:
             return t
 
         H, D = shape.hidden, shape.head_dim
-        for _ in range(start, end):
-            lw = LayerWeights(
-                input_norm=norm_w(H),
-                qkv=_randn((shape.qkv_out, H), std, device, gen),
-                qkv_bias=_randn((shape.qkv_out,), std, device, gen) if shape.qkv_bias else None,
-                q_norm=norm_w(D) if shape.qk_norm else None,
-                k_norm=norm_w(D) if shape.qk_norm else None,
-                o=_randn((H, shape.num_q_heads * D), std, device, gen),
-                post_norm=norm_w(H),
-            )
-            if shape.moe is not None:
+        for li in range(start, end):
+            if shape.mla is not None:
+                a = shape.mla
+                lw = LayerWeights(
+                    input_norm=norm_w(H),
+                    qkv=_randn((shape.num_q_heads * (a.qk_nope + a.qk_rope), H), std, device, gen),  # q_proj
+                    qkv_bias=None, q_norm=None, k_norm=None,
+                    o=_randn((H, shape.num_q_heads * a.v_head), std, device, gen),
+                    post_norm=norm_w(H),
+                    kv_a=_randn((a.kv_lora_rank + a.qk_rope, H), std, device, gen),
+                    kv_a_norm=norm_w(a.kv_lora_rank),
+                    kv_b=_randn((shape.num_q_heads * (a.qk_nope + a.v_head), a.kv_lora_rank), std, device, gen),
+                )
+            else:
+                lw = LayerWeights(
+                    input_norm=norm_w(H),
+                    qkv=_randn((shape.qkv_out, H), std, device, gen),
+                    qkv_bias=_randn((shape.qkv_out,), std, device, gen) if shape.qkv_bias else None,
+                    q_norm=norm_w(D) if shape.qk_norm else None,
+                    k_norm=norm_w(D) if shape.qk_norm else None,
+                    o=_randn((H, shape.num_q_heads * D), std, device, gen),
+                    post_norm=norm_w(H),
+                )
+            if shape.layer_is_moe(li):
                 m = shape.moe
                 lw.router = _randn((m.num_experts, H), std, device, gen)
                 lw.experts_gate_up = _randn((m.num_experts, 2 * m.intermediate, H), std, device, gen)
                 lw.experts_down = _randn((m.num_experts, H, m.intermediate), std, device, gen)
+                if m.scoring == "sigmoid_group":
+                    lw.router_bias = torch.zeros(m.num_experts, device=device, dtype=torch.float32)
+                    if norm_jitter:
+                        lw.router_bias.normal_(0.0, norm_jitter, generator=gen)
+                if m.n_shared_experts:
+                    si = m.intermediate * m.n_shared_experts
+                    lw.shared_gate_up = _randn((2 * si, H), std, device, gen)
+                    lw.shared_down = _randn((H, si), std, device, gen)
             else:
                 lw.gate_up = _randn((2 * shape.ffn, H), std, device, gen)
                 lw.down = _randn((H, shape.ffn), std, device, gen)
@@ -149,7 +213,8 @@ class StageWeights:
         if pp_rank == pp_size - 1:
             w.final_norm = norm_w(H)
             w.lm_head = _randn((shape.vocab, H), std, device, gen)
-        w.inv_freq = (1.0 / (shape.rope_theta ** (torch.arange(0, D, 2, dtype=torch.int64).float() / D))).to(device)
+        rd = shape.mla.qk_rope if shape.mla is not None else D
+        w.inv_freq = (1.0 / (shape.rope_theta ** (torch.arange(0, rd, 2, dtype=torch.int64).float() / rd))).to(device)
         return w
 
     def num_bytes(self) -> int:
@@ -207,14 +272,22 @@ class StageRunner:
 
     def prepare(self, T: int, device="cuda") -> None:
         """Build host-constructed constants for a token count (call before graph capture)."""
-        if self.shape.moe is None:
-            self._dense_plan(T, device)
+        self._dense_plan(T, device)
+
+    def _norm(self, x, w):
+        s = self.shape
+        return batch_invariant_rms_norm(x, w, s.rms_eps) if s.norm_single_round else hf_rms_norm(x, w, s.rms_eps)
+
+    def _add_norm(self, x, residual, w):
+        return add_rms_norm(x, residual, w, self.shape.rms_eps, hf=not self.shape.norm_single_round)
 
     def _attention_block(self, lw: LayerWeights, layer_idx: int, xn: torch.Tensor, inp: StepInputs) -> torch.Tensor:
         s = self.shape
         T = xn.shape[0]
-        qkv = linear(xn, lw.qkv, lw.qkv_bias)
         kc, vc = self.key_cache[layer_idx], self.value_cache[layer_idx]
+        if s.mla is not None:
+            return self._mla_block(lw, kc, vc, xn, inp)
+        qkv = linear(xn, lw.qkv, lw.qkv_bias)
         q = torch.empty((T, s.num_q_heads, s.head_dim), device=xn.device, dtype=BF)
         _lib.check(
             _lib.load().b200_qknorm_rope_store(
@@ -228,21 +301,55 @@ class StageRunner:
                                s.head_dim ** -0.5, inp.max_seqlen_q)
         return linear(attn.view(T, s.num_q_heads * s.head_dim), lw.o)
 
+    def _mla_block(self, lw: LayerWeights, kc, vc, xn: torch.Tensor, inp: StepInputs) -> torch.Tensor:
+        """deepseek_v3_attention_forward (modeling_deepseek_v3.py:225-283), q_lora_rank = None."""
+        s, a = self.shape, self.shape.mla
+        T, heads = xn.shape[0], s.num_q_heads
+        q_in = linear(xn, lw.qkv)                                   # q_proj: [T, heads * (nope + rope)]
+        ckv = linear(xn, lw.kv_a)                                   # [T, kv_lora + rope]
+        k_lat = batch_invariant_rms_norm(ckv[:, :a.kv_lora_rank], lw.kv_a_norm, s.rms_eps)
+        kvb = linear(k_lat, lw.kv_b)                                # [T, heads * (nope + v)]
+        k_rot = ckv[:, a.kv_lora_rank:]
+        q = torch.empty((T, heads, a.qk_nope + a.qk_rope), device=xn.device, dtype=BF)
+        _lib.check(
+            _lib.load().b200_mla_rope_store(
+                q_in.data_ptr(), q_in.stride(0), kvb.data_ptr(), kvb.stride(0), k_rot.data_ptr(), k_rot.stride(0),
+                inp.positions.data_ptr(), inp.slot_mapping.data_ptr(), self.w.inv_freq.data_ptr(), q.data_ptr(),
+                kc.data_ptr(), vc.data_ptr(), T, heads, a.qk_nope, a.qk_rope, a.v_head, kc.shape[0] * kc.shape[1],
+                _lib.current_stream()),
+            "b200_mla_rope_store",
+        )
+        attn = paged_attention(q, kc, vc, inp.query_start_loc, inp.context_lens, inp.block_tables,
+                               (a.qk_nope + a.qk_rope) ** -0.5, inp.max_seqlen_q)
+        return linear(attn.view(T, heads * a.v_head), lw.o)
+
+    def _dense_mlp(self, xn, gate_up, down, width):
+        plan = self._dense_plan(xn.shape[0], xn.device)
+        act = _grouped_gemm(xn, gate_up.view(1, 2 * width, self.shape.hidden), None, plan, width, mode=1)
+        return linear(act, down)
+
     def _mlp_block(self, lw: LayerWeights, xn: torch.Tensor) -> torch.Tensor:
         s = self.shape
-        if s.moe is not None:
-            m = s.moe
-            logits = linear(xn, lw.router)
-            rw, sel = route_softmax_topk(logits, m.top_k, m.norm_topk_prob)
+        if lw.router is None:
+            return self._dense_mlp(xn, lw.gate_up, lw.down, s.ffn)
+        m = s.moe
+        if m.scoring == "sigmoid_group":
+            # PatchDeepseekV3TopkRouter: F.linear in fp32, then route_tokens_to_experts; experts + shared experts
+            logits = linear(xn.float(), lw.router.float())
+            sel, rw = route_sigmoid_group_topk(logits, lw.router_bias, m.n_group, m.topk_group, m.top_k,
+                                               m.norm_topk_prob, m.routed_scaling_factor)
+            shared = None
+            if lw.shared_gate_up is not None:
+                shared = self._dense_mlp(xn, lw.shared_gate_up, lw.shared_down, m.intermediate * m.n_shared_experts)
             return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
-                                     fc1_1_2_weight=lw.experts_gate_up)
-        plan = self._dense_plan(xn.shape[0], xn.device)
-        act = _grouped_gemm(xn, lw.gate_up.view(1, 2 * s.ffn, s.hidden), None, plan, s.ffn, mode=1)
-        return linear(act, lw.down)
+                                     fc1_1_2_weight=lw.experts_gate_up, addend=shared)
+        logits = linear(xn, lw.router)
+        rw, sel = route_softmax_topk(logits, m.top_k, m.norm_topk_prob)
+        return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
+                                 fc1_1_2_weight=lw.experts_gate_up)
 
     def forward(self, inp: StepInputs) -> torch.Tensor:
         """Hidden states after the local layers ([T, H]); the residual stream is complete."""
-        s = self.shape
         if self.is_first:
             h = self.w.embed.index_select(0, inp.input_ids)
         else:
@@ -250,11 +357,11 @@ class StageRunner:
         delta = None
         for li, lw in zip(range(self.w.start_layer, self.w.end_layer), self.w.layers):
             if delta is None:
-                xn = hf_rms_norm(h, lw.input_norm, s.rms_eps)
+                xn = self._norm(h, lw.input_norm)
             else:
-                h, xn = add_rms_norm(delta, h, lw.input_norm, s.rms_eps)
+                h, xn = self._add_norm(delta, h, lw.input_norm)
             attn_out = self._attention_block(lw, li, xn, inp)
-            h, xn2 = add_rms_norm(attn_out, h, lw.post_norm, s.rms_eps)
+            h, xn2 = self._add_norm(attn_out, h, lw.post_norm)
             delta = self._mlp_block(lw, xn2)
         if delta is not None:
             h = h + delta
@@ -265,7 +372,7 @@ class StageRunner:
         s = self.shape
         last = (inp.query_start_loc[1:] - 1).to(torch.long)
         rows = h.index_select(0, last.clamp(min=0))
-        xn = hf_rms_norm(rows, self.w.final_norm, s.rms_eps)
+        xn = self._norm(rows, self.w.final_norm)
         logits = linear(xn, self.w.lm_head)
         tokens = torch.argmax(logits, dim=-1)
         logprobs = logprobs_from_logits_flash_attn(logits, tokens)
@@ -301,7 +408,8 @@ def allocate_kv_cache(shape: ModelShape, start_layer: int, end_layer: int, num_b
     gen = torch.Generator(device=device).manual_seed(seed + 17)
     for li in range(start_layer, end_layer):
         for store in (kc, vc):
-            t = torch.zeros((num_blocks, page_size, shape.num_kv_heads, shape.head_dim), device=device, dtype=BF)
+            dim = shape.k_dim if store is kc else shape.v_dim
+            t = torch.zeros((num_blocks, page_size, shape.num_kv_heads, dim), device=device, dtype=BF)
             if fill_std:
                 t.normal_(0.0, fill_std, generator=gen)
             store[li] = t
