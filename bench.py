@@ -456,7 +456,7 @@ def main():
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at exactly this shape, from the ncu
     # capture summarised in profiles/hot_kernels_ncu_full.md (2.152 GB + 5.1 MB); other shapes: null
     ncu_traffic = 2157270000 if (S, args.ctx, args.page) == (512, 2048, 16) else None
-    att = {"bound": "hbm", "kernel": "paged_attn_kernel<128,128>", "achieved": achieved, "peak": peak,
+    att = {"bound": "hbm", "kernel": "paged_attn_tc_kernel<128,128,16,3,3>", "achieved": achieved, "peak": peak,
            "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
            "frac": achieved / peak, "traffic": ncu_traffic, "algorithmic_bytes_per_launch": att_bytes,
            "ms_per_launch": att_ms}

@@ -73,6 +73,12 @@ int b200_log_softmax_f32(const void* x, void* out, long long rows, int n, long l
 int b200_gather_logprob(const void* logits, const void* labels, void* out, long long rows, int n,
                         long long row_stride, int dtype, long long ignore_index, void* stream);
 
+/* ---- vexact/inferencer/inferencer.py:393-449 _select_tokens for greedy decoding: the argmax of each
+ *      row of logits (lowest index on ties) and that token's log-probability (the value
+ *      logprobs_from_logits_flash_attn returns for it), in one pass.  tokens int64, logprobs fp32. */
+int b200_greedy_logprob(const void* logits, void* tokens_i64, void* logprobs_f32, long long rows, int n,
+                        long long row_stride, int dtype, void* stream);
+
 /* ---- vexact/batch_invariant_ops/kv_cache_context.py:294 store_kvcache.
  * key [T, heads, dk], value [T, heads, dv] (token strides given, heads*dim contiguous);
  * caches [blocks, page, heads, d] contiguous; slot_mapping int32 [T], -1 = skip.

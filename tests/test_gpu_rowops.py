@@ -105,6 +105,21 @@ def test_gather_logprob(vb, dtype):
     assert vb.logprobs_from_logits_flash_attn(xg, lg2)[3].item() == 0.0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_greedy_token_and_logprob(vb, dtype):
+    from vexact_b200.standalone_logprobs import greedy_token_and_logprob
+
+    x = _seeded(40, 151936, seed=30, std=2.0).to(dtype)
+    x[3, 100] = x[3, 70000] = x[3].max() + 1        # a tie: the lower index wins, as torch.argmax
+    xg = x.cuda()
+    tok, lp = greedy_token_and_logprob(xg)
+    assert torch.equal(tok.cpu(), torch.argmax(x.float(), dim=-1)) and tok[3].item() == 100
+    assert torch.equal(lp, vb.logprobs_from_logits_flash_attn(xg, tok))      # same bits as the two-kernel path
+    torch.testing.assert_close(lp.cpu(), ops.gather_logprob(x, tok.cpu()), rtol=0, atol=2e-5)
+    t1, l1 = greedy_token_and_logprob(xg[5:6])
+    assert torch.equal(t1, tok[5:6]) and torch.equal(l1, lp[5:6])
+
+
 def test_kv_store_golden_exact(vb):
     c = load_golden("kv_store")
     kc = torch.zeros_like(c["k_cache"]).cuda()

@@ -55,6 +55,8 @@ struct AttnParams {
   int head_chunks;   // ceil(group / 8)
   float qk_scale;    // softmax_scale * log2(e)
   int num_blocks;    // cache blocks
+  // tcgen05 kernel (persistent CTAs): tile grid dims and total
+  int tc_q_tiles, tc_hy, tc_tiles;
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -371,6 +373,19 @@ inline int attn_launch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnP
   return launch_status();
 }
 
+// Which attention kernel runs: the tcgen05 kernel (attn_tc.cuh) for the head dims it covers, unless
+// B200_ATTN=simt asks for this file's mma.sync kernel (kept as the fallback for other head dims and as
+// a cross-check).  The choice never depends on the batch.
+inline bool attn_use_tensor_memory() {
+  static const bool on = []() {
+    const char* v = getenv("B200_ATTN");
+    return !(v && v[0] == 's');
+  }();
+  return on;
+}
+int attn_tc_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid, int dk, int nc,
+                     cudaStream_t st);
+
 }  // namespace b200
 
 // Causal attention of packed queries against a paged KV cache.
@@ -429,10 +444,24 @@ extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const voi
   rc = make_tmap_cache(&tv, v_cache, num_blocks, page_size, num_kv_heads, dv, vc_block_stride, vc_page_stride,
                        vc_head_stride, p.box_tokens);
   if (rc) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (num_seqs > 65535 || num_kv_heads * p.head_chunks > 65535) return B200_ERR_SHAPE;
+  const int hh = group < 8 ? group : 8;
+  if (attn_use_tensor_memory() && dv == 128 && (dk == 128 || dk == 192) && q_tok_stride % 8 == 0 &&
+      q_head_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
+    // tcgen05 kernel: NC columns per CTA; a decode step (one query per sequence) uses the narrow tile
+    const int nc = max_seqlen_q == 1 ? 16 : (dk == 128 ? 64 : 32);
+    p.pos_per_tile = nc / hh;
+    dim3 grid((unsigned)((max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile),
+              (unsigned)(num_kv_heads * p.head_chunks), (unsigned)num_seqs);
+    p.tc_q_tiles = (int)grid.x;
+    p.tc_hy = (int)grid.y;
+    if ((long long)grid.x * grid.y * grid.z > 0x7fffffffll) return B200_ERR_SHAPE;
+    p.tc_tiles = (int)(grid.x * grid.y * grid.z);
+    return attn_tc_dispatch(tk, tv, p, grid, dk, nc, st);
+  }
   const int q_tiles = (max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile;
   dim3 grid((unsigned)q_tiles, (unsigned)(num_kv_heads * p.head_chunks), (unsigned)num_seqs);
-  if (num_seqs > 65535 || grid.y > 65535) return B200_ERR_SHAPE;
-  cudaStream_t st = (cudaStream_t)stream;
   if (dk == 128 && dv == 128) return attn_launch<128, 128, 3>(tk, tv, p, grid, st);
   if (dk == 192 && dv == 128) return attn_launch<192, 128, 2>(tk, tv, p, grid, st);
   if (dk == 64 && dv == 64) return attn_launch<64, 64, 3>(tk, tv, p, grid, st);

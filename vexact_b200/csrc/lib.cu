@@ -5,6 +5,7 @@
 #include "kv.cuh"
 #include "gemm.cuh"
 #include "attn.cuh"
+#include "attn_tc.cuh"
 #include "moe.cuh"
 #include "noalloc.cuh"
 

@@ -176,6 +176,45 @@ gather_logprob_kernel(const T* __restrict__ x, const long long* __restrict__ lab
   }
 }
 
+// Greedy token and its log-probability in one pass over a row of logits: argmax (lowest index on
+// ties, as torch.argmax) and logprob = max - logsumexp = -log(sum exp(x - max)).  Replaces the
+// torch.argmax + cross-entropy pair of Inferencer._select_tokens (inferencer.py:393-449) for greedy
+// decoding; the log-probability has the same bits as gather_logprob_kernel given the same label.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+greedy_logprob_kernel(const T* __restrict__ x, long long* __restrict__ tokens, float* __restrict__ logprobs,
+                      int n, long long x_stride, bool vec) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float sm[32], ss[32];
+  __shared__ int si[32];
+  const T* row = x + (long long)blockIdx.x * x_stride;
+  const MaxSum r = row_max_sum<T>(row, n, vec, sm, ss);
+  // second pass (L2-resident row): lowest index holding the maximum
+  int best = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x)
+    if ((float)row[i] == r.m) {
+      best = i;
+      break;
+    }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+  __syncthreads();
+  if (lane == 0) si[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    int b = lane < (int)(blockDim.x >> 5) ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) b = min(b, __shfl_xor_sync(0xffffffffu, b, o));
+    if (lane == 0) {
+      tokens[blockIdx.x] = b;
+      const float lse = logf(r.s) + r.m;
+      logprobs[blockIdx.x] = (float)row[b] - lse;
+    }
+  }
+}
+
 }  // namespace b200
 
 extern "C" int b200_log_softmax_f32(const void* x, void* out, long long rows, int n, long long x_row_stride,
@@ -209,5 +248,24 @@ extern "C" int b200_gather_logprob(const void* logits, const void* labels, void*
   } else {
     return B200_ERR_ARG;
   }
+  return launch_status();
+}
+
+extern "C" int b200_greedy_logprob(const void* logits, void* tokens_i64, void* logprobs_f32, long long rows, int n,
+                                   long long row_stride, int dtype /*0 = f32, 1 = bf16*/, void* stream) {
+  using namespace b200;
+  if (!logits || !tokens_i64 || !logprobs_f32 || rows < 0 || n <= 0) return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  if (dtype == 0)
+    launch_k(greedy_logprob_kernel<float>, dim3((unsigned)rows), dim3(1024), 0, st, (const float*)logits,
+             (long long*)tokens_i64, (float*)logprobs_f32, n, row_stride, aligned && row_stride % 4 == 0);
+  else if (dtype == 1)
+    launch_k(greedy_logprob_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(1024), 0, st,
+             (const __nv_bfloat16*)logits, (long long*)tokens_i64, (float*)logprobs_f32, n, row_stride,
+             aligned && row_stride % 8 == 0);
+  else
+    return B200_ERR_ARG;
   return launch_status();
 }

@@ -25,7 +25,7 @@ from .attention import paged_attention
 from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
 from .fused_moe import (TILE_ROWS, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
                         route_softmax_topk)
-from .standalone_logprobs import logprobs_from_logits_flash_attn
+from .standalone_logprobs import greedy_token_and_logprob
 
 BF = torch.bfloat16
 
@@ -374,8 +374,7 @@ class StageRunner:
         rows = h.index_select(0, last.clamp(min=0))
         xn = self._norm(rows, self.w.final_norm)
         logits = linear(xn, self.w.lm_head)
-        tokens = torch.argmax(logits, dim=-1)
-        logprobs = logprobs_from_logits_flash_attn(logits, tokens)
+        tokens, logprobs = greedy_token_and_logprob(logits)
         return tokens, logprobs, logits
 
     def step(self, inp: StepInputs):

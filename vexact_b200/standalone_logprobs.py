@@ -35,3 +35,26 @@ def logprobs_from_logits_flash_attn(logits: torch.Tensor, labels: torch.Tensor,
         "b200_gather_logprob",
     )
     return out.reshape(batch_shape)
+
+
+def greedy_token_and_logprob(logits: torch.Tensor):
+    """(argmax token ids int64, their log-probabilities fp32) per row, one kernel, one pass.
+
+    Same values as `torch.argmax(logits, -1)` followed by `logprobs_from_logits_flash_attn`.
+    """
+    if not logits.is_cuda:
+        raise ValueError("logits must be a CUDA tensor")
+    if logits.dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError(f"logits dtype {logits.dtype} is not supported")
+    vocab = logits.shape[-1]
+    x = logits.reshape(-1, vocab)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    tokens = torch.empty((x.shape[0],), device=logits.device, dtype=torch.int64)
+    lp = torch.empty((x.shape[0],), device=logits.device, dtype=torch.float32)
+    _lib.check(
+        _lib.load().b200_greedy_logprob(x.data_ptr(), tokens.data_ptr(), lp.data_ptr(), x.shape[0], vocab, x.stride(0),
+                                        0 if x.dtype == torch.float32 else 1, _lib.current_stream()),
+        "b200_greedy_logprob",
+    )
+    return tokens.reshape(logits.shape[:-1]), lp.reshape(logits.shape[:-1])
