@@ -50,6 +50,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quick", action="store_true", help="device-timed run only (for profiler captures)")
+    ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
+                    help="side measurement: time one causal prefill attention call of QLEN queries on the "
+                         "model's head shape (context --ctx if larger) and print its own JSON line")
     return ap.parse_args()
 
 
@@ -230,6 +233,40 @@ def build_inputs(args, shape, seed, device):
     return host, dev, S * pages
 
 
+def run_prefill_attention(args, shape):
+    """Side measurement (not the contract line): one sequence's causal prefill through paged attention."""
+    import vexact_b200 as vb
+
+    dev = torch.device("cuda", 0)
+    hq, hkv, d, page = shape.num_q_heads, shape.num_kv_heads, shape.head_dim, args.page
+    qlen = args.prefill_attention
+    kvlen = max(qlen, args.ctx if args.ctx > qlen else qlen)
+    pages = (kvlen + page - 1) // page
+    g = torch.Generator(device=dev).manual_seed(0)
+    k_cache = torch.randn(pages + 1, page, hkv, d, device=dev, generator=g).bfloat16()
+    v_cache = torch.randn(pages + 1, page, hkv, d, device=dev, generator=g).bfloat16()
+    table = torch.randperm(pages, device=dev, generator=g).view(1, pages).int()
+    q = torch.randn(qlen, hq, d, device=dev, generator=g).bfloat16()
+    cu = torch.tensor([0, qlen], dtype=torch.int32, device=dev)
+    used = torch.tensor([kvlen], dtype=torch.int32, device=dev)
+    call = lambda: vb.paged_attention(q, k_cache, v_cache, cu, used, table, d ** -0.5, qlen)
+    for _ in range(max(args.warmup, 1)):
+        call()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(max(args.steps, 1)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    keys = sum(range(kvlen - qlen + 1, kvlen + 1))          # causal (query, key) pairs
+    flops = 2.0 * keys * hq * 2 * d                          # QK^T and PV
+    print(json.dumps({"measurement": "prefill_attention", "queries": qlen, "context": kvlen, "heads": hq,
+                      "kv_heads": hkv, "head_dim": d, "ms": best, "tflops": flops / best / 1e9}))
+
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -243,6 +280,9 @@ def main():
         shape = ModelShape(**{**shape.__dict__, "num_layers": args.layers})
     if args.impl == "reference":
         run_reference(args, shape, rank)
+        return
+    if args.prefill_attention:
+        run_prefill_attention(args, shape)
         return
 
     import torch.distributed as dist
