@@ -13,7 +13,9 @@ flight (one per stage), hidden states handed over with NCCL send/recv: per-GPU w
 fixed, so scaling is "weak" and a step advances all N in-flight batches by one token.
 
 Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in HBM;
-`e2e` copies each step's inputs from pinned host memory and reads tokens/logprobs back.
+`e2e` uploads each step's per-request counters from pinned host memory, builds the step's input
+buffers from them on the device (b200_prepare_step; block tables and the previous step's tokens
+stay in HBM) and reads tokens/logprobs back.
 """
 from __future__ import annotations
 
@@ -290,6 +292,7 @@ def main():
     import vexact_b200 as vb
     from vexact_b200 import _lib
     from vexact_b200.inferencer import StageRunner, StageWeights, StepInputs, allocate_kv_cache
+    from vexact_b200.step_inputs import StepBuffers
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU path for the product arm")
@@ -303,16 +306,32 @@ def main():
 
     weights = StageWeights.random_init(shape, rank, pp, device=device, seed=0)
     n_inflight = pp
-    runners, graphs, outs, dev_inputs, host_inputs, step_inputs = [], [], [], [], [], []
+    runners, graphs, outs, dev_inputs, host_inputs, step_inputs, step_bufs = [], [], [], [], [], [], []
+    computed_host, tts_host = [args.ctx] * S, [1] * S    # per-request counters of a decode step
     hidden_in = [torch.zeros((S, H), device=device, dtype=torch.bfloat16) for _ in range(n_inflight)]
     for b in range(n_inflight):
         host, dev, nblocks = build_inputs(args, shape, seed=100 + b, device=device)
         kc, vc = allocate_kv_cache(shape, weights.start_layer, weights.end_layer, nblocks, args.page, device=device,
                                    fill_std=1.0, seed=b)
         r = StageRunner(weights, kc, vc, rank, pp)
-        inp = StepInputs(input_ids=dev["input_ids"], hidden_in=hidden_in[b], positions=dev["positions"],
-                         slot_mapping=dev["slot_mapping"], query_start_loc=dev["query_start_loc"],
-                         context_lens=dev["context_lens"], block_tables=dev["block_tables"], max_seqlen_q=1)
+        if rank == 0:
+            # first stage: the step's buffers are built on the device from per-request counters
+            # (b200_prepare_step); block tables and the previous step's tokens stay in HBM
+            sb = StepBuffers(device, S, S, dev["block_tables"].shape[1], args.page)
+            sb.request_blocks.copy_(dev["block_tables"])
+            sb.last_tokens.copy_(dev["input_ids"])
+            inp = sb.prepare([args.ctx] * S, [1] * S, None, S, S)
+            inp.hidden_in = hidden_in[b]
+            for name, built in [("positions", inp.positions), ("slot_mapping", inp.slot_mapping),
+                                ("query_start_loc", inp.query_start_loc), ("context_lens", inp.context_lens),
+                                ("block_tables", inp.block_tables), ("input_ids", inp.input_ids)]:
+                if not torch.equal(built, dev[name]):
+                    raise SystemExit(f"device-built {name} differs from the host-built one")
+            step_bufs.append(sb)
+        else:
+            inp = StepInputs(input_ids=dev["input_ids"], hidden_in=hidden_in[b], positions=dev["positions"],
+                             slot_mapping=dev["slot_mapping"], query_start_loc=dev["query_start_loc"],
+                             context_lens=dev["context_lens"], block_tables=dev["block_tables"], max_seqlen_q=1)
         runners.append(r)
         host_inputs.append(host)
         dev_inputs.append(dev)
@@ -367,9 +386,10 @@ def main():
                     # a receive posted earlier would poll on the GPU all through the stages in between
                     dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
                     pending[b] = False
-                if e2e:
-                    for k, v in host_inputs[b].items():
-                        dev_inputs[b][k].copy_(v, non_blocking=True)
+                    if e2e:
+                        step_bufs[b].last_tokens.copy_(recv_tok[b])
+                if e2e:                         # counters up, one kernel builds the step's buffers
+                    step_bufs[b].prepare(computed_host, tts_host, None, S, S)
             else:
                 # posted only now: the receive kernel starts when the previous stage ends, so it does
                 # not sit on the GPU polling while that stage computes
@@ -389,6 +409,8 @@ def main():
                 if e2e:
                     tok_host.copy_(out[0], non_blocking=True)
                     lp_host.copy_(out[1], non_blocking=True)
+                    if pp == 1:
+                        step_bufs[b].last_tokens.copy_(out[0])   # next step's input ids never leave HBM
                 if pp > 1:
                     send_h[b] = dist.isend(out[0], dst=0, group=fb_group)
             if pp > 1 and rank == 0:
@@ -447,7 +469,7 @@ def main():
         return
 
     # ---- end-to-end run: pinned host inputs in, tokens + logprobs out, every step
-    h2d = sum(v.numel() * v.element_size() for v in host_inputs[0].values()) if rank == 0 else 0
+    h2d = step_bufs[0].h2d_bytes_last_step if rank == 0 else 0   # per-request counters (3 x int32 per sequence)
     d2h = (tok_host.numel() * 8 + lp_host.numel() * 4) if rank == pp - 1 else 0
 
     def e2e_step():

@@ -79,6 +79,26 @@ int b200_gather_logprob(const void* logits, const void* labels, void* out, long 
 int b200_greedy_logprob(const void* logits, void* tokens_i64, void* logprobs_f32, long long rows, int n,
                         long long row_stride, int dtype, void* stream);
 
+/* ---- vexact/inferencer/inferencer.py:193-291 Inferencer._prepare_gen_ctx and :293-349
+ *      _prepare_input_buffers_from_gen_ctx: one scheduler step's padded input buffers, built on the
+ *      device from per-request counters instead of per-token host loops.
+ * Per request i (device arrays): num_computed_tokens[i] (= context length after this step),
+ * tokens_this_step[i], row i of block_tables_in [num_seqs, max_blocks] (-1 beyond the request's
+ * blocks), prefill_offset[i] = offset of the request's first token of this step in prefill_ids
+ * (int64, packed) or -1 for a decode request, which feeds last_tokens[i] (int64, e.g. the previous
+ * step's sampled tokens, still on the device).  prefill_ids / prefill_offset / last_tokens may be NULL.
+ * Outputs (all sizes are the captured graph's): input_ids, position_ids int64 [capture_tokens]
+ * (0 beyond the step's tokens), slot_mapping int32 [capture_tokens] (-1 beyond), context_lens
+ * [graph_num_seqs] (0 for padded requests), query_start_loc [graph_num_seqs + 1] (padded entries =
+ * total tokens), block_tables_out [graph_num_seqs, max_blocks] (padded rows 0), step_info[2] =
+ * {total tokens, max tokens_this_step}.  num_seqs <= 8192.  A request whose block is missing or whose
+ * start is negative gets slot -1 and sets the status word (b200_status_read). */
+int b200_prepare_step(const int* num_computed_tokens, const int* tokens_this_step, const int* block_tables_in,
+                      const long long* prefill_ids, const int* prefill_offset, const long long* last_tokens,
+                      int num_seqs, int graph_num_seqs, int capture_tokens, int max_blocks, int page_size,
+                      long long* input_ids, long long* position_ids, int* slot_mapping, int* context_lens,
+                      int* query_start_loc, int* block_tables_out, int* step_info, void* stream);
+
 /* ---- vexact/batch_invariant_ops/kv_cache_context.py:294 store_kvcache.
  * key [T, heads, dk], value [T, heads, dv] (token strides given, heads*dim contiguous);
  * caches [blocks, page, heads, d] contiguous; slot_mapping int32 [T], -1 = skip.

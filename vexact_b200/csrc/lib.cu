@@ -8,6 +8,7 @@
 #include "attn_tc.cuh"
 #include "moe.cuh"
 #include "noalloc.cuh"
+#include "step.cuh"
 
 // Copies the device status word ({code, detail, block, spare}) to host memory and clears it.
 // Synchronises the stream: call it outside graph capture, after the work of interest.
