@@ -79,6 +79,17 @@ int b200_gather_logprob(const void* logits, const void* labels, void* out, long 
 int b200_greedy_logprob(const void* logits, void* tokens_i64, void* logprobs_f32, long long rows, int n,
                         long long row_stride, int dtype, void* stream);
 
+/* ---- vexact/inferencer/sampler.py:32-87 Sampler.batch_sample_token with uniform sampling
+ *      parameters (temperature, top-k :168-173, top-p :175-181, arg-max of probs / q :146), fused
+ *      with the chosen token's log-probability on the raw logits (inferencer.py:436-441).
+ * noise_q_f32 [rows, n]: one draw of Exp(1) per logit (torch's exponential_(), as the reference
+ * makes); NULL, temperature <= 0 or top_p <= 0 select the arg-max path (= b200_greedy_logprob).
+ * top_k <= 0 or >= n: no top-k; top_p >= 1: no top-p.  tokens int64, logprobs fp32.
+ * dtype of logits: 0 = fp32, 1 = bf16 (cast to fp32 first, as the reference does). */
+int b200_sample_token(const void* logits, const void* noise_q_f32, void* tokens_i64, void* logprobs_f32,
+                      long long rows, int n, long long row_stride, long long q_row_stride, int dtype,
+                      float temperature, int top_k, float top_p, void* stream);
+
 /* ---- vexact/inferencer/inferencer.py:193-291 Inferencer._prepare_gen_ctx and :293-349
  *      _prepare_input_buffers_from_gen_ctx: one scheduler step's padded input buffers, built on the
  *      device from per-request counters instead of per-token host loops.

@@ -9,6 +9,7 @@
 #include "moe.cuh"
 #include "noalloc.cuh"
 #include "step.cuh"
+#include "sample.cuh"
 
 // Copies the device status word ({code, detail, block, spare}) to host memory and clears it.
 // Synchronises the stream: call it outside graph capture, after the work of interest.

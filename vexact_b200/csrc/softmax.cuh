@@ -189,14 +189,36 @@ greedy_logprob_kernel(const T* __restrict__ x, long long* __restrict__ tokens, f
   __shared__ float sm[32], ss[32];
   __shared__ int si[32];
   const T* row = x + (long long)blockIdx.x * x_stride;
-  const MaxSum r = row_max_sum<T>(row, n, vec, sm, ss);
-  // second pass (L2-resident row): lowest index holding the maximum
-  int best = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x)
-    if ((float)row[i] == r.m) {
-      best = i;
-      break;
+  // One pass: the (max, sum) walk of row_max_sum, element for element, plus this thread's first
+  // index of its own maximum (a thread's indices ascend, so `>` keeps the lowest one).
+  constexpr int VEC = RowLoader<T>::VEC;
+  MaxSum acc;
+  acc.m = -INFINITY;
+  acc.s = 0.f;
+  float bm = -INFINITY;
+  int bi = 0x7fffffff;
+  const int nvec = vec ? n / VEC : 0;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float xv[VEC];
+    RowLoader<T>::load(row + (size_t)v * VEC, xv);
+    ms_push_vec<VEC>(acc, xv);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      if (xv[j] > bm) {
+        bm = xv[j];
+        bi = v * VEC + j;
+      }
+  }
+  for (int i = nvec * VEC + threadIdx.x; i < n; i += blockDim.x) {
+    const float xi = (float)row[i];
+    ms_push(acc, xi);
+    if (xi > bm) {
+      bm = xi;
+      bi = i;
     }
+  }
+  const MaxSum r = ms_block_reduce(acc, sm, ss);
+  int best = (bm == r.m) ? bi : 0x7fffffff;  // lowest index holding the row maximum
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -208,6 +230,7 @@ greedy_logprob_kernel(const T* __restrict__ x, long long* __restrict__ tokens, f
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) b = min(b, __shfl_xor_sync(0xffffffffu, b, o));
     if (lane == 0) {
+      if (b == 0x7fffffff) b = 0;  // a row without any value above -inf
       tokens[blockIdx.x] = b;
       const float lse = logf(r.s) + r.m;
       logprobs[blockIdx.x] = (float)row[b] - lse;

@@ -26,6 +26,7 @@ from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_
 from .fused_moe import (TILE_ROWS, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
                         route_softmax_topk)
 from .standalone_logprobs import greedy_token_and_logprob
+from .sampler import sample_token_and_logprob
 
 BF = torch.bfloat16
 
@@ -258,6 +259,8 @@ class StageRunner:
         self.is_last = pp_rank == pp_size - 1
         self._graphs: dict = {}
         self._dense_tiles: dict = {}
+        # None = greedy; else dict(temperature=..., top_k=..., top_p=...) applied to every request
+        self.sampling: Optional[dict] = None
 
     # -- dense MLP through the grouped-GEMM kernel's fused SwiGLU epilogue (one group)
     def _dense_plan(self, T: int, device):
@@ -374,7 +377,10 @@ class StageRunner:
         rows = h.index_select(0, last.clamp(min=0))
         xn = self._norm(rows, self.w.final_norm)
         logits = linear(xn, self.w.lm_head)
-        tokens, logprobs = greedy_token_and_logprob(logits)
+        if self.sampling is None:
+            tokens, logprobs = greedy_token_and_logprob(logits)
+        else:   # temperature / top-k / top-p sampling (reference: sampler.py:32-87), one kernel
+            tokens, logprobs = sample_token_and_logprob(logits, **self.sampling)
         return tokens, logprobs, logits
 
     def step(self, inp: StepInputs):
