@@ -372,15 +372,23 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     constexpr int NCL = NC / 2;        // columns per thread
     constexpr int CHG = 2;             // groups handled per pass (bounds the registers in flight)
     constexpr bool LOCAL_M = NC <= 16;
+    // The running maximum never goes below this, so a column whose keys are all masked so far (only
+    // possible for a query placed before the cached context) needs no -inf special cases: its
+    // probabilities and rescale factors come out as exact zeros.
+    constexpr float kMinMax = -3.0e38f;
     const int ct = threadIdx.x - 64;   // 0..255
     const int q4 = warp & 3;           // TMEM lane quadrant of this warp
     const int hsel = (warp - 2) >> 2;  // 0: even column groups, 1: odd ones
     const int tl = q4 * 32 + lane;     // TMEM lane
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     auto gcol = [&](int lg) { return (2 * lg + hsel) * 4; };  // first column of my group lg
-    // my key's 2-byte slot in row c of the P^T tile (K-major, 128-byte swizzle) is p_mine + c*128 + ((p_ch ^ (c&7)) << 4)
+    // my key's 2-byte slot in row c of the P^T tile (K-major, 128-byte swizzle) is
+    // p_mine + c*128 + ((p_ch ^ (c&7)) << 4); for column i of my group lg that is p_slot[i] + lg*1024
     uint8_t* p_mine = p_ptr + (tl >> 6) * (NC * 128) + (tl & 7) * 2;
     const int p_ch = (tl & 63) >> 3;
+    uint8_t* p_slot[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p_slot[i] = p_mine + (hsel * 4 + i) * 128 + ((p_ch ^ (hsel * 4 + i)) << 4);
     uint32_t g0 = 0;
     AtcTile t, tn;
     int lin = atc_next_tile<NC>(p, blockIdx.x, t);
@@ -474,9 +482,9 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           for (int c = ct; c < NC; c += NCT) {
             const float4 w = *reinterpret_cast<const float4*>(s_wmax[b][c]);
             const float m_old = j == 0 ? -INFINITY : s_m[b ^ 1][c];
-            const float m_new = fmaxf(m_old, fmaxf(fmaxf(w.x, w.y), fmaxf(w.z, w.w)));
+            const float m_new = fmaxf(fmaxf(m_old, kMinMax), fmaxf(fmaxf(w.x, w.y), fmaxf(w.z, w.w)));
             s_m[b][c] = m_new;
-            s_alpha[b][c] = m_new == -INFINITY ? 0.f : fast_exp2(m_old - m_new);
+            s_alpha[b][c] = fast_exp2(m_old - m_new);
           }
           ptx::named_barrier_sync(3, NCT);
           if (*abort_flag) break;
@@ -516,7 +524,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 #pragma unroll
                   for (int i = 0; i < 4; ++i) {
                     const float4 w = *reinterpret_cast<const float4*>(s_wmax[b][gc + i]);
-                    mv[k][i] = fmaxf(m_run[(ch0 + k) * 4 + i], fmaxf(fmaxf(w.x, w.y), fmaxf(w.z, w.w)));
+                    mv[k][i] = fmaxf(fmaxf(m_run[(ch0 + k) * 4 + i], kMinMax), fmaxf(fmaxf(w.x, w.y), fmaxf(w.z, w.w)));
                   }
                 } else {
                   const float4 m4 = *reinterpret_cast<const float4*>(&s_m[b][gc]);
@@ -534,14 +542,14 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                 for (int i = 0; i < 4; ++i) {
                   const int lc = (ch0 + k) * 4 + i;
                   if constexpr (LOCAL_M) {
-                    av[k][i] = mv[k][i] == -INFINITY ? 0.f : fast_exp2(m_run[lc] - mv[k][i]);
+                    av[k][i] = fast_exp2(m_run[lc] - mv[k][i]);
                     m_run[lc] = mv[k][i];
                   }
-                  const float mm = mv[k][i] == -INFINITY ? 0.f : mv[k][i];
-                  pb[k][i] = f2bf(fast_exp2(v[k][i] - mm));
+                  pb[k][i] = f2bf(fast_exp2(v[k][i] - mv[k][i]));
                   l_part[lc] = l_part[lc] * av[k][i] + bf2f(pb[k][i]);
-                  const float o_in = j > 0 ? o_acc[lc] + __uint_as_float(ro[k][i]) : o_acc[lc];
-                  o_acc[lc] = o_in * av[k][i];
+                  // (the first block finds o = 0 and no O^T yet: the product below is 0 either way)
+                  if (j > 0) o_acc[lc] += __uint_as_float(ro[k][i]);
+                  o_acc[lc] *= av[k][i];
                 }
               }
             }
@@ -551,8 +559,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
               if (gc < ncv) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                  const int c = gc + i;
-                  *reinterpret_cast<__nv_bfloat16*>(p_mine + c * 128 + ((p_ch ^ (c & 7)) << 4)) = pb[k][i];
+                  *reinterpret_cast<__nv_bfloat16*>(p_slot[i] + (ch0 + k) * 1024) = pb[k][i];
                 }
               }
             }
