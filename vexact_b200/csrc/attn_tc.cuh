@@ -403,6 +403,9 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       // rows hold only reaches O^T columns that are not stored
       const int npos = min(t.pos_per_tile, t.q_len - t.tile_pos0);
       const int ncv = npos * t.heads_here;
+      // Narrow (decode) tiles skip their padding groups; wide tiles work on them too, which keeps the
+      // column groups in one straight run of instructions (padding only occurs in a sequence's last tile).
+      auto live = [&](int gc) { return NC > 16 || gc < ncv; };
       bool go;
       for (int c = ct; c < NC; c += NCT) {
         const int pi = c / t.heads_here;
@@ -446,12 +449,12 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             uint32_t rs[CHG][4];
 #pragma unroll
             for (int k = 0; k < CHG; ++k)
-              if (gcol(ch0 + k) < ncv) ptx::tmem_ld4(tm_s0 + b * NC + lane_addr + gcol(ch0 + k), rs[k]);
+              if (live(gcol(ch0 + k))) ptx::tmem_ld4(tm_s0 + b * NC + lane_addr + gcol(ch0 + k), rs[k]);
             ptx::tmem_ld_wait();
 #pragma unroll
             for (int k = 0; k < CHG; ++k) {
               const int gc = gcol(ch0 + k);
-              if (gc < ncv) {
+              if (live(gc)) {
                 float v[4];
                 finish_scores(rs[k], gc, key, v);
                 float mine = -INFINITY;
@@ -501,19 +504,20 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 #pragma unroll
             for (int k = 0; k < CHG; ++k) {
               const int gc = gcol(ch0 + k);
-              if (gc < ncv) {
+              if (live(gc)) {
                 if constexpr (NC != 16) ptx::tmem_ld4(tm_s0 + b * NC + lane_addr + gc, rc[k]);
-                if (j > 0) ptx::tmem_ld4(tm_o + lane_addr + gc, ro[k]);
+                // (block 0 reads whatever the buffer holds and drops it below: no branch in this run)
+                ptx::tmem_ld4(tm_o + lane_addr + gc, ro[k]);
               }
             }
-            if (NC != 16 || j > 0) ptx::tmem_ld_wait();
+            ptx::tmem_ld_wait();
             // Loads first, stores last: the compiler cannot tell that the P^T stores leave the shared
             // arrays read here alone, so interleaving them would serialise the columns.
             float v[CHG][4], mv[CHG][4], av[CHG][4];
 #pragma unroll
             for (int k = 0; k < CHG; ++k) {
               const int gc = gcol(ch0 + k);
-              if (gc < ncv) {
+              if (live(gc)) {
                 if constexpr (NC == 16) {
 #pragma unroll
                   for (int i = 0; i < 4; ++i) v[k][i] = sv[(ch0 + k) * 4 + i];
@@ -537,7 +541,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
             __nv_bfloat16 pb[CHG][4];
 #pragma unroll
             for (int k = 0; k < CHG; ++k) {
-              if (gcol(ch0 + k) < ncv) {
+              if (live(gcol(ch0 + k))) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   const int lc = (ch0 + k) * 4 + i;
@@ -548,7 +552,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                   pb[k][i] = f2bf(fast_exp2(v[k][i] - mv[k][i]));
                   l_part[lc] = l_part[lc] * av[k][i] + bf2f(pb[k][i]);
                   // (the first block finds o = 0 and no O^T yet: the product below is 0 either way)
-                  if (j > 0) o_acc[lc] += __uint_as_float(ro[k][i]);
+                  o_acc[lc] += j > 0 ? __uint_as_float(ro[k][i]) : 0.f;
                   o_acc[lc] *= av[k][i];
                 }
               }
@@ -556,7 +560,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 #pragma unroll
             for (int k = 0; k < CHG; ++k) {
               const int gc = gcol(ch0 + k);
-              if (gc < ncv) {
+              if (live(gc)) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                   *reinterpret_cast<__nv_bfloat16*>(p_slot[i] + (ch0 + k) * 1024) = pb[k][i];
@@ -585,11 +589,11 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           uint32_t ro[CHG][4];
 #pragma unroll
           for (int k = 0; k < CHG; ++k)
-            if (gcol(ch0 + k) < ncv) ptx::tmem_ld4(tm_o + lane_addr + gcol(ch0 + k), ro[k]);
+            if (live(gcol(ch0 + k))) ptx::tmem_ld4(tm_o + lane_addr + gcol(ch0 + k), ro[k]);
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < CHG; ++k)
-            if (gcol(ch0 + k) < ncv) {
+            if (live(gcol(ch0 + k))) {
 #pragma unroll
               for (int i = 0; i < 4; ++i) o_acc[(ch0 + k) * 4 + i] += __uint_as_float(ro[k][i]);
             }
@@ -601,7 +605,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
 #pragma unroll
         for (int lg = 0; lg < NG; ++lg) {
           const int gc = gcol(lg);
-          if (gc < ncv) {
+          if (live(gc)) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               float v = l_part[lg * 4 + i];
