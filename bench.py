@@ -319,6 +319,8 @@ def main():
             # (b200_prepare_step); block tables and the previous step's tokens stay in HBM
             sb = StepBuffers(device, S, S, dev["block_tables"].shape[1], args.page)
             sb.request_blocks.copy_(dev["block_tables"])
+            # decode input ids come from device memory (`last_tokens`); they keep their seeded random
+            # values in every step so that the e2e leg routes tokens exactly as the device-timed leg does
             sb.last_tokens.copy_(dev["input_ids"])
             inp = sb.prepare([args.ctx] * S, [1] * S, None, S, S)
             inp.hidden_in = hidden_in[b]
@@ -366,8 +368,12 @@ def main():
     # group: every direction has its own communicator and stream, so a stage can receive the next
     # batch, send the previous one and return tokens at the same time.  All transfers are
     # asynchronous; a buffer's transfer is waited for only where the buffer is next touched.
-    tok_host = torch.empty(S, dtype=torch.int64).pin_memory()
-    lp_host = torch.empty(S, dtype=torch.float32).pin_memory()
+    # e2e results land in two pinned buffers in turn: the host reads step N's tokens while step N + 1
+    # runs (its inputs need only the requests' lengths; the token ids themselves stay on the device)
+    tok_host = [torch.empty(S, dtype=torch.int64).pin_memory() for _ in range(2)]
+    lp_host = [torch.empty(S, dtype=torch.float32).pin_memory() for _ in range(2)]
+    e2e_done = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_count = [0]
     pair_groups = [dist.new_group(ranks=[i, i + 1]) for i in range(pp - 1)] if pp > 1 else []
     fb_group = dist.new_group(ranks=list(range(pp))) if pp > 1 else None
     g_prev = pair_groups[rank - 1] if rank > 0 else None
@@ -386,8 +392,6 @@ def main():
                     # a receive posted earlier would poll on the GPU all through the stages in between
                     dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
                     pending[b] = False
-                    if e2e:
-                        step_bufs[b].last_tokens.copy_(recv_tok[b])
                 if e2e:                         # counters up, one kernel builds the step's buffers
                     step_bufs[b].prepare(computed_host, tts_host, None, S, S)
             else:
@@ -407,16 +411,17 @@ def main():
                 send_h[b] = dist.isend(out, dst=rank + 1, group=g_next)
             else:
                 if e2e:
-                    tok_host.copy_(out[0], non_blocking=True)
-                    lp_host.copy_(out[1], non_blocking=True)
-                    if pp == 1:
-                        step_bufs[b].last_tokens.copy_(out[0])   # next step's input ids never leave HBM
+                    tok_host[e2e_count[0] & 1].copy_(out[0], non_blocking=True)
+                    lp_host[e2e_count[0] & 1].copy_(out[1], non_blocking=True)
                 if pp > 1:
                     send_h[b] = dist.isend(out[0], dst=0, group=fb_group)
             if pp > 1 and rank == 0:
                 pending[b] = True               # one token message is now owed to this batch
         if e2e:
-            torch.cuda.current_stream().synchronize()
+            e2e_done[e2e_count[0] & 1].record()
+            if e2e_count[0] > 0:
+                e2e_done[(e2e_count[0] - 1) & 1].synchronize()   # the previous step's results are on the host
+            e2e_count[0] += 1
 
     def drain():
         for b in range(n_inflight):
@@ -459,7 +464,6 @@ def main():
               f"gap ms mean {sum(gaps) / max(len(gaps), 1):.3f} max {max(gaps) if gaps else 0:.3f}; "
               f"step {dev_ms / args.steps:.3f}", file=sys.stderr, flush=True)
         trace.clear()
-        trace = None
     if args.quick:
         if rank == 0:
             print(json.dumps({"quick": True, "ms_per_step": dev_ms / args.steps,
@@ -470,7 +474,7 @@ def main():
 
     # ---- end-to-end run: pinned host inputs in, tokens + logprobs out, every step
     h2d = step_bufs[0].h2d_bytes_last_step if rank == 0 else 0   # per-request counters (3 x int32 per sequence)
-    d2h = (tok_host.numel() * 8 + lp_host.numel() * 4) if rank == pp - 1 else 0
+    d2h = (tok_host[0].numel() * 8 + lp_host[0].numel() * 4) if rank == pp - 1 else 0
 
     def e2e_step():
         global_step(e2e=True)
@@ -483,6 +487,14 @@ def main():
         e2e_step()
     sync_all()
     e2e_s = time.perf_counter() - t0
+    if trace is not None:
+        tail = trace[-args.steps * n_inflight:]
+        st = [a.elapsed_time(b) for a, b in tail]
+        gaps = [tail[i][1].elapsed_time(tail[i + 1][0]) for i in range(len(tail) - 1)]
+        print(f"[trace rank {rank}, e2e] stage ms mean {sum(st) / len(st):.3f} max {max(st):.3f}; "
+              f"gap ms mean {sum(gaps) / max(len(gaps), 1):.3f} max {max(gaps) if gaps else 0:.3f}",
+              file=sys.stderr, flush=True)
+        trace = None
     clocks = sampler.stop(first_sample)
 
     # ---- dominant kernel alone (paged decode attention over every local layer's cache)
@@ -539,7 +551,7 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(args, shape), "pipeline_stages": pp, "batches_in_flight": n_inflight,
                    "l2": "inputs (weights + KV, >100 GB per GPU) far exceed L2; no flush needed",
-                   "cuda_graph": not args.no_graph},
+                   "cuda_graph": not args.no_graph, "e2e": "per step: H2D of per-request counters, device-built inputs, graph replay, D2H of tokens + logprobs; the host reads step N's results while step N+1 runs"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * n_inflight,
                 "d2h_bytes_per_step": d2h * n_inflight, "ms_per_step": e2e_ms / args.steps},

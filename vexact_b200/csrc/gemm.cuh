@@ -226,7 +226,15 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (!gemm_tile(p, t_tiles, lin, t)) break;
       const int buf = tile_it & 1;
       const bool ready = ptx::mbar_wait(tfull_bar(buf), (tile_it >> 1) & 1, abort_flag, 400 + buf);
-      if (!__all_sync(0xffffffffu, ready)) break;
+      if (SWIGLU) {
+        // The four epilogue warps meet at named barriers below, so they must leave together: a wait
+        // that gave up has raised the abort flag before its warp arrives here, and everyone reads
+        // the flag after this barrier.
+        ptx::named_barrier_sync(1, 128);
+        if (*abort_flag) break;
+      } else if (!__all_sync(0xffffffffu, ready)) {
+        break;
+      }
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.xrows_max);
       const int ncol = ((t.n + 15) / 16) * 16;
