@@ -63,6 +63,19 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
   pdl_wait();
   constexpr int D = 128;
   const int heads_total = num_q_heads + 2 * num_kv_heads;
+  // When the head count is a multiple of the 8 warps of a CTA, all of them serve one token: its 64
+  // (cos, sin) pairs are computed once into shared memory instead of once per head.
+  __shared__ float s_cos[64], s_sin[64];
+  const bool one_token = heads_total % 8 == 0;
+  if (one_token) {
+    const long long tok0 = (long long)blockIdx.x * 8 / heads_total;
+    if (threadIdx.x < 64 && tok0 < num_tokens) {
+      const float ang = (float)positions[tok0] * inv_freq[threadIdx.x];
+      s_cos[threadIdx.x] = round_bf(cosf(ang));
+      s_sin[threadIdx.x] = round_bf(sinf(ang));
+    }
+    __syncthreads();
+  }
   const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (wid >= num_tokens * heads_total) return;
   const int lane = threadIdx.x & 31;
@@ -116,9 +129,15 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int fi = (lane & 15) * 4 + j;  // frequency index in [0, 64)
-    const float ang = pos * inv_freq[fi];
-    const float c = round_bf(cosf(ang));
-    const float s = round_bf(sinf(ang));
+    float c, s;
+    if (one_token) {
+      c = s_cos[fi];
+      s = s_sin[fi];
+    } else {
+      const float ang = pos * inv_freq[fi];
+      c = round_bf(cosf(ang));
+      s = round_bf(sinf(ang));
+    }
     const float rot = upper ? partner[j] : -partner[j];  // rotate_half: cat(-x2, x1)
     y[j] = round_bf(round_bf(x[j] * c) + round_bf(rot * s));
   }
