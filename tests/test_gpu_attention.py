@@ -181,3 +181,18 @@ def test_argument_errors(vb):
 def test_status_word_clean(vb):
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+def test_mma_sync_kernel_cross_check():
+    """The mma.sync kernel (fallback for head dims the tcgen05 kernel does not cover) against the same
+    oracle, golden and bitwise cases: the kernel choice is read once per process, so a child runs it."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, B200_ATTN="simt")
+    here = os.path.abspath(__file__)
+    res = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-m", "gpu", "-x", "-k",
+                          "golden or oracle or bitwise or padding or unwritten"], env=env, capture_output=True,
+                         text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
