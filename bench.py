@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quick", action="store_true", help="device-timed run only (for profiler captures)")
+    ap.add_argument("--ragged-attention", action="store_true",
+                    help="side measurement: decode attention over a ragged batch, with / without sequence order")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
                     help="side measurement: time one causal prefill attention call of QLEN queries on the "
                          "model's head shape (context --ctx if larger) and print its own JSON line")
@@ -235,6 +237,51 @@ def build_inputs(args, shape, seed, device):
     return host, dev, S * pages
 
 
+def run_ragged_attention(args, shape):
+    """Side measurement (not the contract line): one layer's decode attention over a ragged batch
+    (context lengths uniform in [64, 2 * ctx]), with and without the longest-first sequence order."""
+    import vexact_b200 as vb
+
+    dev = torch.device("cuda", 0)
+    hq, hkv, d, page, S = shape.num_q_heads, shape.num_kv_heads, shape.head_dim, args.page, args.batch
+    g = torch.Generator().manual_seed(1)
+    lens = torch.randint(64, 2 * args.ctx + 1, (S,), generator=g)
+    pages = int((int(lens.max()) + page - 1) // page)
+    gd = torch.Generator(device=dev).manual_seed(0)
+    k_cache = torch.randn(S * pages, page, hkv, d, device=dev, generator=gd).bfloat16()
+    v_cache = torch.randn(S * pages, page, hkv, d, device=dev, generator=gd).bfloat16()
+    table = torch.randperm(S * pages, device=dev, generator=gd).view(S, pages).int()
+    q = torch.randn(S, hq, d, device=dev, generator=gd).bfloat16()
+    cu = torch.arange(S + 1, dtype=torch.int32, device=dev)
+    used = lens.to(torch.int32).to(dev)
+    order = torch.argsort(lens, descending=True, stable=True).to(torch.int32).to(dev)
+    kv_bytes = int(lens.sum()) * hkv * 2 * d * 2
+    res = {"measurement": "ragged_decode_attention", "sequences": S, "context": f"uniform 64..{2 * args.ctx}",
+           "kv_bytes": kv_bytes}
+    outs = []
+    for name, so in (("unordered", None), ("longest_first", order)):
+        call = lambda: vb.paged_attention(q, k_cache, v_cache, cu, used, table, d ** -0.5, 1, seq_order=so)
+        for _ in range(max(args.warmup, 3)):
+            outs.append(call())
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(4):
+                call()
+        gr.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(max(args.steps, 1)):
+            gr.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / (4 * max(args.steps, 1))
+        res[name] = {"ms": ms, "GBps": kv_bytes / ms / 1e6}
+    res["same_bits"] = bool(torch.equal(outs[0], outs[-1]))
+    print(json.dumps(res))
+
+
 def run_prefill_attention(args, shape):
     """Side measurement (not the contract line): one sequence's causal prefill through paged attention."""
     import vexact_b200 as vb
@@ -285,6 +332,9 @@ def main():
         return
     if args.prefill_attention:
         run_prefill_attention(args, shape)
+        return
+    if args.ragged_attention:
+        run_ragged_attention(args, shape)
         return
 
     import torch.distributed as dist

@@ -153,6 +153,20 @@ int b200_paged_attn_fwd(const void* q, const void* k_cache, const void* v_cache,
                         long long vc_block_stride, long long vc_page_stride, long long vc_head_stride,
                         float softmax_scale, void* stream);
 
+/* Same call with a processing order for ragged batches: seq_order (int32 [num_seqs], a permutation,
+ * typically sequences by descending context length; may be NULL) names the sequence each group of
+ * tiles belongs to.  The persistent tcgen05 kernel deals tiles to its CTAs round by round, so a
+ * longest-first order keeps the CTAs' totals within about one tile of each other.  Results do not
+ * depend on the order.  No counterpart in the reference (its grid is one program per head and tile). */
+int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
+                                int num_seqs, int max_seqlen_q, int num_q_heads, int num_kv_heads, int dk, int dv,
+                                int num_blocks, int page_size, int max_pages, long long page_table_stride,
+                                long long q_tok_stride, long long q_head_stride, long long o_tok_stride,
+                                long long o_head_stride, long long kc_block_stride, long long kc_page_stride,
+                                long long kc_head_stride, long long vc_block_stride, long long vc_page_stride,
+                                long long vc_head_stride, float softmax_scale, const void* seq_order, void* stream);
+
 /* ---- vexact/models/qwen3_moe/modeling_qwen3_moe.py:128-134 (softmax, top-k, renormalise, cast).
  * logits_dtype: 0 = fp32, 1 = bf16.  Any of the four outputs may be NULL except that one weight
  * and one expert output are required. */

@@ -196,3 +196,28 @@ def test_mma_sync_kernel_cross_check():
                           "golden or oracle or bitwise or padding or unwritten"], env=env, capture_output=True,
                          text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_sequence_order_changes_no_result(vb):
+    """A processing order (longest context first) only moves tiles between CTAs."""
+    g = torch.Generator().manual_seed(21)
+    S, hq, hkv, d, page = 37, 16, 4, 128, 16
+    lens = torch.randint(1, 700, (S,), generator=g)
+    qlens = torch.where(torch.rand(S, generator=g) < 0.3, torch.minimum(lens, torch.randint(1, 90, (S,), generator=g)),
+                        torch.ones(S, dtype=torch.long))
+    pages = int((int(lens.max()) + page - 1) // page)
+    kc = torch.randn(S * pages, page, hkv, d, generator=g).bfloat16().cuda()
+    vc = torch.randn(S * pages, page, hkv, d, generator=g).bfloat16().cuda()
+    table = torch.randperm(S * pages, generator=g).view(S, pages).int().cuda()
+    cu = torch.zeros(S + 1, dtype=torch.int32)
+    cu[1:] = qlens.cumsum(0)
+    q = torch.randn(int(cu[-1]), hq, d, generator=g).bfloat16().cuda()
+    cu, used = cu.cuda(), lens.int().cuda()
+    base = vb.paged_attention(q, kc, vc, cu, used, table, d ** -0.5, int(qlens.max()))
+    for order in (torch.argsort(lens, descending=True), torch.randperm(S, generator=g), torch.arange(S).flip(0)):
+        got = vb.paged_attention(q, kc, vc, cu, used, table, d ** -0.5, int(qlens.max()),
+                                 seq_order=order.int().cuda())
+        assert torch.equal(got, base)
+    with pytest.raises(ValueError):
+        vb.paged_attention(q, kc, vc, cu, used, table, d ** -0.5, int(qlens.max()),
+                           seq_order=torch.arange(S - 1).int().cuda())

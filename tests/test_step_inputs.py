@@ -132,7 +132,8 @@ def test_block_table_deltas_and_device_resident_tokens():
     assert inp.query_start_loc.tolist() == [0, 1, 2, 2]
     assert inp.context_lens.tolist() == [9, 3, 0]
     assert inp.block_tables.tolist() == [[5, 2, 9, -1, -1, -1, -1, -1], [7, -1, -1, -1, -1, -1, -1, -1], [0] * 8]
-    assert buf.h2d_bytes_last_step == 24
+    assert buf.h2d_bytes_last_step == 24 + 3 * 4
+    assert inp.seq_order.tolist() == [0, 1, 2]          # contexts 9, 3, then the padded row
     with pytest.raises(ValueError):
         buf.prepare([9, 3], [1, 1], None, graph_num_seqs=1, capture_tokens=4)
     with pytest.raises(ValueError):

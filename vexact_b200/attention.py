@@ -29,8 +29,11 @@ def _require_cuda_int32(name: str, t: torch.Tensor) -> None:
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_seqlens_q: torch.Tensor,
                     seqused_k: torch.Tensor, page_table: torch.Tensor, softmax_scale: float,
-                    max_seqlen_q: int) -> torch.Tensor:
-    """q (total_q, heads, dk) against caches (blocks, page, kv_heads, d); returns (total_q, heads, dv)."""
+                    max_seqlen_q: int, seq_order: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q (total_q, heads, dk) against caches (blocks, page, kv_heads, d); returns (total_q, heads, dv).
+
+    seq_order (int32 [num_seqs], optional): a permutation of the sequences, longest context first,
+    that balances the persistent kernel's CTAs on ragged batches; it never changes a result."""
     for name, t in (("q", q), ("k", k_cache), ("v", v_cache)):
         if not t.is_cuda:
             raise ValueError(f"{name} must be a CUDA tensor")
@@ -57,15 +60,20 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         seqused_k = seqused_k.contiguous()
     out = torch.empty((q.shape[0], q.shape[1], v_cache.shape[-1]), device=q.device, dtype=q.dtype)
     num_seqs = seqused_k.numel()
+    if seq_order is not None:
+        _require_cuda_int32("seq_order", seq_order)
+        if seq_order.numel() != num_seqs or not seq_order.is_contiguous():
+            raise ValueError("seq_order must be a contiguous permutation of the sequences")
     _lib.check(
-        _lib.load().b200_paged_attn_fwd(
+        _lib.load().b200_paged_attn_fwd_ordered(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), cu_seqlens_q.data_ptr(),
             seqused_k.data_ptr(), page_table.data_ptr(), num_seqs, int(max_seqlen_q), q.shape[1],
             k_cache.shape[2], q.shape[-1], v_cache.shape[-1], k_cache.shape[0], k_cache.shape[1],
             page_table.shape[1], page_table.stride(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1),
             k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
-            v_cache.stride(2), float(softmax_scale), _lib.current_stream()),
-        "b200_paged_attn_fwd",
+            v_cache.stride(2), float(softmax_scale), seq_order.data_ptr() if seq_order is not None else None,
+            _lib.current_stream()),
+        "b200_paged_attn_fwd_ordered",
     )
     return out
 

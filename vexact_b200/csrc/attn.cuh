@@ -57,6 +57,9 @@ struct AttnParams {
   int num_blocks;    // cache blocks
   // tcgen05 kernel (persistent CTAs): tile grid dims and total
   int tc_q_tiles, tc_hy, tc_tiles;
+  int tc_slots;          // tile positions walked: tc_tiles rounded up to whole rounds of the grid
+  int num_seqs;
+  const int* seq_order;  // [num_seqs] sequence of each slot (longest first), or null
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -395,6 +398,17 @@ int attn_tc_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnPar
 //   out [total_q, num_q_heads, dv]
 // Sequence i's queries are its last (cu[i+1] - cu[i]) positions of seqused_k[i] cached tokens.
 // max_seqlen_q bounds the per-sequence query count (it sizes the grid).
+extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
+                                           int num_seqs, int max_seqlen_q, int num_q_heads, int num_kv_heads,
+                                           int dk, int dv, int num_blocks, int page_size, int max_pages,
+                                           long long page_table_stride, long long q_tok_stride,
+                                           long long q_head_stride, long long o_tok_stride, long long o_head_stride,
+                                           long long kc_block_stride, long long kc_page_stride,
+                                           long long kc_head_stride, long long vc_block_stride,
+                                           long long vc_page_stride, long long vc_head_stride, float softmax_scale,
+                                           const void* seq_order, void* stream);
+
 extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
                                    int num_seqs, int max_seqlen_q, int num_q_heads, int num_kv_heads, int dk,
@@ -404,6 +418,26 @@ extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const voi
                                    long long kc_page_stride, long long kc_head_stride, long long vc_block_stride,
                                    long long vc_page_stride, long long vc_head_stride, float softmax_scale,
                                    void* stream) {
+  return b200_paged_attn_fwd_ordered(q, k_cache, v_cache, out, cu_seqlens_q, seqused_k, page_table, num_seqs,
+                                     max_seqlen_q, num_q_heads, num_kv_heads, dk, dv, num_blocks, page_size,
+                                     max_pages, page_table_stride, q_tok_stride, q_head_stride, o_tok_stride,
+                                     o_head_stride, kc_block_stride, kc_page_stride, kc_head_stride,
+                                     vc_block_stride, vc_page_stride, vc_head_stride, softmax_scale, nullptr, stream);
+}
+
+// Same, with an optional processing order: seq_order[i] (int32, a permutation of 0..num_seqs-1, e.g.
+// sequences by descending context length) is the sequence the i-th group of tiles belongs to.  The
+// order changes which CTA computes a sequence and when, never a result.  The mma.sync kernel ignores it.
+extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                           const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
+                                           int num_seqs, int max_seqlen_q, int num_q_heads, int num_kv_heads,
+                                           int dk, int dv, int num_blocks, int page_size, int max_pages,
+                                           long long page_table_stride, long long q_tok_stride,
+                                           long long q_head_stride, long long o_tok_stride, long long o_head_stride,
+                                           long long kc_block_stride, long long kc_page_stride,
+                                           long long kc_head_stride, long long vc_block_stride,
+                                           long long vc_page_stride, long long vc_head_stride, float softmax_scale,
+                                           const void* seq_order, void* stream) {
   using namespace b200;
   if (!q || !k_cache || !v_cache || !out || !cu_seqlens_q || !seqused_k || !page_table || num_seqs < 0 ||
       max_seqlen_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_blocks <= 0 || page_size <= 0 ||
@@ -458,6 +492,12 @@ extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const voi
     p.tc_hy = (int)grid.y;
     if ((long long)grid.x * grid.y * grid.z > 0x7fffffffll) return B200_ERR_SHAPE;
     p.tc_tiles = (int)(grid.x * grid.y * grid.z);
+    {
+      const int ctas = p.tc_tiles < sm_count() ? p.tc_tiles : sm_count();  // = the launch's grid
+      if (ctas > 0) p.tc_slots = (p.tc_tiles + ctas - 1) / ctas * ctas;
+    }
+    p.num_seqs = num_seqs;
+    p.seq_order = (const int*)seq_order;
     return attn_tc_dispatch(tk, tv, p, grid, dk, nc, st);
   }
   const int q_tiles = (max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile;

@@ -72,26 +72,46 @@ struct AtcTile {
 
 // The three words of a tile's description that live in global memory.
 struct AtcRaw {
-  int q_start, q_end, kv_len;
+  int q_start, q_end, kv_len, seq, eff;
 };
 
-// Tiles are numbered with the query tile fastest, then the KV head, then the sequence, and dealt to the
-// persistent CTAs round-robin, so the CTAs walking one sequence's pages run at the same time.
+// Tiles are numbered with the query tile fastest, then the KV head, then the sequence slot; slot i is
+// sequence seq_order[i] when the caller gives an order (longest contexts first), else sequence i.
+// The persistent CTAs take the tiles round by round, every other round in reverse ("snake"): with a
+// longest-first order the CTAs' totals then differ by about one tile however ragged the batch is.
+// Position `lin` of a CTA's walk (blockIdx.x + round * gridDim.x) maps to tile `eff`, or to none in the
+// last, partly filled round.
+__device__ __forceinline__ int atc_eff(const AttnParams& p, int lin) {
+  const int G = (int)gridDim.x;
+  const int round = lin / G, pos = lin - round * G;
+  const int eff = round * G + ((round & 1) ? G - 1 - pos : pos);
+  return eff < p.tc_tiles ? eff : -1;
+}
+
 __device__ __forceinline__ AtcRaw atc_raw(const AttnParams& p, int lin) {
-  const int seq = lin / (p.tc_q_tiles * p.tc_hy);
-  AtcRaw r;
-  r.q_start = p.cu_seqlens_q[seq];
-  r.q_end = p.cu_seqlens_q[seq + 1];
-  r.kv_len = p.seqused_k[seq];
+  AtcRaw r = {0, 0, 0, 0, -1};
+  r.eff = atc_eff(p, lin);
+  if (r.eff < 0) return r;
+  const int slot = r.eff / (p.tc_q_tiles * p.tc_hy);
+  r.seq = p.seq_order ? p.seq_order[slot] : slot;
+  if (r.seq < 0 || r.seq >= p.num_seqs) {  // a bad order entry: skip the tile, flag it
+    report_status(B200_STATUS_BAD_INDEX, r.seq);
+    r.eff = -1;
+    return r;
+  }
+  r.q_start = p.cu_seqlens_q[r.seq];
+  r.q_end = p.cu_seqlens_q[r.seq + 1];
+  r.kv_len = p.seqused_k[r.seq];
   return r;
 }
 
 template <int NC>
 __device__ __forceinline__ void atc_make(const AttnParams& p, int lin, const AtcRaw& r, AtcTile& t) {
-  const int x = lin % p.tc_q_tiles;
-  const int rest = lin / p.tc_q_tiles;
+  const int eff = r.eff < 0 ? 0 : r.eff;
+  const int x = eff % p.tc_q_tiles;
+  const int rest = eff / p.tc_q_tiles;
   const int y = rest % p.tc_hy;
-  t.seq = rest / p.tc_hy;
+  t.seq = r.seq;
   t.kvh = y / p.head_chunks;
   t.hchunk = y % p.head_chunks;
   t.heads_here = min(8, p.group - t.hchunk * 8);
@@ -100,7 +120,7 @@ __device__ __forceinline__ void atc_make(const AttnParams& p, int lin, const Atc
   t.q_len = r.q_end - r.q_start;
   t.kv_len = r.kv_len;
   t.tile_pos0 = x * t.pos_per_tile;
-  t.valid = t.q_len > 0 && t.kv_len > 0 && t.tile_pos0 < t.q_len;
+  t.valid = r.eff >= 0 && t.q_len > 0 && t.kv_len > 0 && t.tile_pos0 < t.q_len;
   t.q_abs0 = t.kv_len - t.q_len;
   int last_q = t.tile_pos0 + t.pos_per_tile - 1;
   if (last_q > t.q_len - 1) last_q = t.q_len - 1;
@@ -116,7 +136,7 @@ __device__ __forceinline__ void atc_tile(const AttnParams& p, int lin, AtcTile& 
 // First valid tile at or after lin in this CTA's round-robin sequence, or -1.
 template <int NC>
 __device__ __forceinline__ int atc_next_tile(const AttnParams& p, int lin, AtcTile& t) {
-  for (; lin < p.tc_tiles; lin += (int)gridDim.x) {
+  for (; lin < p.tc_slots; lin += (int)gridDim.x) {
     atc_tile<NC>(p, lin, t);
     if (t.valid) return lin;
   }
@@ -216,7 +236,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int boxes = ATC_BN / p.box_tokens;
     uint32_t g = 0;  // running block counter over this CTA's tiles
     bool ok = true;
-    for (int lin = blockIdx.x; lin < p.tc_tiles && ok; lin += (int)gridDim.x) {
+    for (int lin = blockIdx.x; lin < p.tc_slots && ok; lin += (int)gridDim.x) {
       AtcTile t;
       atc_tile<NC>(p, lin, t);
       if (!t.valid) continue;
@@ -267,12 +287,12 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       int lin = atc_next_tile<NC>(p, blockIdx.x, t);  // tile of the next QK^T to issue
       uint32_t gs = 0, gp = 0, tile_it = 0;                 // next QK^T block, next PV block, tile counter
       int j = 0;                                            // block of that tile
-      AtcRaw raw_next = {0, 0, 0};
+      AtcRaw raw_next = {0, 0, 0, 0, -1};
       auto issue_next_s = [&]() {  // S^T of global block gs into S buffer gs & 1
         const int qb = tile_it & 1;
         if (j == 0) {
           // the next tile's description: loads only, used when this tile's last QK^T has been issued
-          if (lin + (int)gridDim.x < p.tc_tiles) raw_next = atc_raw(p, lin + (int)gridDim.x);
+          if (lin + (int)gridDim.x < p.tc_slots) raw_next = atc_raw(p, lin + (int)gridDim.x);
           if (!ptx::mbar_wait(qfull_bar(qb), (tile_it >> 1) & 1, abort_flag, 605 + qb)) return false;
         }
         const int s = gs % KST, b = gs & 1;
@@ -295,7 +315,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
           ++tile_it;
           const int cand = lin + (int)gridDim.x;
           lin = -1;
-          if (cand < p.tc_tiles) {
+          if (cand < p.tc_slots) {
             atc_make<NC>(p, cand, raw_next, t);
             lin = t.valid ? cand : atc_next_tile<NC>(p, cand + (int)gridDim.x, t);
           }
@@ -396,8 +416,8 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       // the next tile's description is read now (loads only, nothing waits for them) so that it is at
       // hand when the tile starts
       const int cand = lin + (int)gridDim.x;
-      const bool have_cand = cand < p.tc_tiles;
-      AtcRaw raw_next = {0, 0, 0};
+      const bool have_cand = cand < p.tc_slots;
+      AtcRaw raw_next = {0, 0, 0, 0, -1};
       if (have_cand) raw_next = atc_raw(p, cand);
       // columns at or beyond ncv are padding: their scores are never looked at and whatever their P^T
       // rows hold only reaches O^T columns that are not stored

@@ -243,6 +243,7 @@ class StepInputs:
     context_lens: torch.Tensor               # [S] int32
     block_tables: torch.Tensor               # [S, max_blocks] int32
     max_seqlen_q: int
+    seq_order: Optional[torch.Tensor] = None  # [S] int32, sequences by descending context (attention balance)
 
 
 class StageRunner:
@@ -301,7 +302,7 @@ class StageRunner:
             "b200_qknorm_rope_store",
         )
         attn = paged_attention(q, kc, vc, inp.query_start_loc, inp.context_lens, inp.block_tables,
-                               s.head_dim ** -0.5, inp.max_seqlen_q)
+                               s.head_dim ** -0.5, inp.max_seqlen_q, seq_order=inp.seq_order)
         return linear(attn.view(T, s.num_q_heads * s.head_dim), lw.o)
 
     def _mla_block(self, lw: LayerWeights, kc, vc, xn: torch.Tensor, inp: StepInputs) -> torch.Tensor:
@@ -323,7 +324,7 @@ class StageRunner:
             "b200_mla_rope_store",
         )
         attn = paged_attention(q, kc, vc, inp.query_start_loc, inp.context_lens, inp.block_tables,
-                               (a.qk_nope + a.qk_rope) ** -0.5, inp.max_seqlen_q)
+                               (a.qk_nope + a.qk_rope) ** -0.5, inp.max_seqlen_q, seq_order=inp.seq_order)
         return linear(attn.view(T, heads * a.v_head), lw.o)
 
     def _dense_mlp(self, xn, gate_up, down, width):

@@ -41,6 +41,8 @@ class StepBuffers:
         self.input_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
         self.position_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
         self.step_info = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.seq_order = torch.arange(S, dtype=torch.int32, device=dev)   # requests by descending context
+        self._order_host = torch.empty(S, dtype=torch.int32, pin_memory=self.device.type == "cuda")
         # per-request state kept on the device between steps
         self.request_blocks = torch.full((S, B), -1, dtype=torch.int32, device=dev)
         self.last_tokens = torch.zeros(S, dtype=torch.long, device=dev)
@@ -108,14 +110,22 @@ class StepBuffers:
         self._counters_dev[:, :num_seqs].copy_(c[:, :num_seqs], non_blocking=True)
         if n_prefill:
             self._prefill_dev[:n_prefill].copy_(self._prefill_host[:n_prefill], non_blocking=True)
-        self.h2d_bytes_last_step = 3 * num_seqs * 4 + n_prefill * 8
+        # longest context first: the attention kernel deals its tiles in this order (padded rows last)
+        order = torch.argsort(torch.as_tensor(list(num_computed_tokens), dtype=torch.int32), descending=True,
+                              stable=True)
+        self._order_host[:num_seqs] = order.to(torch.int32)
+        if graph_num_seqs > num_seqs:
+            self._order_host[num_seqs:graph_num_seqs] = torch.arange(num_seqs, graph_num_seqs, dtype=torch.int32)
+        self.seq_order[:graph_num_seqs].copy_(self._order_host[:graph_num_seqs], non_blocking=True)
+        self.h2d_bytes_last_step = 3 * num_seqs * 4 + graph_num_seqs * 4 + n_prefill * 8
         self.launch(num_seqs, graph_num_seqs, capture_tokens, n_prefill > 0)
         max_q = max((int(t) for t in tokens_this_step), default=0)
         return StepInputs(
             input_ids=self.input_ids[0, :capture_tokens], hidden_in=None,
             positions=self.position_ids[0, :capture_tokens], slot_mapping=self.slot_mapping[:capture_tokens],
             query_start_loc=self.query_start_loc[: graph_num_seqs + 1], context_lens=self.context_lens[:graph_num_seqs],
-            block_tables=self.block_tables[:graph_num_seqs], max_seqlen_q=max_q)
+            block_tables=self.block_tables[:graph_num_seqs], max_seqlen_q=max_q,
+            seq_order=self.seq_order[:graph_num_seqs])
 
     def launch(self, num_seqs: int, graph_num_seqs: int, capture_tokens: int, has_prefill: bool) -> None:
         """The kernel alone, on counters already in `_counters_dev` (what a replayed step calls)."""
