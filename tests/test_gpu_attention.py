@@ -61,7 +61,7 @@ def test_golden_reference_kernel(vb):
 
 @pytest.mark.parametrize("hq,hkv,dk,dv,page", [(32, 4, 128, 128, 16), (16, 8, 128, 128, 16), (12, 2, 128, 128, 64),
                                                (16, 8, 128, 128, 256), (16, 16, 192, 128, 16), (4, 4, 64, 64, 16),
-                                               (32, 2, 128, 128, 16)])
+                                               (32, 2, 128, 128, 16), (6, 2, 128, 128, 8), (5, 1, 128, 128, 32)])
 def test_oracle_mixed_batch(vb, hq, hkv, dk, dv, page):
     q_lens = [1, 5, 1, 17, 64, 1]
     kv_lens = [1, 5, 130, 200, 64, 257]
