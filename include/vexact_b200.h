@@ -221,6 +221,15 @@ int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, v
 int b200_moe_unpermute_reduce(const void* y, const void* scatter_index, const void* addend, void* out,
                               long long T, int topk, int H, void* stream);
 
+/* b200_moe_unpermute_reduce followed by b200_add_rmsnorm (the residual add and input RMSNorm the next
+ * decoder layer starts with) in one launch, with that pair's arithmetic element for element:
+ * sum_out[t] = bf16(residual[t] + moe[t]), out[t] = rmsnorm(sum_out[t]) * weight (mode as b200_rmsnorm).
+ * H a multiple of 8 in 1032..8192; all pointers 16-byte aligned.  No counterpart in the reference
+ * (there: moe_gather, a torch add and the RMSNorm module are separate ops). */
+int b200_moe_unpermute_add_rmsnorm(const void* y, const void* scatter_index, const void* addend,
+                                   const void* residual, const void* weight, void* sum_out, void* out,
+                                   long long T, int topk, int H, float eps, int mode, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -143,3 +143,30 @@ def test_fused_moe_batch_invariance_bitwise(vb):
 def test_status_word_clean(vb):
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+def test_deferred_topk_sum_fused_with_add_rmsnorm_bitwise(vb):
+    """PendingMoE.add_norm == finish() followed by add_rms_norm, bit for bit (with and without addend)."""
+    for H in (2048, 512):      # one-CTA-per-row norm (fused kernel) and the short-row fallback
+        _check_deferred_sum(vb, H)
+
+
+def _check_deferred_sum(vb, H):
+    g = torch.Generator().manual_seed(5)
+    T, E, k, I = 96, 16, 4, 256
+    x = (torch.randn(T, H, generator=g) * 0.5).bfloat16().cuda()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16().cuda()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16().cuda()
+    logits = torch.randn(T, E, generator=g).bfloat16().cuda()
+    rw, sel = vb.route_softmax_topk(logits, k, True)
+    residual = torch.randn(T, H, generator=g).bfloat16().cuda()
+    norm_w = (1 + 0.02 * torch.randn(H, generator=g)).bfloat16().cuda()
+    for addend in (None, (torch.randn(T, H, generator=g) * 0.3).bfloat16().cuda()):
+        for hf in (True, False):
+            plain = vb.fused_moe_forward(E, rw, sel, x, fc2_weight=w2, fc1_1_2_weight=w13, addend=addend)
+            want_sum, want_norm = vb.add_rms_norm(plain, residual, norm_w, 1e-6, hf=hf)
+            pend = vb.fused_moe_forward(E, rw, sel, x, fc2_weight=w2, fc1_1_2_weight=w13, addend=addend,
+                                        defer_reduce=True)
+            got_sum, got_norm = pend.add_norm(residual, norm_w, 1e-6, hf=hf)
+            assert torch.equal(got_sum, want_sum) and torch.equal(got_norm, want_norm)
+            assert torch.equal(pend.finish(), plain)

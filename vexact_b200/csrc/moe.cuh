@@ -342,6 +342,100 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
   if (threadIdx.x == 0 && row_scale && weights) row_scale[pos] = weights[f];
 }
 
+// The top-k sum below followed, in the same launch, by the residual add and the RMSNorm that the next
+// decoder layer starts with:  m = bf16(sum_k y[...]) (+ addend);  s = bf16(residual + m);
+// out = rmsnorm(s) * w.  Same arithmetic, element for element, as moe_unpermute_reduce_kernel followed
+// by rmsnorm_cta_kernel<true> (the sum of squares is accumulated and reduced in that kernel's order).
+__global__ void __launch_bounds__(128)
+moe_unpermute_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ scatter_index,
+                                 const __nv_bfloat16* __restrict__ addend, const __nv_bfloat16* __restrict__ res,
+                                 const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ sum_out,
+                                 __nv_bfloat16* __restrict__ out, int H, int topk, float eps, int mode) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float scratch[32];
+  constexpr int MAXV = 8, THREADS = 128;
+  const long long t = blockIdx.x;
+  const int nvec = H >> 3;
+  uint4 cache[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int k = 0; k < topk; ++k) {
+        const int pos = scatter_index[t * topk + k];
+        if (pos < 0) continue;
+        const uint4 r = reinterpret_cast<const uint4*>(y + (long long)pos * H)[v];
+        const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a, b;
+          unpack_bf2(rp[j], a, b);
+          acc[2 * j] += a;
+          acc[2 * j + 1] += b;
+        }
+      }
+      if (addend) {
+        const uint4 r = reinterpret_cast<const uint4*>(addend + t * H)[v];
+        const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a, b;
+          unpack_bf2(rp[j], a, b);
+          acc[2 * j] = round_bf(acc[2 * j]) + a;
+          acc[2 * j + 1] = round_bf(acc[2 * j + 1]) + b;
+        }
+      }
+      // m = bf16(acc); s = bf16(residual + m)
+      const uint4 r = reinterpret_cast<const uint4*>(res + t * H)[v];
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+      uint4 a;
+      uint32_t* ap = reinterpret_cast<uint32_t*>(&a);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float r0, r1;
+        unpack_bf2(rp[j], r0, r1);
+        ap[j] = pack_bf2(r0 + round_bf(acc[2 * j]), r1 + round_bf(acc[2 * j + 1]));
+      }
+      reinterpret_cast<uint4*>(sum_out + t * H)[v] = a;
+      cache[i] = a;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a0, a1;
+        unpack_bf2(ap[j], a0, a1);
+        ss += a0 * a0;
+        ss += a1 * a1;
+      }
+    }
+  }
+  const float tot = block_sum(ss, scratch);
+  const float inv = rms_scale(tot, H, eps, mode);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * THREADS;
+    if (v < nvec) {
+      const uint4 a = cache[i];
+      const uint4 ww = reinterpret_cast<const uint4*>(w)[v];
+      const uint32_t* ap = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* wp = reinterpret_cast<const uint32_t*>(&ww);
+      uint4 o;
+      uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a0, a1, w0, w1;
+        unpack_bf2(ap[j], a0, a1);
+        unpack_bf2(wp[j], w0, w1);
+        op[j] = pack_bf2(rms_apply(a0, inv, w0, mode), rms_apply(a1, inv, w1, mode));
+      }
+      reinterpret_cast<uint4*>(out + t * H)[v] = o;
+    }
+  }
+}
+
 // out[t] = bf16( sum_k fp32(y[scatter_index[t, k]]) ), k ascending; optionally followed by
 // out[t] = bf16(fp32(out[t]) + fp32(addend[t])) (shared-expert or residual add as a separate bf16 op).
 __global__ void __launch_bounds__(256)
@@ -492,6 +586,29 @@ extern "C" int b200_moe_unpermute_reduce(const void* y, const void* scatter_inde
   launch_k(moe_unpermute_reduce_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, H,
       topk);
+  return launch_status();
+}
+
+// b200_moe_unpermute_reduce + b200_add_rmsnorm in one launch: sum_out = residual + moe output (the new
+// residual stream), out = rmsnorm(sum_out) * weight.  H a multiple of 8 in 1032..8192.
+extern "C" int b200_moe_unpermute_add_rmsnorm(const void* y, const void* scatter_index, const void* addend,
+                                              const void* residual, const void* weight, void* sum_out, void* out,
+                                              long long T, int topk, int H, float eps, int mode, void* stream) {
+  using namespace b200;
+  if (!y || !scatter_index || !residual || !weight || !sum_out || !out || T < 0 || topk <= 0 || H <= 0 ||
+      (mode != 0 && mode != 1))
+    return B200_ERR_ARG;
+  // rows of up to 1024 elements go through the warp-per-row norm kernel, whose reduction tree differs
+  if (H % 8 != 0 || H > 8192 || H <= 1024) return B200_ERR_SHAPE;
+  if (((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(weight) |
+        reinterpret_cast<uintptr_t>(sum_out) | reinterpret_cast<uintptr_t>(out) |
+        reinterpret_cast<uintptr_t>(addend)) & 15) != 0)
+    return B200_ERR_ARG;
+  if (T == 0) return B200_OK;
+  launch_k(moe_unpermute_add_rmsnorm_kernel, dim3((unsigned)T), dim3(128), 0, (cudaStream_t)stream,
+           (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend,
+           (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, (__nv_bfloat16*)sum_out, (__nv_bfloat16*)out,
+           H, topk, eps, mode);
   return launch_status();
 }
 

@@ -135,6 +135,44 @@ def _grouped_gemm(x, w, row_scale, plan, n_out, mode):
     return out
 
 
+class PendingMoE:
+    """Expert outputs still in expert-sorted order: the top-k sum has not run yet, so that it can be
+    fused with the residual add and RMSNorm that follow (`add_norm`) or run on its own (`finish`)."""
+
+    def __init__(self, y, scatter_index, addend, T, k, H, shape):
+        self.y, self.scatter_index, self.addend = y, scatter_index, addend
+        self.T, self.k, self.H, self.shape = T, k, H, shape
+
+    def finish(self) -> torch.Tensor:
+        out = torch.empty((self.T, self.H), device=self.y.device, dtype=torch.bfloat16)
+        _lib.check(
+            _lib.load().b200_moe_unpermute_reduce(self.y.data_ptr(), self.scatter_index.data_ptr(),
+                                                  _lib.ptr(self.addend), out.data_ptr(), self.T, self.k, self.H,
+                                                  _lib.current_stream()),
+            "b200_moe_unpermute_reduce",
+        )
+        return out.reshape(self.shape)
+
+    def add_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, hf: bool = True):
+        """(residual + moe output, rmsnorm of that sum): `finish()` + `add_rms_norm` in one launch."""
+        # the fused kernel reproduces the one-CTA-per-row norm kernel, which serves rows of 1025..8192 elements
+        if self.H % 8 != 0 or self.H > 8192 or self.H <= 1024:
+            from .batch_invariant_ops import add_rms_norm
+            return add_rms_norm(self.finish(), residual, weight, eps, hf)
+        r = residual.reshape(self.T, self.H).contiguous()
+        w = weight.to(torch.bfloat16).contiguous()
+        s = torch.empty_like(r)
+        out = torch.empty_like(r)
+        _lib.check(
+            _lib.load().b200_moe_unpermute_add_rmsnorm(
+                self.y.data_ptr(), self.scatter_index.data_ptr(), _lib.ptr(self.addend), r.data_ptr(), w.data_ptr(),
+                s.data_ptr(), out.data_ptr(), self.T, self.k, self.H, float(eps), 1 if hf else 0,
+                _lib.current_stream()),
+            "b200_moe_unpermute_add_rmsnorm",
+        )
+        return s.reshape(residual.shape), out.reshape(residual.shape)
+
+
 def fused_moe_forward(
     num_experts: int,
     routing_weights: torch.Tensor,
@@ -145,8 +183,11 @@ def fused_moe_forward(
     fc2_weight: Optional[torch.Tensor] = None,
     fc1_1_2_weight: Optional[torch.Tensor] = None,
     addend: Optional[torch.Tensor] = None,
-) -> torch.Tensor:
+    defer_reduce: bool = False,
+):
     """sum_k w_k * fc2_e(silu(fc1_1_e x) * fc1_2_e x) for the selected experts e of each token.
+
+    With defer_reduce the call stops before the top-k sum and returns a `PendingMoE`.
 
     Weights: fc1_1 / fc1_2 [E, I, H] (split) or fc1_1_2 [E, 2I, H] (gate rows first), fc2 [E, H, I].
     The routing weight multiplies the activation before fc2 and every intermediate is a bf16
@@ -187,12 +228,7 @@ def fused_moe_forward(
     fc2_weight = fc2_weight if (fc2_weight.dtype == torch.bfloat16 and fc2_weight.is_contiguous()) \
         else fc2_weight.to(torch.bfloat16).contiguous()
     y = _grouped_gemm(h, fc2_weight, None, plan, H, mode=0)
-    out = torch.empty((T, H), device=x.device, dtype=torch.bfloat16)
     if addend is not None:
         addend = addend.to(torch.bfloat16).reshape(T, H).contiguous()
-    _lib.check(
-        _lib.load().b200_moe_unpermute_reduce(y.data_ptr(), plan["scatter_index"].data_ptr(), _lib.ptr(addend),
-                                              out.data_ptr(), T, k, H, _lib.current_stream()),
-        "b200_moe_unpermute_reduce",
-    )
-    return out.reshape(orig_shape)
+    pending = PendingMoE(y, plan["scatter_index"], addend, T, k, H, orig_shape)
+    return pending if defer_reduce else pending.finish()

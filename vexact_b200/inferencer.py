@@ -23,7 +23,7 @@ import torch
 from . import _lib
 from .attention import paged_attention
 from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
-from .fused_moe import (TILE_ROWS, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
+from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
                         route_softmax_topk)
 from .standalone_logprobs import greedy_token_and_logprob
 from .sampler import sample_token_and_logprob
@@ -283,6 +283,8 @@ class StageRunner:
         return batch_invariant_rms_norm(x, w, s.rms_eps) if s.norm_single_round else hf_rms_norm(x, w, s.rms_eps)
 
     def _add_norm(self, x, residual, w):
+        if isinstance(x, PendingMoE):   # the MoE's top-k sum joins the residual add and the norm
+            return x.add_norm(residual, w, self.shape.rms_eps, hf=not self.shape.norm_single_round)
         return add_rms_norm(x, residual, w, self.shape.rms_eps, hf=not self.shape.norm_single_round)
 
     def _attention_block(self, lw: LayerWeights, layer_idx: int, xn: torch.Tensor, inp: StepInputs) -> torch.Tensor:
@@ -346,11 +348,11 @@ class StageRunner:
             if lw.shared_gate_up is not None:
                 shared = self._dense_mlp(xn, lw.shared_gate_up, lw.shared_down, m.intermediate * m.n_shared_experts)
             return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
-                                     fc1_1_2_weight=lw.experts_gate_up, addend=shared)
+                                     fc1_1_2_weight=lw.experts_gate_up, addend=shared, defer_reduce=True)
         logits = linear(xn, lw.router)
         rw, sel = route_softmax_topk(logits, m.top_k, m.norm_topk_prob)
         return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
-                                 fc1_1_2_weight=lw.experts_gate_up)
+                                 fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True)
 
     def forward(self, inp: StepInputs) -> torch.Tensor:
         """Hidden states after the local layers ([T, H]); the residual stream is complete."""
@@ -368,7 +370,7 @@ class StageRunner:
             h, xn2 = self._add_norm(attn_out, h, lw.post_norm)
             delta = self._mlp_block(lw, xn2)
         if delta is not None:
-            h = h + delta
+            h = h + (delta.finish() if isinstance(delta, PendingMoE) else delta)
         return h
 
     def select_tokens(self, h: torch.Tensor, inp: StepInputs):
