@@ -230,20 +230,6 @@ int b200_moe_unpermute_add_rmsnorm(const void* y, const void* scatter_index, con
                                    const void* residual, const void* weight, void* sum_out, void* out,
                                    long long T, int topk, int H, float eps, int mode, void* stream);
 
-/* What sits between the attention output projection and the experts of a Qwen3-MoE layer
- * (modeling_qwen3_moe.py:119-134 after the decoder layer's residual add and post-attention RMSNorm),
- * in one launch: sum_out = bf16(residual + attn_out), xn_out = rmsnorm(sum_out) * norm_weight (both
- * bit-identical to b200_add_rmsnorm), router logits = bf16(xn_out . router_weight[e]) with fp32
- * accumulation in a fixed per-token order, then softmax -> top-k -> renorm as
- * b200_moe_route_softmax_topk.  logits_out [T, E] bf16 may be NULL; weights bf16 [T, topk]; experts
- * int32 and / or int64 [T, topk].  H a multiple of 8 in 1032..8192; E <= 256.  The logits can differ
- * from b200_gemm_bf16's in the last bf16 bit (different fp32 summation order); a token's values do
- * not depend on the batch either way. */
-int b200_post_attn_norm_route(const void* attn_out, const void* residual, const void* norm_weight, void* sum_out,
-                              void* xn_out, const void* router_weight, void* logits_out, void* weights_bf16,
-                              void* experts_i32, void* experts_i64, long long T, int H, int E, int topk,
-                              int renorm, float eps, int mode, void* stream);
-
 #ifdef __cplusplus
 }
 #endif

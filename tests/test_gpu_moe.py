@@ -170,32 +170,3 @@ def _check_deferred_sum(vb, H):
             got_sum, got_norm = pend.add_norm(residual, norm_w, 1e-6, hf=hf)
             assert torch.equal(got_sum, want_sum) and torch.equal(got_norm, want_norm)
             assert torch.equal(pend.finish(), plain)
-
-
-def test_post_attn_norm_route_fused(vb):
-    """Norm outputs bit-identical to add_rms_norm; logits within one bf16 ulp of the GEMM's; routing
-    equal to routing those logits through the stand-alone kernel; batch invariant."""
-    from vexact_b200.fused_moe import post_attn_norm_route
-
-    g = torch.Generator().manual_seed(9)
-    T, H, E, k = 203, 2048, 128, 8
-    attn = (torch.randn(T, H, generator=g) * 0.7).bfloat16().cuda()
-    res = torch.randn(T, H, generator=g).bfloat16().cuda()
-    nw = (1 + 0.02 * torch.randn(H, generator=g)).bfloat16().cuda()
-    rw = (torch.randn(E, H, generator=g) * 0.02).bfloat16().cuda()
-    hid, xn, w, sel, logits = post_attn_norm_route(attn, res, nw, rw, k, True, 1e-6, hf=True, return_logits=True)
-    want_hid, want_xn = vb.add_rms_norm(attn, res, nw, 1e-6, hf=True)
-    assert torch.equal(hid, want_hid) and torch.equal(xn, want_xn)
-    gemm_logits = vb.linear(xn, rw)
-    ref = xn.float() @ rw.float().t()
-    err = (logits.float() - ref).abs()
-    assert (err <= 2.0 ** -8 * ref.abs() + 1e-6).all()                      # half a bf16 ulp of the exact value
-    assert (logits == gemm_logits).float().mean().item() > 0.98            # same bits nearly everywhere
-    w2, sel2 = vb.route_softmax_topk(logits, k, True)
-    assert torch.equal(sel, sel2) and torch.equal(w, w2)
-    # a token's outputs do not depend on the batch it is in
-    h1, x1, w1, s1 = post_attn_norm_route(attn[37:38], res[37:38], nw, rw, k, True, 1e-6, hf=True)
-    assert torch.equal(h1, hid[37:38]) and torch.equal(x1, xn[37:38]) and torch.equal(w1, w[37:38])
-    assert torch.equal(s1, sel[37:38])
-    h5, x5, w5, s5 = post_attn_norm_route(attn[100:105], res[100:105], nw, rw, k, True, 1e-6, hf=True)
-    assert torch.equal(w5, w[100:105]) and torch.equal(s5, sel[100:105])

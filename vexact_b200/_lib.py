@@ -45,7 +45,6 @@ SIGNATURES = {
     "b200_swiglu_scale": [P, P, P, P, LL, I, P],
     "b200_moe_unpermute_reduce": [P, P, P, P, LL, I, I, P],
     "b200_moe_unpermute_add_rmsnorm": [P, P, P, P, P, P, P, LL, I, I, F, I, P],
-    "b200_post_attn_norm_route": [P, P, P, P, P, P, P, P, P, P, LL, I, I, I, I, F, I, P],
 }
 
 _ERRORS = {

@@ -114,85 +114,6 @@ moe_route_softmax_topk_kernel(const TIn* __restrict__ logits, long long row_stri
                                 threadIdx.x & 31);
 }
 
-// What sits between the attention output projection and the experts of a Qwen3-MoE layer, in one
-// launch for POST_TOK tokens per CTA: hidden = residual + attn_out and its RMSNorm (the arithmetic
-// of rmsnorm_cta_kernel<true>, bit for bit), the router logits (bf16(fp32 dot) per expert, summed in
-// ascending order by one thread - a token's logits do not depend on the batch) and the softmax -> top-k -> renorm of moe_route_softmax_topk_kernel.
-constexpr int POST_TOK = 4;
-
-__global__ void __launch_bounds__(128)
-post_attn_norm_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
-                            const __nv_bfloat16* __restrict__ norm_w, __nv_bfloat16* __restrict__ sum_out,
-                            __nv_bfloat16* __restrict__ xn_out, const __nv_bfloat16* __restrict__ router_w,
-                            __nv_bfloat16* __restrict__ logits_out, __nv_bfloat16* __restrict__ w_bf16,
-                            int* __restrict__ idx_i32, long long* __restrict__ idx_i64, long long T, int H, int E,
-                            int topk, int renorm, float eps, int mode) {
-  pdl_trigger();
-  pdl_wait();
-  extern __shared__ __align__(16) uint8_t post_smem[];
-  __nv_bfloat16* s_xn = reinterpret_cast<__nv_bfloat16*>(post_smem);  // [POST_TOK][H]
-  __shared__ float scratch[32];
-  __shared__ __nv_bfloat16 s_logits[POST_TOK][MOE_MAX_EXPERTS];
-  const long long tok0 = (long long)blockIdx.x * POST_TOK;
-  const int ntok = (int)min((long long)POST_TOK, T - tok0);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (int r = 0; r < ntok; ++r) {
-    const long long tok = tok0 + r;
-    rmsnorm_row<128, 8, true>(x + tok * H, res + tok * H, norm_w, xn_out + tok * H, sum_out + tok * H, H, eps, mode,
-                              tid, scratch);
-    __syncthreads();  // scratch is reused by the next row
-  }
-  // the normalised rows, back from this CTA's own global writes, into shared memory
-  const int nvec = H >> 3;
-  for (int r = 0; r < ntok; ++r)
-    for (int v = tid; v < nvec; v += 128)
-      reinterpret_cast<uint4*>(s_xn + (size_t)r * H)[v] = reinterpret_cast<const uint4*>(xn_out + (tok0 + r) * H)[v];
-  __syncthreads();
-  // router logits: thread = expert (E <= 128 in one pass, else in passes of 128).  A thread walks its
-  // expert's weight row in ascending order with one fp32 accumulator per token: the order is fixed and
-  // the x values come from shared memory as broadcasts, so a token's logits do not depend on the batch.
-  for (int e0 = 0; e0 < E; e0 += 128) {
-    const int e = e0 + tid;
-    float acc[POST_TOK];
-#pragma unroll
-    for (int r = 0; r < POST_TOK; ++r) acc[r] = 0.f;
-    if (e < E) {
-      const uint4* wrow = reinterpret_cast<const uint4*>(router_w + (size_t)e * H);
-#pragma unroll 4
-      for (int v = 0; v < nvec; ++v) {
-        const uint4 wv = wrow[v];
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&wv);
-        float wf[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) unpack_bf2(wp[j], wf[2 * j], wf[2 * j + 1]);
-#pragma unroll
-        for (int r = 0; r < POST_TOK; ++r) {
-          const uint4 xv = reinterpret_cast<const uint4*>(s_xn + (size_t)r * H)[v];
-          const uint32_t* xp = reinterpret_cast<const uint32_t*>(&xv);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float a, b;
-            unpack_bf2(xp[j], a, b);
-            acc[r] = fmaf(a, wf[2 * j], acc[r]);
-            acc[r] = fmaf(b, wf[2 * j + 1], acc[r]);
-          }
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < POST_TOK; ++r) {
-        if (r < ntok) {
-          s_logits[r][e] = f2bf(acc[r]);
-          if (logits_out) logits_out[(tok0 + r) * E + e] = f2bf(acc[r]);
-        }
-      }
-    }
-  }
-  __syncthreads();
-  if (warp < ntok)
-    route_softmax_topk_token<__nv_bfloat16>(s_logits[warp], tok0 + warp, w_bf16, nullptr, idx_i32, idx_i64, E, topk,
-                                            renorm, lane);
-}
-
 // DeepSeek-V3 routing.  One warp per token; E <= 256.
 //   s = sigmoid(logit); c = s + bias; group score = sum of the group's top-2 c;
 //   keep the top `topk_group` groups, zero the rest (masked_fill 0.0), top-k over c;
@@ -699,41 +620,6 @@ extern "C" int b200_moe_unpermute_add_rmsnorm(const void* y, const void* scatter
            (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend,
            (const __nv_bfloat16*)residual, (const __nv_bfloat16*)weight, (__nv_bfloat16*)sum_out, (__nv_bfloat16*)out,
            H, topk, eps, mode);
-  return launch_status();
-}
-
-// b200_add_rmsnorm (attention output + residual, post-attention norm), the router projection and
-// b200_moe_route_softmax_topk in one launch.  sum_out / xn_out [T, H] bf16 (bit-identical to
-// b200_add_rmsnorm); logits_out [T, E] bf16 may be null; weights bf16 [T, topk]; experts int32 and / or
-// int64 [T, topk].  H a multiple of 8 in 1032..8192, E <= 256.
-extern "C" int b200_post_attn_norm_route(const void* attn_out, const void* residual, const void* norm_weight,
-                                         void* sum_out, void* xn_out, const void* router_weight, void* logits_out,
-                                         void* weights_bf16, void* experts_i32, void* experts_i64, long long T,
-                                         int H, int E, int topk, int renorm, float eps, int mode, void* stream) {
-  using namespace b200;
-  if (!attn_out || !residual || !norm_weight || !sum_out || !xn_out || !router_weight || !weights_bf16 ||
-      (!experts_i32 && !experts_i64) || T < 0 || E <= 0 || topk <= 0 || (mode != 0 && mode != 1))
-    return B200_ERR_ARG;
-  if (H % 8 != 0 || H > 8192 || H <= 1024 || E > MOE_MAX_EXPERTS || topk > MOE_MAX_TOPK || topk > E)
-    return B200_ERR_SHAPE;
-  if (((reinterpret_cast<uintptr_t>(attn_out) | reinterpret_cast<uintptr_t>(residual) |
-        reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(sum_out) |
-        reinterpret_cast<uintptr_t>(xn_out) | reinterpret_cast<uintptr_t>(router_weight)) & 15) != 0)
-    return B200_ERR_ARG;
-  if (T == 0) return B200_OK;
-  const size_t smem = (size_t)POST_TOK * H * sizeof(__nv_bfloat16);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(post_attn_norm_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             POST_TOK * 8192 * 2) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
-  launch_k(post_attn_norm_route_kernel, dim3((unsigned)((T + POST_TOK - 1) / POST_TOK)), dim3(128), smem,
-           (cudaStream_t)stream, (const __nv_bfloat16*)attn_out, (const __nv_bfloat16*)residual,
-           (const __nv_bfloat16*)norm_weight, (__nv_bfloat16*)sum_out, (__nv_bfloat16*)xn_out,
-           (const __nv_bfloat16*)router_weight, (__nv_bfloat16*)logits_out, (__nv_bfloat16*)weights_bf16,
-           (int*)experts_i32, (long long*)experts_i64, T, H, E, topk, renorm, eps, mode);
   return launch_status();
 }
 

@@ -135,37 +135,6 @@ def _grouped_gemm(x, w, row_scale, plan, n_out, mode):
     return out
 
 
-def post_attn_norm_route(attn_out: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
-                         router_weight: torch.Tensor, top_k: int, norm_topk_prob: bool, eps: float = 1e-6,
-                         hf: bool = True, return_logits: bool = False):
-    """Residual add + post-attention RMSNorm + router projection + softmax/top-k routing in one launch.
-
-    Returns (hidden, normed, routing_weights bf16 [T, k], selected_experts int64 [T, k][, logits]).
-    hidden / normed are bit-identical to `add_rms_norm(attn_out, residual, norm_weight)`."""
-    T, H = attn_out.shape
-    E = router_weight.shape[0]
-    x = attn_out.contiguous()
-    r = residual.reshape(T, H).contiguous()
-    w = norm_weight.to(torch.bfloat16).contiguous()
-    rw_ = router_weight if (router_weight.dtype == torch.bfloat16 and router_weight.is_contiguous()) \
-        else router_weight.to(torch.bfloat16).contiguous()
-    hidden = torch.empty_like(x)
-    normed = torch.empty_like(x)
-    weights = torch.empty((T, top_k), device=x.device, dtype=torch.bfloat16)
-    experts = torch.empty((T, top_k), device=x.device, dtype=torch.long)
-    logits = torch.empty((T, E), device=x.device, dtype=torch.bfloat16) if return_logits else None
-    _lib.check(
-        _lib.load().b200_post_attn_norm_route(
-            x.data_ptr(), r.data_ptr(), w.data_ptr(), hidden.data_ptr(), normed.data_ptr(), rw_.data_ptr(),
-            _lib.ptr(logits), weights.data_ptr(), None, experts.data_ptr(), T, H, E, int(top_k),
-            1 if norm_topk_prob else 0, float(eps), 1 if hf else 0, _lib.current_stream()),
-        "b200_post_attn_norm_route",
-    )
-    if return_logits:
-        return hidden, normed, weights, experts, logits
-    return hidden, normed, weights, experts
-
-
 class PendingMoE:
     """Expert outputs still in expert-sorted order: the top-k sum has not run yet, so that it can be
     fused with the residual add and RMSNorm that follow (`add_norm`) or run on its own (`finish`)."""

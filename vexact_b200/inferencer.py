@@ -23,8 +23,8 @@ import torch
 from . import _lib
 from .attention import paged_attention
 from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
-from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, post_attn_norm_route,
-                        route_sigmoid_group_topk, route_softmax_topk)
+from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
+                        route_softmax_topk)
 from .standalone_logprobs import greedy_token_and_logprob
 from .sampler import sample_token_and_logprob
 
@@ -262,9 +262,6 @@ class StageRunner:
         self._dense_tiles: dict = {}
         # None = greedy; else dict(temperature=..., top_k=..., top_p=...) applied to every request
         self.sampling: Optional[dict] = None
-        # True: router projection + routing fused with the post-attention norm (b200_post_attn_norm_route);
-        # off by default: at 512 tokens the tcgen05 router GEMM + separate routing kernel is the faster path
-        self.fuse_router = False
 
     # -- dense MLP through the grouped-GEMM kernel's fused SwiGLU epilogue (one group)
     def _dense_plan(self, T: int, device):
@@ -357,13 +354,6 @@ class StageRunner:
         return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
                                  fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True)
 
-    def _fused_route(self, lw: LayerWeights) -> bool:
-        """Softmax-top-k MoE layers with a bf16 router and a hidden size the fused kernel covers."""
-        s = self.shape
-        return (self.fuse_router and lw.router is not None and s.moe is not None and s.moe.scoring != "sigmoid_group"
-                and lw.router.dtype == BF and 1024 < s.hidden <= 8192 and s.hidden % 8 == 0
-                and s.moe.num_experts <= 256)
-
     def forward(self, inp: StepInputs) -> torch.Tensor:
         """Hidden states after the local layers ([T, H]); the residual stream is complete."""
         if self.is_first:
@@ -377,16 +367,8 @@ class StageRunner:
             else:
                 h, xn = self._add_norm(delta, h, lw.input_norm)
             attn_out = self._attention_block(lw, li, xn, inp)
-            if self._fused_route(lw):
-                # residual add + post-attention norm + router + top-k routing: one launch
-                m = self.shape.moe
-                h, xn2, rw, sel = post_attn_norm_route(attn_out, h, lw.post_norm, lw.router, m.top_k, m.norm_topk_prob,
-                                                       self.shape.rms_eps, hf=not self.shape.norm_single_round)
-                delta = fused_moe_forward(m.num_experts, rw, sel, xn2, fc2_weight=lw.experts_down,
-                                          fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True)
-            else:
-                h, xn2 = self._add_norm(attn_out, h, lw.post_norm)
-                delta = self._mlp_block(lw, xn2)
+            h, xn2 = self._add_norm(attn_out, h, lw.post_norm)
+            delta = self._mlp_block(lw, xn2)
         if delta is not None:
             h = h + (delta.finish() if isinstance(delta, PendingMoE) else delta)
         return h
