@@ -27,7 +27,9 @@ import sys
 os.environ["TRITON_INTERPRET"] = "1"
 os.environ.setdefault("VEXACT_DISABLE_MODEL_PATCH", "1")
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("VEXACT_SRC", "")
+if not os.path.isdir(REF):
+    raise SystemExit("usage: pass the path of a vexact checkout (or set VEXACT_SRC)")
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "tests"))
 

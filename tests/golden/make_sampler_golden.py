@@ -15,7 +15,9 @@ import os
 import sys
 
 os.environ.setdefault("VEXACT_DISABLE_MODEL_PATCH", "1")
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("VEXACT_SRC", "")
+if not os.path.isdir(REF):
+    raise SystemExit("usage: pass the path of a vexact checkout (or set VEXACT_SRC)")
 sys.path.insert(0, REF)
 
 import torch  # noqa: E402
