@@ -27,6 +27,11 @@ extern "C" {
 
 int b200_abi_version(void);
 
+/* Self-test of the bounded device wait: one CTA waits limit_us microseconds (1..1000000) on an mbarrier that
+ * nothing completes; the wait must expire, put {1 (wait expired), 999, ...} into the status word and let the
+ * kernel return.  out_flag_device[0] (int32, device) becomes 1.  No counterpart in the reference. */
+int b200_selftest_wait_expiry(int limit_us, int* out_flag_device, void* stream);
+
 /* Reads {code, detail, block, spare} of the device status word into host_out4 and clears it.
  * Synchronises `stream`.  code: 0 ok, 1 a bounded wait expired, 2 an index was out of range. */
 int b200_status_read(int* host_out4, void* stream);

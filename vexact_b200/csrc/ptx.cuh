@@ -58,7 +58,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // barrier id in the device status word) or another thread already did.
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   // Fast path: no timer read (%globaltimer is slow) until the wait has spun for a long while.
   uint64_t t0 = 0;
   for (uint32_t spins = 1;; ++spins) {
@@ -68,7 +69,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         report_status(B200_STATUS_WAIT_EXPIRED, id);
         return false;
