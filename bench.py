@@ -52,6 +52,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--quick", action="store_true", help="device-timed run only (for profiler captures)")
+    ap.add_argument("--model", default="qwen3-30b-a3b-shape",
+                    help="another preset (qwen3-1.7b-shape, qwen2-1.5b-shape, moonlight-16b-a3b-shape) runs a "
+                         "one-GPU decode step of that shape as a side measurement with its own JSON line")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="side measurement: decode attention over a ragged batch, with / without sequence order")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
@@ -237,6 +240,57 @@ def build_inputs(args, shape, seed, device):
     return host, dev, S * pages
 
 
+def measured_peaks() -> dict:
+    """The pool's measured peaks (driver-written file), {} when absent."""
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+def run_side_model(args, shape):
+    """Side measurement (not the contract line): one decode step of another model shape (BASELINE
+    configs 2, 3, 5: dense Qwen3 / Qwen2 shapes, the Moonlight MLA + MoE shape) on one GPU through the
+    same stage runner and CUDA graph, against its own weights + KV HBM bound."""
+    from vexact_b200 import _lib
+    from vexact_b200.inferencer import StageRunner, StageWeights, StepInputs, allocate_kv_cache
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    S = args.batch
+    weights = StageWeights.random_init(shape, 0, 1, device=device, seed=0)
+    host, dev, nblocks = build_inputs(args, shape, seed=100, device=device)
+    kc, vc = allocate_kv_cache(shape, 0, shape.num_layers, nblocks, args.page, device=device, fill_std=1.0, seed=0)
+    runner = StageRunner(weights, kc, vc, 0, 1)
+    inp = StepInputs(input_ids=dev["input_ids"], hidden_in=None, positions=dev["positions"],
+                     slot_mapping=dev["slot_mapping"], query_start_loc=dev["query_start_loc"],
+                     context_lens=dev["context_lens"], block_tables=dev["block_tables"], max_seqlen_q=1)
+    _lib.reset_launch_count()
+    runner.step(inp)
+    torch.cuda.synchronize()
+    launches = _lib.launch_count()
+    graph, _ = runner.capture(inp)
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    kv_bytes = S * args.ctx * shape.num_kv_heads * (shape.k_dim + shape.v_dim) * 2 * shape.num_layers
+    w_bytes = weights.num_bytes() - shape.vocab * shape.hidden * 2   # the embedding table is gathered, not streamed
+    peak = float(measured_peaks().get("hbm_gbs", 6650.0))
+    bound_ms = (kv_bytes + w_bytes) / peak / 1e6
+    status = _lib.read_status()
+    print(json.dumps({"measurement": "decode_step", "model": shape.name, "batch": S, "ctx": args.ctx,
+                      "layers": shape.num_layers, "ms_per_step": ms, "tokens_per_s": S / ms * 1e3,
+                      "weights_gb": w_bytes / 1e9, "kv_gb": kv_bytes / 1e9, "hbm_bound_ms": bound_ms,
+                      "frac": bound_ms / ms, "launches_per_step": launches, "status": list(status)}))
+
+
 def run_ragged_attention(args, shape):
     """Side measurement (not the contract line): one layer's decode attention over a ragged batch
     (context lengths uniform in [64, 2 * ctx]), with and without the longest-first sequence order."""
@@ -324,7 +378,7 @@ def main():
 
     from vexact_b200.inferencer import PRESETS, ModelShape
 
-    shape = PRESETS["qwen3-30b-a3b-shape"]
+    shape = PRESETS[args.model]
     if args.layers:
         shape = ModelShape(**{**shape.__dict__, "num_layers": args.layers})
     if args.impl == "reference":
@@ -335,6 +389,9 @@ def main():
         return
     if args.ragged_attention:
         run_ragged_attention(args, shape)
+        return
+    if args.model != "qwen3-30b-a3b-shape":
+        run_side_model(args, shape)
         return
 
     import torch.distributed as dist
@@ -570,11 +627,7 @@ def main():
     att_ms = a0.elapsed_time(a1) / (reps * len(layers))
     kv_bytes = S * args.ctx * shape.num_kv_heads * 2 * shape.head_dim * 2
     att_bytes = kv_bytes + 2 * S * shape.num_q_heads * shape.head_dim * 2 + 4 * S * (step_inputs[0].block_tables.shape[1] + 2)
-    peaks = {}
-    try:
-        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-    except Exception:
-        pass
+    peaks = measured_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = att_bytes / (att_ms * 1e-3) / 1e9
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch at exactly this shape, from the ncu
