@@ -81,8 +81,13 @@ def test_sampler_is_batch_invariant_and_greedy_when_asked():
     assert torch.equal(t2.flip(0), tok) and torch.equal(l2.flip(0), lp)
     cfg = [SimpleNamespace(do_sample=False, temperature=1.0, top_k=None, top_p=1.0) for _ in range(24)]
     assert torch.equal(Sampler().batch_sample_token(x, cfg), x.float().argmax(-1))
+    # top-1 keeps the maximum - every token tied for it (bf16 logits do tie), as the reference's mask does
     cfg = [SimpleNamespace(do_sample=True, temperature=1.0, top_k=1, top_p=1.0) for _ in range(24)]
-    assert torch.equal(Sampler().batch_sample_token(x, cfg), x.float().argmax(-1))   # top-1 leaves one token
+    tok1 = Sampler().batch_sample_token(x, cfg)
+    xf = x.float()
+    assert torch.equal(xf.gather(1, tok1[:, None])[:, 0], xf.max(-1).values)
+    unique_max = (xf == xf.max(-1, keepdim=True).values).sum(-1) == 1
+    assert torch.equal(tok1[unique_max], xf.argmax(-1)[unique_max])
 
 
 @pytest.mark.gpu

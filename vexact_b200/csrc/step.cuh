@@ -35,6 +35,8 @@ struct StepParams {
 };
 
 __global__ void __launch_bounds__(STEP_THREADS) prepare_step_kernel(const StepParams p) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ int s_qsl[];  // [num_seqs + 1] exclusive prefix sums of tokens_this_step
   __shared__ int s_part[STEP_THREADS];
   __shared__ int s_max[STEP_THREADS];
