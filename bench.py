@@ -55,6 +55,8 @@ def parse_args():
     ap.add_argument("--model", default="qwen3-30b-a3b-shape",
                     help="another preset (qwen3-1.7b-shape, qwen2-1.5b-shape, moonlight-16b-a3b-shape) runs a "
                          "one-GPU decode step of that shape as a side measurement with its own JSON line")
+    ap.add_argument("--prefill-chunk", type=int, default=0, metavar="TOKENS",
+                    help="side measurement: one chunked-prefill step of TOKENS prompt tokens after --ctx cached ones")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="side measurement: decode attention over a ragged batch, with / without sequence order")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
@@ -248,6 +250,57 @@ def measured_peaks() -> dict:
         return {}
 
 
+def run_prefill_chunk(args, shape):
+    """Side measurement (not the contract line): one chunked-prefill step - `--prefill-chunk` prompt
+    tokens of one sequence appended to `--ctx` cached tokens - through the stage runner (eager, as a
+    prefill step runs), against the tensor-core bound of its GEMMs."""
+    from vexact_b200 import _lib
+    from vexact_b200.inferencer import StageRunner, StageWeights, StepInputs, allocate_kv_cache
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    T, page = args.prefill_chunk, args.page
+    past = args.ctx
+    total = past + T
+    pages = (total + page - 1) // page
+    weights = StageWeights.random_init(shape, 0, 1, device=device, seed=0)
+    kc, vc = allocate_kv_cache(shape, 0, shape.num_layers, pages, page, device=device, fill_std=1.0, seed=0)
+    g = torch.Generator().manual_seed(3)
+    table = torch.randperm(pages, generator=g).view(1, pages).to(torch.int32)
+    pos = torch.arange(past, total, dtype=torch.int64)
+    slots = (table[0, (pos // page)].long() * page + pos % page).to(torch.int32)
+    inp = StepInputs(input_ids=torch.randint(0, shape.vocab, (T,), generator=g).to(device), hidden_in=None,
+                     positions=pos.to(device), slot_mapping=slots.to(device),
+                     query_start_loc=torch.tensor([0, T], dtype=torch.int32, device=device),
+                     context_lens=torch.tensor([total], dtype=torch.int32, device=device),
+                     block_tables=table.to(device), max_seqlen_q=T)
+    runner = StageRunner(weights, kc, vc, 0, 1)
+    for _ in range(max(args.warmup, 2)):
+        runner.step(inp)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        runner.step(inp)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / args.steps
+    s = shape
+    per_layer = 2.0 * T * s.hidden * (s.qkv_out + s.num_q_heads * s.v_dim)          # qkv + o projections
+    if s.moe is None:
+        per_layer += 2.0 * T * s.hidden * 3 * s.ffn
+    else:
+        per_layer += 2.0 * T * s.hidden * (s.moe.num_experts + 3 * s.moe.top_k * s.moe.intermediate)
+    keys = sum(range(past + 1, total + 1))
+    attn = 2.0 * keys * s.num_q_heads * (s.k_dim + s.v_dim) * s.num_layers
+    flops = per_layer * s.num_layers + attn + 2.0 * s.hidden * s.vocab               # last-token lm_head
+    peak = float(measured_peaks().get("bf16_tflops", 1590.0))
+    print(json.dumps({"measurement": "prefill_chunk_step", "model": shape.name, "chunk": T, "cached": past,
+                      "ms_per_step": ms, "tokens_per_s": T / ms * 1e3, "tflop": flops / 1e12,
+                      "tflops": flops / ms / 1e9, "frac_of_bf16_peak": flops / ms / 1e9 / peak,
+                      "status": list(_lib.read_status())}))
+
+
 def run_side_model(args, shape):
     """Side measurement (not the contract line): one decode step of another model shape (BASELINE
     configs 2, 3, 5: dense Qwen3 / Qwen2 shapes, the Moonlight MLA + MoE shape) on one GPU through the
@@ -389,6 +442,9 @@ def main():
         return
     if args.ragged_attention:
         run_ragged_attention(args, shape)
+        return
+    if args.prefill_chunk:
+        run_prefill_chunk(args, shape)
         return
     if args.model != "qwen3-30b-a3b-shape":
         run_side_model(args, shape)
