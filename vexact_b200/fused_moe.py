@@ -129,7 +129,7 @@ def _grouped_gemm(x, w, row_scale, plan, n_out, mode):
         _lib.load().b200_moe_grouped_gemm(
             x.data_ptr(), w.data_ptr(), _lib.ptr(row_scale), out.data_ptr(), plan["tile_table"].data_ptr(),
             plan["tile_count"].data_ptr(), rows, w.shape[0], n_out, K, out.stride(0), plan["max_tiles"],
-            TILE_ROWS, mode, _lib.current_stream()),
+            plan.get("tile_rows", TILE_ROWS), mode, _lib.current_stream()),
         "b200_moe_grouped_gemm",
     )
     return out

@@ -267,10 +267,14 @@ class StageRunner:
     def _dense_plan(self, T: int, device):
         plan = self._dense_tiles.get(T)
         if plan is None:
-            rows = [(0, r, min(TILE_ROWS, T - r), 0) for r in range(0, T, TILE_ROWS)]
+            # one "expert" holding every token; token tiles as wide as the UMMA allows (a tile's width
+            # never changes a token's result, only how often the weights are re-read)
+            tile = max(TILE_ROWS, min(256, (T + 15) // 16 * 16))
+            tile = tile // 64 * 64 if tile >= 64 else tile
+            rows = [(0, r, min(tile, T - r), 0) for r in range(0, T, tile)]
             plan = dict(tile_table=torch.tensor(rows, dtype=torch.int32, device=device),
                         tile_count=torch.tensor([len(rows)], dtype=torch.int32, device=device),
-                        max_tiles=len(rows))
+                        max_tiles=len(rows), tile_rows=tile)
             self._dense_tiles[T] = plan
         return plan
 
