@@ -199,3 +199,22 @@ def test_hf_dropin_attention_and_aten_overrides():
         # (rope adds two rounded products that may cancel: absolute tolerance of ~2 ulp of the inputs)
         torch.testing.assert_close(vc[li].float(), vc2[li].float(), rtol=2 ** -6, atol=5e-2)
         torch.testing.assert_close(kc[li].float(), kc2[li].float(), rtol=2 ** -6, atol=5e-2)
+
+
+@pytest.mark.gpu
+def test_dense_mlp_routes_agree_bitwise():
+    """The dense MLP runs fused (few tokens) or as two GEMMs + an elementwise kernel (many tokens):
+    a token must get the same bits on both routes."""
+    from vexact_b200.inferencer import QWEN3_1P7B, ModelShape, StageRunner, StageWeights, allocate_kv_cache
+
+    shape = ModelShape(**{**QWEN3_1P7B.__dict__, "num_layers": 1})
+    w = StageWeights.random_init(shape, 0, 1, device="cuda", seed=3)
+    kc, vc = allocate_kv_cache(shape, 0, 1, 4, 16, device="cuda")
+    r = StageRunner(w, kc, vc, 0, 1)
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(300, shape.hidden, generator=g).bfloat16().cuda()
+    lw = w.layers[0]
+    big = r._dense_mlp(x, lw.gate_up, lw.down, shape.ffn)                 # 300 tokens: split route
+    small = r._dense_mlp(x[:64], lw.gate_up, lw.down, shape.ffn)         # 64 tokens: fused route
+    one = r._dense_mlp(x[17:18], lw.gate_up, lw.down, shape.ffn)
+    assert torch.equal(big[:64], small) and torch.equal(big[17:18], one)

@@ -267,10 +267,7 @@ class StageRunner:
     def _dense_plan(self, T: int, device):
         plan = self._dense_tiles.get(T)
         if plan is None:
-            # one "expert" holding every token; token tiles as wide as the UMMA allows (a tile's width
-            # never changes a token's result, only how often the weights are re-read)
-            tile = max(TILE_ROWS, min(256, (T + 15) // 16 * 16))
-            tile = tile // 64 * 64 if tile >= 64 else tile
+            tile = TILE_ROWS
             rows = [(0, r, min(tile, T - r), 0) for r in range(0, T, tile)]
             plan = dict(tile_table=torch.tensor(rows, dtype=torch.int32, device=device),
                         tile_count=torch.tensor([len(rows)], dtype=torch.int32, device=device),
@@ -333,9 +330,23 @@ class StageRunner:
                                (a.qk_nope + a.qk_rope) ** -0.5, inp.max_seqlen_q, seq_order=inp.seq_order)
         return linear(attn.view(T, heads * a.v_head), lw.o)
 
+    # Above this many tokens the fused SwiGLU epilogue (two of the four epilogue warps do the
+    # activation math of a whole 128 x 256 tile) costs more than it saves: two plain GEMMs and the
+    # elementwise kernel are used instead.  Both routes round at the same points, so a token's result
+    # is the same bits either way (tests/test_gpu_model.py).
+    DENSE_FUSED_MAX_TOKENS = 64
+
     def _dense_mlp(self, xn, gate_up, down, width):
-        plan = self._dense_plan(xn.shape[0], xn.device)
-        act = _grouped_gemm(xn, gate_up.view(1, 2 * width, self.shape.hidden), None, plan, width, mode=1)
+        T = xn.shape[0]
+        if T <= self.DENSE_FUSED_MAX_TOKENS:
+            plan = self._dense_plan(T, xn.device)
+            act = _grouped_gemm(xn, gate_up.view(1, 2 * width, self.shape.hidden), None, plan, width, mode=1)
+        else:
+            g = linear(xn, gate_up[:width])
+            u = linear(xn, gate_up[width:])
+            act = torch.empty_like(g)
+            _lib.check(_lib.load().b200_swiglu_scale(g.data_ptr(), u.data_ptr(), None, act.data_ptr(), T, width,
+                                                     _lib.current_stream()), "b200_swiglu_scale")
         return linear(act, down)
 
     def _mlp_block(self, lw: LayerWeights, xn: torch.Tensor) -> torch.Tensor:
