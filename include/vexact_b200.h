@@ -220,6 +220,11 @@ int b200_moe_grouped_gemm_noalloc(const void* x, const void* w, const void* row_
 int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out, long long rows,
                       int I, void* stream);
 
+/* Same with gate and up read from rows in_row_stride elements apart (e.g. the two column halves of one
+ * [rows, 2I] GEMM output); out is [rows, I] contiguous. */
+int b200_swiglu_scale_strided(const void* gate, const void* up, const void* row_scale, void* out, long long rows,
+                              int I, long long in_row_stride, void* stream);
+
 /* ---- vexact/batch_invariant_ops/group_gemm/kernel/moe.py:131 moe_gather
  *      (+ optional bf16 add of `addend` [T, H] afterwards, e.g. the shared experts'
  *      output of modeling_deepseek_v3.py:217). */

@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200_moe_grouped_gemm": [P, P, P, P, P, P, LL, I, I, I, LL, I, I, I, P],
     "b200_moe_grouped_gemm_noalloc": [P, P, P, P, P, LL, I, I, I, LL, I, P],
     "b200_swiglu_scale": [P, P, P, P, LL, I, P],
+    "b200_swiglu_scale_strided": [P, P, P, P, LL, I, LL, P],
     "b200_moe_unpermute_reduce": [P, P, P, P, LL, I, I, P],
     "b200_moe_unpermute_add_rmsnorm": [P, P, P, P, P, P, P, LL, I, I, F, I, P],
 }

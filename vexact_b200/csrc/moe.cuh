@@ -496,16 +496,18 @@ moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __re
 __global__ void __launch_bounds__(256)
 swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
                     const __nv_bfloat16* __restrict__ row_scale, __nv_bfloat16* __restrict__ out, long long rows,
-                    int I) {
+                    int I, long long in_stride) {
   pdl_trigger();
   pdl_wait();
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
   if (i >= rows * I) return;
-  const float g = bf2f(gate[i]);
-  const float u = bf2f(up[i]);
+  const long long r = i / I;
+  const long long src = r * in_stride + (i - r * I);
+  const float g = bf2f(gate[src]);
+  const float u = bf2f(up[src]);
   const float sg = round_bf(g / (1.0f + expf(-g)));
   float h = round_bf(sg * u);
-  if (row_scale) h = round_bf(h * bf2f(row_scale[i / I]));
+  if (row_scale) h = round_bf(h * bf2f(row_scale[r]));
   out[i] = f2bf(h);
 }
 
@@ -623,14 +625,19 @@ extern "C" int b200_moe_unpermute_add_rmsnorm(const void* y, const void* scatter
   return launch_status();
 }
 
-extern "C" int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out,
-                                 long long rows, int I, void* stream) {
+extern "C" int b200_swiglu_scale_strided(const void* gate, const void* up, const void* row_scale, void* out,
+                                         long long rows, int I, long long in_row_stride, void* stream) {
   using namespace b200;
-  if (!gate || !up || !out || rows < 0 || I <= 0) return B200_ERR_ARG;
+  if (!gate || !up || !out || rows < 0 || I <= 0 || in_row_stride < I) return B200_ERR_ARG;
   if (rows == 0) return B200_OK;
   const long long n = rows * I;
-  launch_k(swiglu_scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
-      (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (const __nv_bfloat16*)row_scale, (__nv_bfloat16*)out,
-      rows, I);
+  launch_k(swiglu_scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+           (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (const __nv_bfloat16*)row_scale, (__nv_bfloat16*)out,
+           rows, I, in_row_stride);
   return launch_status();
+}
+
+extern "C" int b200_swiglu_scale(const void* gate, const void* up, const void* row_scale, void* out,
+                                 long long rows, int I, void* stream) {
+  return b200_swiglu_scale_strided(gate, up, row_scale, out, rows, I, I, stream);
 }

@@ -21,6 +21,7 @@ import torch
 from . import _lib
 
 TILE_ROWS = 64  # largest token tile of the grouped GEMM (rows of one expert per tile)
+FUSED_SWIGLU_MAX_ROWS_PER_EXPERT = 64  # mean rows per expert up to which fc1 keeps its fused SwiGLU epilogue
 
 
 def max_token_tiles(num_rows: int, num_experts: int, tile_rows: int = TILE_ROWS) -> int:
@@ -210,7 +211,20 @@ def fused_moe_forward(
     if fc1_1_2_weight is not None:
         assert fc1_1_2_weight.dtype == torch.bfloat16 and fc1_1_2_weight.is_contiguous()
         I = fc1_1_2_weight.shape[1] // 2
-        h = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, plan["row_scale"], plan, I, mode=1)
+        if T * k > FUSED_SWIGLU_MAX_ROWS_PER_EXPERT * num_experts:
+            # many rows per expert (prefill): the fused SwiGLU epilogue, where two of the four epilogue
+            # warps do a tile's activation math, would bound the kernel; one plain grouped GEMM over the
+            # gate and up rows plus the elementwise kernel rounds at the same points (same bits)
+            gu = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, None, plan, 2 * I, mode=0)
+            h = torch.empty((gu.shape[0], I), device=gu.device, dtype=torch.bfloat16)
+            _lib.check(
+                _lib.load().b200_swiglu_scale_strided(gu.data_ptr(), gu.data_ptr() + I * gu.element_size(),
+                                                      plan["row_scale"].data_ptr(), h.data_ptr(), gu.shape[0], I,
+                                                      gu.stride(0), _lib.current_stream()),
+                "b200_swiglu_scale_strided",
+            )
+        else:
+            h = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, plan["row_scale"], plan, I, mode=1)
     else:
         if fc1_1_weight is None or fc1_2_weight is None:
             raise ValueError("pass fc1_1_weight and fc1_2_weight, or fc1_1_2_weight")
