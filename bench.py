@@ -250,6 +250,21 @@ def measured_peaks() -> dict:
         return {}
 
 
+def recorded_traffic(kernel: str, batch: int, ctx: int, page: int):
+    """DRAM bytes per launch that ncu measured for `kernel` on this workload, from the tracked summary
+    next to the other profiler summaries; None when that workload was never captured."""
+    try:
+        for line in open(os.path.join(ROOT, "profiles", "roofline_traffic.txt")):
+            if line.startswith("#") or "|" not in line:
+                continue
+            f = [x.strip() for x in line.split("|")]
+            if len(f) == 5 and f[0] == kernel and (int(f[1]), int(f[2]), int(f[3])) == (batch, ctx, page):
+                return int(f[4])
+    except (OSError, ValueError):
+        pass
+    return None
+
+
 def run_prefill_chunk(args, shape):
     """Side measurement (not the contract line): one chunked-prefill step - `--prefill-chunk` prompt
     tokens of one sequence appended to `--ctx` cached tokens - through the stage runner (eager, as a
@@ -686,10 +701,9 @@ def main():
     peaks = measured_peaks()
     peak = float(peaks.get("hbm_gbs", 6650.0))
     achieved = att_bytes / (att_ms * 1e-3) / 1e9
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch at exactly this shape, from the ncu
-    # capture summarised in profiles/hot_kernels_ncu_full.md (2.152 GB + 5.1 MB); other shapes: null
-    ncu_traffic = 2157270000 if (S, args.ctx, args.page) == (512, 2048, 16) else None
-    att = {"bound": "hbm", "kernel": "paged_attn_tc_kernel<128,128,16,3,3>", "achieved": achieved, "peak": peak,
+    kernel_name = "paged_attn_tc_kernel<128,128,16,3,3>"
+    ncu_traffic = recorded_traffic(kernel_name, S, args.ctx, args.page)
+    att = {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
            "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback 6650 GB/s", "unit": "GB/s",
            "frac": achieved / peak, "traffic": ncu_traffic, "algorithmic_bytes_per_launch": att_bytes,
            "ms_per_launch": att_ms}

@@ -25,7 +25,13 @@
 extern "C" {
 #endif
 
+/* Changes whenever an exported signature changes (currently 2). */
 int b200_abi_version(void);
+
+/* Hash of the sources and compiler flags the binary was built from: the Python loader compares it with
+ * the sources next to it, so that a library left over from an older checkout is never bound to newer
+ * argument lists.  No counterpart in the reference (it ships no compiled code). */
+const char* b200_source_hash(void);
 
 /* Self-test of the bounded device wait: one CTA waits limit_us microseconds (1..1000000) on an mbarrier that
  * nothing completes; the wait must expire, put {1 (wait expired), 999, ...} into the status word and let the

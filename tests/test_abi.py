@@ -27,7 +27,7 @@ def test_ctypes_signatures_cover_header(lib):
     from vexact_b200 import _lib
 
     assert sorted(_lib.SIGNATURES) == _declared_symbols()
-    assert lib.b200_abi_version() == 1
+    assert lib.b200_abi_version() == _lib.ABI_VERSION == 2
 
 
 def test_argument_validation_without_gpu(lib):
@@ -45,3 +45,29 @@ def test_no_product_import_of_oracle():
             if f.endswith(".py"):
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", src, flags=re.M), f
+
+
+def test_library_carries_the_hash_of_its_sources(lib):
+    """The loader binds argument lists by position, so a library built from other sources must be
+    refused: the hash compiled into the binary has to equal the hash of the sources beside it."""
+    import ctypes as C
+
+    from vexact_b200 import _lib, build
+
+    text = open(os.path.join(ROOT, "include", "vexact_b200.h")).read()
+    assert re.search(r"const\s+char\s*\*\s*b200_source_hash\s*\(", text)
+    fn = lib.b200_source_hash
+    fn.restype = C.c_char_p
+    assert fn().decode() == build._source_hash() == build.built_hash()
+
+    class Stale:
+        class b200_source_hash:  # noqa: N801  (stands in for the ctypes function object)
+            restype = None
+
+            def __new__(cls):
+                return b"0" * 64
+
+    import pytest
+
+    with pytest.raises(_lib.B200Error, match="other sources"):
+        _lib._check_fresh(Stale)

@@ -61,6 +61,28 @@ class B200Error(RuntimeError):
     pass
 
 
+ABI_VERSION = 2
+
+
+def _check_fresh(lib) -> None:
+    """Refuse a library built from other sources than the ones beside this file: its entry points
+    may take other argument lists than SIGNATURES declares."""
+    from . import build
+
+    if not build.sources_present():
+        return
+    try:
+        fn = lib.b200_source_hash
+    except AttributeError:
+        raise B200Error(f"{_LIB_PATH} predates the source-hash check: rebuild it with "
+                        "`python -m vexact_b200.build --force`") from None
+    fn.restype = C.c_char_p
+    have, want = fn().decode(), build._source_hash()
+    if have != want:
+        raise B200Error(f"{_LIB_PATH} was built from other sources (hash {have[:12]}, sources {want[:12]}): "
+                        "rebuild it with `python -m vexact_b200.build`")
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
@@ -78,10 +100,14 @@ def load() -> C.CDLL:
                     "(there is no fallback implementation)"
                 )
             lib = C.CDLL(str(_LIB_PATH))
+            _check_fresh(lib)
             for name, argtypes in SIGNATURES.items():
                 fn = getattr(lib, name)
                 fn.argtypes = argtypes
                 fn.restype = C.c_int
+            if lib.b200_abi_version() != ABI_VERSION:
+                raise B200Error(f"{_LIB_PATH} has ABI version {lib.b200_abi_version()}, this binding needs "
+                                f"{ABI_VERSION}: rebuild it with `python -m vexact_b200.build --force`")
             _lib = lib
     return _lib
 

@@ -303,6 +303,12 @@ def set_batch_invariant_mode(enabled: bool = True):
 AttentionBlockSize = namedtuple("AttentionBlockSize", ["block_m", "block_n"])
 
 
-def get_batch_invariant_attention_block_size() -> AttentionBlockSize:
-    """Block sizes of the attention kernel: 8-column query tiles, 64-key KV blocks."""
-    return AttentionBlockSize(block_m=8, block_n=64)
+def get_batch_invariant_attention_block_size(head_dim: int = 128, decode: bool = False) -> AttentionBlockSize:
+    """Tiling of the default (tcgen05) paged-attention kernel: block_n = 128 keys per KV block for
+    every shape; block_m = (query position, head) columns per tile: 16 in a decode step, otherwise 64
+    for head_dim 128 and 32 for the 192 / 128 MLA dims.  (Head dims the tcgen05 kernel does not cover
+    run the mma.sync kernel: 8 columns, 64-key blocks.)  A row's arithmetic does not depend on block_m.
+    Reference: batch_invariant_ops.py:787 (same name, reports its own kernel's tiles)."""
+    if head_dim not in (128, 192):
+        return AttentionBlockSize(block_m=8, block_n=64)
+    return AttentionBlockSize(block_m=16 if decode else (64 if head_dim == 128 else 32), block_n=128)

@@ -16,7 +16,6 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 OUT_DIR = PKG_DIR / "_C"
 LIB_PATH = OUT_DIR / "libvexact_b200.so"
-STAMP = OUT_DIR / "libvexact_b200.stamp"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -42,13 +41,36 @@ def _source_hash() -> str:
     return h.hexdigest()
 
 
+def built_hash() -> str | None:
+    """Source hash compiled into the library on disk (b200_source_hash), None when there is none."""
+    if not LIB_PATH.exists():
+        return None
+    try:
+        import ctypes
+
+        lib = ctypes.CDLL(str(LIB_PATH))
+        fn = lib.b200_source_hash
+        fn.restype = ctypes.c_char_p
+        return fn().decode()
+    except (OSError, AttributeError):
+        return None
+
+
+def sources_present() -> bool:
+    return (CSRC / "lib.cu").exists()
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if sources changed; return its path."""
+    """Compile the library unless the one on disk was built from exactly these sources; return its path.
+
+    The hash of the sources and flags is compiled into the library itself, so a stale library (sources
+    updated by a checkout, library left over from before) is recognised whatever files sit beside it."""
     OUT_DIR.mkdir(exist_ok=True)
     want = _source_hash()
-    if not force and LIB_PATH.exists() and STAMP.exists() and STAMP.read_text().strip() == want:
+    if not force and built_hash() == want:
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), str(CSRC / "lib.cu"), "-o", str(LIB_PATH)]
+    cmd = [_nvcc(), *NVCC_FLAGS, f'-DB200_SOURCE_HASH="{want}"', "-I", str(CSRC), str(CSRC / "lib.cu"), "-o",
+           str(LIB_PATH)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -58,7 +80,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
     if verbose:
         print(res.stderr, file=sys.stderr)
-    STAMP.write_text(want)
     return LIB_PATH
 
 

@@ -60,6 +60,7 @@ struct AttnParams {
   int tc_slots;          // tile positions walked: tc_tiles rounded up to whole rounds of the grid
   int num_seqs;
   const int* seq_order;  // [num_seqs] sequence of each slot (longest first), or null
+  int max_seqlen_q;      // the caller's bound on queries per sequence: it sized the tile grid
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -122,6 +123,12 @@ paged_attn_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constan
   const int q_len = p.cu_seqlens_q[seq + 1] - q_start;
   const int kv_len = p.seqused_k[seq];
   const int tile_pos0 = blockIdx.x * p.pos_per_tile;  // first query index (within the sequence) of this tile
+  if (q_len > p.max_seqlen_q || (q_len > 0 && kv_len < q_len)) {
+    // more queries than the grid was sized for, or fewer keys than queries: the tail rows would be
+    // skipped silently / the first query's absolute position would be negative.  Flag it, compute nothing.
+    if (lane == 0) report_status(B200_STATUS_BAD_INDEX, seq);
+    return;
+  }
   if (q_len <= 0 || kv_len <= 0 || tile_pos0 >= q_len) return;
   const int q_abs0 = kv_len - q_len;  // absolute position of the sequence's first query
 
@@ -365,13 +372,8 @@ template <int DK, int DV, int STAGES>
 inline int attn_launch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid,
                        cudaStream_t st) {
   constexpr int smem = STAGES * ATT_BN * (DK + DV) * 2 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_attn_kernel<DK, DV, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static PerDeviceFlags attr_set;
+  if (int rc = set_max_dyn_smem_once(attr_set, paged_attn_kernel<DK, DV, STAGES>, smem)) return rc;
   launch_k(paged_attn_kernel<DK, DV, STAGES>, grid, dim3(32), (size_t)smem, st, tk, tv, p);
   return launch_status();
 }
@@ -479,6 +481,7 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
                        vc_head_stride, p.box_tokens);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  p.max_seqlen_q = max_seqlen_q;
   if (num_seqs > 65535 || num_kv_heads * p.head_chunks > 65535) return B200_ERR_SHAPE;
   const int hh = group < 8 ? group : 8;
   if (attn_use_tensor_memory() && dv == 128 && (dk == 128 || dk == 192) && q_tok_stride % 8 == 0 &&

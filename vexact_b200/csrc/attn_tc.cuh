@@ -102,6 +102,12 @@ __device__ __forceinline__ AtcRaw atc_raw(const AttnParams& p, int lin) {
   r.q_start = p.cu_seqlens_q[r.seq];
   r.q_end = p.cu_seqlens_q[r.seq + 1];
   r.kv_len = p.seqused_k[r.seq];
+  const int q_len = r.q_end - r.q_start;
+  if (q_len > p.max_seqlen_q || (q_len > 0 && r.kv_len < q_len)) {
+    // more queries than the tile grid covers, or fewer keys than queries: skip the tile, flag the sequence
+    report_status(B200_STATUS_BAD_INDEX, r.seq);
+    r.eff = -1;
+  }
   return r;
 }
 
@@ -687,13 +693,8 @@ inline int attn_tc_launch(const CUtensorMap& tk, const CUtensorMap& tv, const At
                           cudaStream_t st) {
   constexpr int smem = ATC_BN * (KST * DK + VST * DV) * 2 + 2 * (DK / 64) * NC * 128 + 2 * NC * 128 + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(paged_attn_tc_kernel<DK, DV, NC, KST, VST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static PerDeviceFlags attr_set;
+  if (int rc = set_max_dyn_smem_once(attr_set, paged_attn_tc_kernel<DK, DV, NC, KST, VST>, smem)) return rc;
   const int nctas = p.tc_tiles < sm_count() ? p.tc_tiles : sm_count();
   (void)grid;
   launch_k(paged_attn_tc_kernel<DK, DV, NC, KST, VST>, dim3((unsigned)nctas), dim3(ATC_THREADS), (size_t)smem, st, tk,

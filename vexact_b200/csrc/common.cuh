@@ -15,6 +15,8 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <atomic>
+
 #define B200_OK 0
 #define B200_ERR_ARG (-1)
 #define B200_ERR_SHAPE (-2)
@@ -135,6 +137,46 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
   const int mode = pdl_mode();
   cfg.numAttrs = (mode == 1 || (mode == 2 && smem == 0)) ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Facts and one-time settings that belong to a device, not to the process: a process that drives
+// several GPUs gets each of them looked up / set once, with that device current.
+constexpr int B200_MAX_DEVICES = 64;
+
+struct PerDeviceFlags {
+  std::atomic<int> v[B200_MAX_DEVICES];  // static storage: zero-initialised
+};
+
+inline int current_device_index() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B200_MAX_DEVICES) return -1;
+  return dev;
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute is per device).
+template <typename KernelT>
+inline int set_max_dyn_smem_once(PerDeviceFlags& done, KernelT kernel, int bytes) {
+  const int dev = current_device_index();
+  if (dev < 0) return B200_ERR_LAUNCH;
+  if (done.v[dev].load(std::memory_order_acquire) == 0) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return B200_ERR_LAUNCH;
+    done.v[dev].store(1, std::memory_order_release);
+  }
+  return B200_OK;
+}
+
+// SM count of the current device (cached per device).
+inline int sm_count() {
+  static PerDeviceFlags cache;
+  const int dev = current_device_index();
+  if (dev < 0) return 148;
+  int n = cache.v[dev].load(std::memory_order_acquire);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cache.v[dev].store(n, std::memory_order_release);
+  }
+  return n;
 }
 
 inline int launch_status() {

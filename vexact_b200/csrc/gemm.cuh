@@ -340,16 +340,6 @@ inline int make_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
 }
 
-inline int sm_count() {
-  static int n = []() {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
-    return v;
-  }();
-  return n;
-}
-
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 // Development knobs (unset in normal use): B200_GEMM_XBOX = rows per activation box of the grouped
@@ -362,13 +352,8 @@ inline int env_int(const char* name, int dflt) {
 template <bool SWIGLU>
 inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams& p, long long max_tiles,
                        cudaStream_t st) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_ws_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             GEMM_SMEM_BUDGET) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    attr_set = true;
-  }
+  static PerDeviceFlags attr_set;
+  if (int rc = set_max_dyn_smem_once(attr_set, gemm_ws_kernel<SWIGLU>, GEMM_SMEM_BUDGET)) return rc;
   const int atom_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
   const int exch_bytes_pre = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
   // K atoms per stage: fewer, larger stages cut the per-stage barrier round trips; keep >= 3 stages.

@@ -19,6 +19,8 @@ namespace b200 {
 __global__ void wait_expiry_selftest_kernel(unsigned long long limit_ns, int* out_flag) {
   __shared__ uint64_t bar;
   __shared__ int abort_mem;
+  pdl_trigger();
+  pdl_wait();  // launched through launch_k like every kernel here: wait before touching global memory
   if (threadIdx.x == 0) {
     abort_mem = 0;
     ptx::mbar_init(ptx::smem_u32(&bar), 1);
@@ -53,4 +55,12 @@ extern "C" int b200_status_read(int* host_out4, void* stream) {
   return B200_OK;
 }
 
-extern "C" int b200_abi_version(void) { return 1; }
+// Bumped whenever an exported signature changes.
+extern "C" int b200_abi_version(void) { return 2; }
+
+// Hash of the sources and compiler flags this binary was built from (set by the build script);
+// the loader compares it with the sources beside it and refuses a stale library.
+#ifndef B200_SOURCE_HASH
+#define B200_SOURCE_HASH "unknown"
+#endif
+extern "C" const char* b200_source_hash(void) { return B200_SOURCE_HASH; }

@@ -19,7 +19,16 @@
 //     the tile count and every tile entry it will read before the GEMM reads them (both
 //     kernels are on the caller's stream, in order).  Two calls that overlap on the GPU (on
 //     different streams) race on the array: serialise them.
+//   * The looked-up address is cached per device for the life of the process.  cudaDeviceReset()
+//     destroys the context the address belongs to: after a reset the cached value is stale and
+//     this entry point must not be used again in that process.
+//   * cu_seqlens comes from the caller, so it is checked on the device: a group whose bounds are
+//     not 0 <= cu_seqlens[g] <= cu_seqlens[g+1] <= x_rows is clipped to the valid rows (dropped
+//     when it is decreasing) and B200_STATUS_BAD_INDEX with the group id is left in the status
+//     word; no tile ever names a row outside [0, x_rows).
 #pragma once
+#include <atomic>
+
 #include "gemm.cuh"
 
 namespace b200 {
@@ -32,30 +41,34 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 static __device__ __align__(256) int4 g_noalloc_tiles[NOALLOC_MAX_TILES + 1];
 
 // Device address of the array on the current device (looked up once per device).
+// Host threads may race on the first call: every racer looks up the same value, the slot is atomic.
 inline int noalloc_tiles_ptr(int4** out) {
-  static int4* ptrs[NOALLOC_MAX_DEVICES] = {};
+  static std::atomic<int4*> ptrs[NOALLOC_MAX_DEVICES];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return B200_ERR_LAUNCH;
-  if (ptrs[dev] == nullptr) {
+  int4* cached = ptrs[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_tiles) != cudaSuccess || p == nullptr) return B200_ERR_LAUNCH;
-    ptrs[dev] = static_cast<int4*>(p);
+    cached = static_cast<int4*>(p);
+    ptrs[dev].store(cached, std::memory_order_release);
   }
-  *out = ptrs[dev];
+  *out = cached;
   return B200_OK;
 }
 
 // One CTA: tiles of at most `tile_rows` consecutive rows per group, in group order.
 __global__ void __launch_bounds__(1024)
 tiles_from_cu_seqlens_kernel(const int* __restrict__ cu_seqlens, int num_groups, int tile_rows,
-                             int4* __restrict__ table /* entry 0 = count */, int max_tiles) {
+                             int4* __restrict__ table /* entry 0 = count */, int max_tiles, int x_rows) {
   __shared__ int first_tile[NOALLOC_MAX_GROUPS + 1];
   const int g = threadIdx.x;
   int rows = 0, r0 = 0;
   if (g < num_groups) {
-    r0 = cu_seqlens[g];
-    rows = cu_seqlens[g + 1] - r0;
-    if (rows < 0) rows = 0;
+    const int lo = cu_seqlens[g], hi = cu_seqlens[g + 1];
+    if (lo < 0 || hi < lo || hi > x_rows) report_status(B200_STATUS_BAD_INDEX, g);
+    r0 = min(max(lo, 0), x_rows);
+    rows = hi < lo ? 0 : min(max(hi, r0), x_rows) - r0;  // a decreasing group is dropped, an overrun clipped
   }
   const int tiles = (rows + tile_rows - 1) / tile_rows;
   first_tile[g] = tiles;
@@ -105,8 +118,9 @@ extern "C" int b200_moe_grouped_gemm_noalloc(const void* x, const void* w, const
   int rc = noalloc_tiles_ptr(&table);
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
+  if (x_rows > 0x7fffffffLL) return B200_ERR_SHAPE;
   tiles_from_cu_seqlens_kernel<<<1, 1024, 0, st>>>((const int*)cu_seqlens, num_groups, kTileRows, table,
-                                                   NOALLOC_MAX_TILES);
+                                                   NOALLOC_MAX_TILES, (int)x_rows);
   rc = launch_status();
   if (rc) return rc;
   return b200_moe_grouped_gemm(x, w, row_scale, out, table + 1, table, x_rows, num_groups, n_out, K,
