@@ -59,6 +59,9 @@ def parse_args():
                     help="side measurement: one chunked-prefill step of TOKENS prompt tokens after --ctx cached ones")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="side measurement: decode attention over a ragged batch, with / without sequence order")
+    ap.add_argument("--skew", action="store_true",
+                    help="side measurement: one MoE layer of the model with near-uniform routing and with a "
+                         "Zipf(1.1) router bias: rows per expert, token tiles, fc1 / fc2 time")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
                     help="side measurement: time one causal prefill attention call of QLEN queries on the "
                          "model's head shape (context --ctx if larger) and print its own JSON line")
@@ -404,6 +407,72 @@ def run_ragged_attention(args, shape):
     print(json.dumps(res))
 
 
+def zipf_router_bias(num_experts: int, seed: int, scale: float = 8.0) -> torch.Tensor:
+    """Per-expert router-logit bias ~ Zipf(1.1) over a seeded random ranking of the experts (the skewed
+    variant of the workload): rank r gets scale / r^1.1, so a few experts draw most of the tokens."""
+    g = torch.Generator().manual_seed(seed)
+    rank = torch.randperm(num_experts, generator=g).float() + 1.0
+    return (scale / rank.pow(1.1)).to(torch.bfloat16)
+
+
+def run_skew(args, shape):
+    """Side measurement (not the contract line): the expert GEMMs of one MoE layer at batch `--batch`,
+    under near-uniform routing (router std 0.02) and under the Zipf(1.1) router bias."""
+    import vexact_b200 as vb
+    from vexact_b200 import _lib
+    from vexact_b200.fused_moe import FUSED_SWIGLU_MAX_ROWS_PER_EXPERT, _grouped_gemm, _permute
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    m, H, T = shape.moe, shape.hidden, args.batch
+    E, k, I = m.num_experts, m.top_k, m.intermediate
+    g = torch.Generator(device=dev).manual_seed(0)
+    hidden = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    gate_up = (torch.randn(E, 2 * I, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    down = (torch.randn(E, H, I, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    router = (torch.randn(E, H, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    flush = torch.zeros(160 * 1024 * 1024, dtype=torch.float16, device=dev)     # 320 MB > L2
+    peak = float(measured_peaks().get("hbm_gbs", 6650.0))
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            flush.add_(1)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2] * 1e3      # us
+
+    res = {"measurement": "moe_layer_skew", "model": shape.name, "tokens": T, "experts": E, "top_k": k}
+    for name, bias in (("uniform", None), ("zipf_1.1", zipf_router_bias(E, seed=11).to(dev))):
+        logits = vb.linear(hidden, router, bias)
+        rw, sel = vb.route_softmax_topk(logits, k, True)
+        counts = torch.bincount(sel.flatten(), minlength=E)
+        plan = _permute(sel, rw, hidden, E)
+        xp, rs = plan["x_perm"], plan["row_scale"]
+        hit = int((counts > 0).sum())
+        fused = T * k <= FUSED_SWIGLU_MAX_ROWS_PER_EXPERT * E
+        fc1 = (lambda: _grouped_gemm(xp, gate_up, rs, plan, I, mode=1)) if fused else \
+              (lambda: _grouped_gemm(xp, gate_up, None, plan, 2 * I, mode=0))
+        hmid = _grouped_gemm(xp, gate_up, rs, plan, I, mode=1)
+        e = {"rows_per_expert_max": int(counts.max()), "rows_per_expert_mean": float(counts.float().mean()),
+             "experts_hit": hit, "token_tiles": int(plan["tile_count"].item()),
+             "fc1_us": timed(fc1), "fc2_us": timed(lambda: _grouped_gemm(hmid, down, None, plan, H, mode=0)),
+             "layer_us": timed(lambda: vb.fused_moe_forward(E, rw, sel, hidden, fc2_weight=down, fc1_1_2_weight=gate_up))}
+        w1, w2 = hit * 2 * I * H * 2, hit * H * I * 2
+        e["fc1_frac_of_hbm"] = (w1 + T * k * (H + I) * 2) / (e["fc1_us"] * 1e-6) / 1e9 / peak
+        e["fc2_frac_of_hbm"] = (w2 + T * k * (H + I) * 2) / (e["fc2_us"] * 1e-6) / 1e9 / peak
+        res[name] = e
+    res["status"] = list(_lib.read_status())
+    print(json.dumps(res))
+
+
 def run_prefill_attention(args, shape):
     """Side measurement (not the contract line): one sequence's causal prefill through paged attention."""
     import vexact_b200 as vb
@@ -451,6 +520,9 @@ def main():
         shape = ModelShape(**{**shape.__dict__, "num_layers": args.layers})
     if args.impl == "reference":
         run_reference(args, shape, rank)
+        return
+    if args.skew:
+        run_skew(args, shape)
         return
     if args.prefill_attention:
         run_prefill_attention(args, shape)

@@ -1,7 +1,7 @@
-"""BASELINE configurations 2, 3 and 5 at (or near) their stated sizes, checked through
+"""BASELINE configurations 2, 3, 4 and 5 at (or near) their stated sizes, checked through
 size-independent properties: a sequence's logits are the same bits alone or inside the full batch,
 captured-graph replay equals eager execution, and chunked prefill equals one-shot prefill.
-(Configuration 1 is the operator sweep in test_gpu_gemm / test_gpu_rowops; configuration 4 is bench.py.)"""
+(Configuration 1 is the operator sweep in test_gpu_gemm / test_gpu_rowops.)"""
 import dataclasses
 
 import pytest
@@ -33,11 +33,14 @@ def _single(inp, s, dev):
         block_tables=inp.block_tables[s:s + 1].contiguous())
 
 
-def _check_decode_invariance(shape, S, ctx, page, picks):
+def _check_decode_invariance(shape, S, ctx, page, picks, router_bias=None):
     from vexact_b200.inferencer import StageRunner, StageWeights, allocate_kv_cache
 
     dev = torch.device("cuda")
     w = StageWeights.random_init(shape, device=dev, seed=5)
+    if router_bias is not None:
+        for lw in w.layers:
+            lw.router_logit_bias = router_bias.to(dev)
     inp, nblocks = _decode_inputs(shape, S, ctx, page, dev, seed=6)
     kc, vc = allocate_kv_cache(shape, 0, shape.num_layers, nblocks, page, device=dev, fill_std=1.0, seed=7)
     r = StageRunner(w, kc, vc)
@@ -62,6 +65,21 @@ def test_config2_qwen3_1p7b_decode_batch64_ctx1024_page16():
     from vexact_b200.inferencer import QWEN3_1P7B
 
     _check_decode_invariance(QWEN3_1P7B, S=64, ctx=1024, page=16, picks=(0, 17, 63))
+
+
+@pytest.mark.parametrize("skew", [False, True])
+def test_config4_qwen3_30b_a3b_shape_decode_batch512_ctx2048_page16(skew):
+    """Full width (hidden 2048, 32 / 4 heads, 128 experts top-8, expert FFN 768, vocab 151936), 2 of the
+    48 layers, batch 512 x 2048-token context in 16-token pages: sequences 0, 255 and 511 get the same
+    bits alone as inside the batch of 512, and a captured-graph replay equals eager execution; once with
+    std-0.02 routers (near-uniform expert load) and once with a Zipf(1.1) router bias (tiles of up to 64
+    rows per expert, the many-rows-per-expert route of fc1)."""
+    from bench import zipf_router_bias
+    from vexact_b200.inferencer import QWEN3_30B_A3B
+
+    shape = dataclasses.replace(QWEN3_30B_A3B, num_layers=2)
+    bias = zipf_router_bias(shape.moe.num_experts, seed=11) if skew else None
+    _check_decode_invariance(shape, S=512, ctx=2048, page=16, picks=(0, 255, 511), router_bias=bias)
 
 
 def test_config5_moonlight_shape_decode_batch256_ctx4096():

@@ -1,0 +1,179 @@
+"""The reference-shaped entry points on the GPU: `Inferencer.infer(requests)` over `InputBuffers`,
+`CudaGraphManager` buckets and `PPMessager`-shaped hand-off (reference: tests/test_inferencer.py:180-297
+single-process pipeline ranks, :301-595 CUDA graph vs eager bitwise)."""
+from types import SimpleNamespace as NS
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+DEV = "cuda"
+
+
+def _shape():
+    from vexact_b200.inferencer import ModelShape, MoEShape
+
+    return ModelShape("tiny-moe", 4, 512, 8, 2, 128, 1024, moe=MoEShape(16, 4, 128))
+
+
+def _config(shape, eager):
+    from vexact_b200.config import CacheConfig, EngineConfig, ModelConfig, SchedulerConfig
+
+    hf = NS(num_key_value_heads=shape.num_kv_heads, head_dim=shape.head_dim, hidden_size=shape.hidden,
+            num_attention_heads=shape.num_q_heads, num_hidden_layers=shape.num_layers)
+    return EngineConfig(model=ModelConfig(hf_config=hf, max_model_len=256, enforce_eager=eager),
+                        cache=CacheConfig(page_size=16, max_cache_blocks=64),
+                        scheduler=SchedulerConfig(max_num_seqs=8, max_num_batched_tokens=32))
+
+
+def _requests(shape, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    cfg = NS(do_sample=False, temperature=1.0, top_k=None, top_p=1.0, output_scores=True, output_logits=True, seed=None)
+    reqs, next_block = [], 0
+    for i, n in enumerate([5, 9, 3]):
+        ids = torch.randint(0, shape.vocab, (n,), generator=g).tolist()
+        reqs.append(NS(request_id=f"r{i}", input_ids_list=ids, tokens_this_step=n, num_computed_tokens=n,
+                       block_ids=[next_block], generated_tokens=[], generation_config=cfg))
+        next_block += 2          # leave room for a second block per request
+    return reqs
+
+
+def _advance(reqs, tokens):
+    """What the scheduler does between steps: append the token, plan one decode token, grow the block list."""
+    for r, t in zip(reqs, tokens.tolist()):
+        r.generated_tokens.append(int(t))
+        r.tokens_this_step = 1
+        r.num_computed_tokens += 1
+        if (r.num_computed_tokens + 15) // 16 > len(r.block_ids):
+            r.block_ids.append(r.block_ids[-1] + 1)
+
+
+class _Loopback:
+    """In-process stand-in for the messager between two single-process pipeline ranks."""
+
+    def __init__(self):
+        self.ctx, self.out = [], []
+
+    def send_gen_ctx(self, c):
+        import dataclasses
+        self.ctx.append(dataclasses.replace(c, intermediate_tensors=c.intermediate_tensors.clone()))
+
+    def recv_gen_ctx(self):
+        return self.ctx.pop(0)
+
+    def send_infer_out(self, o):
+        self.out.append(o)
+
+    def recv_infer_out(self):
+        return self.out.pop(0)
+
+
+def _run(inferencers, steps=4):
+    """Drive prefill + decode steps through a chain of single-process pipeline ranks."""
+    shape = _shape()
+    reqs = _requests(shape)
+    history = []
+    for _ in range(steps):
+        out = None
+        for k, inf in enumerate(inferencers):
+            res = inf.infer(reqs if k == 0 else [], recv_infer_out=False)
+            if res is not None:
+                out = res
+        if out is None:                       # multi-rank chain: the last rank handed its output to the loopback
+            out = inferencers[0]._pp_messager.recv_infer_out()
+        history.append((out.token_ids.clone(), out.logprobs.clone(), out.logits.clone()))
+        _advance(reqs, out.token_ids)
+    torch.cuda.synchronize()
+    return history
+
+
+def _make(shape, weights_for, pp_size, eager, messager=None):
+    from vexact_b200.config import PPInfo
+    from vexact_b200.inferencer import Inferencer, StageModel
+
+    out = []
+    for r in range(pp_size):
+        model = StageModel(weights_for(r, pp_size), r, pp_size)
+        out.append(Inferencer(model, _config(shape, eager), PPInfo(pp_size, r), messager, torch.device(DEV),
+                              enable_batch_invariant=False))
+    return out
+
+
+def test_bucket_graph_replay_equals_eager_and_pipeline_split_bitwise():
+    from vexact_b200 import _lib
+    from vexact_b200.cudagraph_utils import CudaGraphManager
+    from vexact_b200.inferencer import StageWeights, get_pp_indices
+
+    shape = _shape()
+    full = StageWeights.random_init(shape, device=DEV, seed=5, std=0.05)
+
+    def weights_for(rank, pp):
+        s0, s1 = get_pp_indices(shape.num_layers, rank, pp)
+        return StageWeights(shape, s0, s1, layers=full.layers[s0:s1], embed=full.embed if rank == 0 else None,
+                            final_norm=full.final_norm if rank == pp - 1 else None,
+                            lm_head=full.lm_head if rank == pp - 1 else None, inv_freq=full.inv_freq)
+
+    assert CudaGraphManager.build_capture_sizes(32) == [1, 2, 4, 8, 16, 32]
+    eager = _run(_make(shape, weights_for, 1, eager=True))
+    graph_inf = _make(shape, weights_for, 1, eager=False)
+    mgr = graph_inf[0]._cudagraph_mgr
+    # prefill of 17 tokens / 3 sequences -> the 32-token bucket (8 sequences); decode of 3 -> the 4-sequence decode graph
+    d = mgr.dispatch(3, 17, 9)
+    assert (d.num_tokens, d.num_seqs, d.decode) == (32, 8, False)
+    d = mgr.dispatch(3, 3, 1)
+    assert (d.num_tokens, d.num_seqs, d.decode) == (4, 4, True)
+    assert mgr.dispatch(9, 9, 1) is None or mgr.dispatch(9, 9, 1).num_seqs >= 9
+    graph = _run(graph_inf)
+    lo = _Loopback()
+    split = _run(_make(shape, weights_for, 2, eager=False, messager=lo))
+    for step, (a, b, c) in enumerate(zip(eager, graph, split)):
+        for x, y, z, what in zip(a, b, c, ("tokens", "logprobs", "logits")):
+            assert torch.equal(x, y), f"step {step}: padded-bucket graph replay differs from eager in {what}"
+            assert torch.equal(x, z), f"step {step}: two pipeline ranks differ from one in {what}"
+    assert _lib.read_status()[0] == 0
+
+
+def test_hf_module_through_the_inferencer_matches_stage_model():
+    """A stock HF Qwen3-MoE module (patched by apply_qwen3_moe_patches) and the native stage on weights loaded from
+    it go through the same Inferencer and agree within the bf16 tolerance of the HF drop-in test."""
+    transformers = pytest.importorskip("transformers")
+    import vexact_b200 as vb
+    from vexact_b200.config import PPInfo
+    from vexact_b200.inferencer import HFModel, Inferencer, StageModel
+    from vexact_b200.attention import register_attention_functions
+    from vexact_b200.models import apply_qwen3_moe_patches, shape_from_hf_config, stage_weights_from_hf
+
+    register_attention_functions()
+    apply_qwen3_moe_patches()
+    cfg = transformers.Qwen3MoeConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                      num_hidden_layers=2, vocab_size=1024, num_experts=16, num_experts_per_tok=4,
+                                      moe_intermediate_size=128, norm_topk_prob=True, tie_word_embeddings=False,
+                                      intermediate_size=256, decoder_sparse_step=1, mlp_only_layers=[],
+                                      rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=4096)
+    cfg._attn_implementation = "fa-invariant"
+    with torch.device(DEV):
+        model = transformers.Qwen3MoeForCausalLM(cfg).to(BF).eval()
+    g = torch.Generator(device=DEV).manual_seed(3)
+    with torch.no_grad():
+        for name, p in sorted(model.named_parameters()):
+            p.normal_(0.0, 0.05, generator=g)
+            if "norm" in name:
+                p.add_(1.0)
+    shape = shape_from_hf_config(cfg)
+    econf = _config(shape, eager=True)
+    econf.model.hf_config = cfg
+    try:
+        hf_inf = Inferencer(HFModel(model), econf, PPInfo(1, 0), None, torch.device(DEV), enable_batch_invariant=True)
+        hf = _run([hf_inf], steps=3)
+    finally:
+        vb.disable_batch_invariant_mode()
+        torch.use_deterministic_algorithms(False)
+    st_inf = Inferencer(StageModel(stage_weights_from_hf(model, shape, device=DEV)), econf, PPInfo(1, 0), None,
+                        torch.device(DEV), enable_batch_invariant=False)
+    st = _run([st_inf], steps=3)
+    # step 0 sees identical inputs on both sides; later steps feed each side's own greedy tokens
+    d = (hf[0][2].float() - st[0][2].float()).abs().max().item()
+    print(f"HF module vs native stage through the Inferencer: max |dlogit| = {d:.4f}")
+    assert d < 0.08
+    assert (hf[0][1] - st[0][1]).abs().max().item() < 0.05 or not torch.equal(hf[0][0], st[0][0])

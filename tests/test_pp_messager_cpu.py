@@ -14,10 +14,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _ctx(T, S, W, H, first):
+def _ctx(T, S, W, H, first, with_requests=True):
+    from types import SimpleNamespace as NS
+
     from vexact_b200.pp_messager import GenerationContext
 
     g = torch.Generator().manual_seed(T * 131 + S)
+    cfgs = [NS(do_sample=bool(i % 2), temperature=0.5 + i, top_k=None if i % 3 == 0 else 40 + i, top_p=0.9,
+               output_scores=True, output_logits=False, seed=None if i % 2 else 1234 + i) for i in range(S)]
     return GenerationContext(
         batch_input_ids=torch.randint(0, 1000, (1, T), generator=g) if first else None,
         intermediate_tensors=None if first else torch.randn(1, T, H, generator=g).to(torch.bfloat16),
@@ -27,38 +31,46 @@ def _ctx(T, S, W, H, first):
         context_lens=torch.randint(1, 4096, (S,), generator=g, dtype=torch.int32),
         slot_mapping=torch.randint(-1, 800, (T,), generator=g, dtype=torch.int32),
         max_seqlen_q=T // S,
-        tokens_generated=torch.arange(S, dtype=torch.int32),
+        generation_configs=cfgs if with_requests else [],
+        tokens_generated=list(range(3, 3 + S)) if with_requests else None,
     )
 
 
 def _same(a, b):
     for name in ("batch_input_ids", "intermediate_tensors", "query_start_loc", "batch_position_ids", "block_tables",
-                 "context_lens", "slot_mapping", "tokens_generated"):
+                 "context_lens", "slot_mapping"):
         x, y = getattr(a, name), getattr(b, name)
         assert (x is None) == (y is None), name
         if x is not None:
             assert torch.equal(x.reshape(-1), y.reshape(-1)), name
     assert a.max_seqlen_q == b.max_seqlen_q
+    assert a.tokens_generated == b.tokens_generated          # a list of ints, or None: the optional field survives
+    assert len(a.generation_configs) == len(b.generation_configs)
+    for x, y in zip(a.generation_configs, b.generation_configs):
+        for f in ("do_sample", "temperature", "top_k", "top_p", "output_scores", "output_logits", "seed"):
+            assert getattr(x, f) == getattr(y, f), f
 
 
 def _worker(rank, world, port, fail_q):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
+        from vexact_b200.config import ParallelConfig, PPInfo
         from vexact_b200.pp_messager import InferencerOutput, PPMessager
 
         H = 64
-        m = PPMessager(rank, world, torch.device("cpu"), hidden_size=H, max_tokens=64, max_seqs=8,
-                       max_blocks_per_seq=5, vocab_size=32, backend="gloo")
+        # the reference's constructor: (pp_info, parallel_config, device)
+        m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), torch.device("cpu"))
         for step, (T, S, W) in enumerate([(8, 4, 5), (64, 8, 3), (2, 1, 1)]):
+            req = step != 2          # the last step carries neither sampling configs nor tokens_generated
             # ring: rank r sends to r + 1; rank 0 sends token ids, the others hidden states
             if rank == 0:
-                m.send_gen_ctx(_ctx(T, S, W, H, first=True))
+                m.send_gen_ctx(_ctx(T, S, W, H, first=True, with_requests=req))
             else:
                 got = m.recv_gen_ctx()
-                _same(got, _ctx(T, S, W, H, first=(rank == 1)))
+                _same(got, _ctx(T, S, W, H, first=(rank == 1), with_requests=req))
                 if rank < world - 1:
-                    m.send_gen_ctx(_ctx(T, S, W, H, first=False))
+                    m.send_gen_ctx(_ctx(T, S, W, H, first=False, with_requests=req))
             # last -> first
             out = InferencerOutput(token_ids=torch.arange(S) * 3 + step,
                                    logits=torch.full((S, 32), 0.5, dtype=torch.bfloat16) if step == 1 else torch.empty(0),
@@ -71,9 +83,32 @@ def _worker(rank, world, port, fail_q):
                 assert got.logits.numel() == out.logits.numel()
                 if out.logits.numel():
                     assert torch.equal(got.logits, out.logits)
+
+        # two contexts in flight: the first one received must survive the second receive (two slots)
         if rank == 0:
-            with pytest.raises(ValueError):
-                m.send_gen_ctx(_ctx(128, 8, 5, H, first=True))  # beyond max_tokens
+            m.send_gen_ctx(_ctx(8, 4, 5, H, first=True))
+            m.send_gen_ctx(_ctx(16, 4, 5, H, first=True))
+        elif rank == 1:
+            first, second = m.recv_gen_ctx(), m.recv_gen_ctx()
+            _same(first, _ctx(8, 4, 5, H, first=True))
+            _same(second, _ctx(16, 4, 5, H, first=True))
+
+        # block tables as deltas: a full table opens slot 7, then two steps ship only the changed entries
+        S, W = 4, 6
+        base = _ctx(8, S, W, H, first=True)
+        if rank == 0:
+            m.send_gen_ctx(base, slot=7)
+            full_bytes = m.bytes_sent_last
+            rows, cols, vals = torch.tensor([1, 3]), torch.tensor([2, 5]), torch.tensor([41, 42])
+            m.send_gen_ctx(base, slot=7, block_delta=(rows, cols, vals))
+            assert m.bytes_sent_last < full_bytes
+            m.send_gen_ctx(base, slot=7, block_delta=(rows[:0], cols[:0], vals[:0]))
+        elif rank == 1:
+            want = base.block_tables.clone()
+            assert torch.equal(m.recv_gen_ctx().block_tables, want)
+            want[1, 2], want[3, 5] = 41, 42
+            assert torch.equal(m.recv_gen_ctx().block_tables, want)
+            assert torch.equal(m.recv_gen_ctx().block_tables, want)
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
     except Exception as e:  # surface the failure to the parent

@@ -136,6 +136,7 @@ class LayerWeights:
     experts_gate_up: Optional[torch.Tensor] = None  # moe: [E, 2I, hidden]
     experts_down: Optional[torch.Tensor] = None     # moe: [E, hidden, I]
     router_bias: Optional[torch.Tensor] = None      # DeepSeek-V3 e_score_correction_bias [E] fp32
+    router_logit_bias: Optional[torch.Tensor] = None  # softmax routing: bias of the router Linear [E] bf16
     shared_gate_up: Optional[torch.Tensor] = None   # shared experts: [2 * I * n_shared, hidden]
     shared_down: Optional[torch.Tensor] = None      # [hidden, I * n_shared]
     kv_a: Optional[torch.Tensor] = None             # MLA: kv_a_proj_with_mqa [kv_lora + rope, hidden]
@@ -364,7 +365,7 @@ class StageRunner:
                 shared = self._dense_mlp(xn, lw.shared_gate_up, lw.shared_down, m.intermediate * m.n_shared_experts)
             return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
                                      fc1_1_2_weight=lw.experts_gate_up, addend=shared, defer_reduce=True)
-        logits = linear(xn, lw.router)
+        logits = linear(xn, lw.router, lw.router_logit_bias)   # (aten::addmm when the router Linear has a bias)
         rw, sel = route_softmax_topk(logits, m.top_k, m.norm_topk_prob)
         return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
                                  fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True)
@@ -388,13 +389,19 @@ class StageRunner:
             h = h + (delta.finish() if isinstance(delta, PendingMoE) else delta)
         return h
 
-    def select_tokens(self, h: torch.Tensor, inp: StepInputs):
-        """Last stage: last-token rows -> final norm -> lm_head -> greedy token + its logprob."""
-        s = self.shape
+    def last_token_logits(self, h: torch.Tensor, inp: StepInputs) -> torch.Tensor:
+        """Last stage: each sequence's last-token row -> final norm -> lm_head.  [num_seqs, vocab].
+        (The reference runs lm_head over every packed token and gathers afterwards,
+        model_loader.py:267-268 + inferencer.py:403-404; the GEMM is row-invariant, so gathering first
+        gives the same rows.)"""
         last = (inp.query_start_loc[1:] - 1).to(torch.long)
         rows = h.index_select(0, last.clamp(min=0))
         xn = self._norm(rows, self.w.final_norm)
-        logits = linear(xn, self.w.lm_head)
+        return linear(xn, self.w.lm_head)
+
+    def select_tokens(self, h: torch.Tensor, inp: StepInputs):
+        """Last stage: last-token logits -> greedy (or sampled) token + its logprob."""
+        logits = self.last_token_logits(h, inp)
         if self.sampling is None:
             tokens, logprobs = greedy_token_and_logprob(logits)
         else:   # temperature / top-k / top-p sampling (reference: sampler.py:32-87), one kernel
@@ -437,3 +444,338 @@ def allocate_kv_cache(shape: ModelShape, start_layer: int, end_layer: int, num_b
                 t.normal_(0.0, fill_std, generator=gen)
             store[li] = t
     return kc, vc
+
+
+# ------------------------------------------------------------------------------------------------
+# The reference's entry points over the stage runner: model-forward keywords, Inferencer.infer
+# ------------------------------------------------------------------------------------------------
+@dataclass
+class StageOutput:
+    """What the reference reads off the HF model output (`hidden_states`, `logits`) plus
+    `last_logits`: the lm_head rows of each sequence's last token, computed inside the forward so that
+    they are part of the captured graph."""
+
+    hidden_states: Optional[torch.Tensor] = None   # [1, T, H]
+    logits: Optional[torch.Tensor] = None          # never materialised for all tokens here
+    last_logits: Optional[torch.Tensor] = None     # [num_seqs, vocab] (last stage)
+
+
+class StageModel:
+    """The native stage behind the forward keywords the reference's `Inferencer` and `CudaGraphManager`
+    use for an HF module (`TransformersForCausalLM.forward`, model_loader.py:225):
+    `model(input_ids=[1, T], intermediate_tensors=[1, T, H], position_ids=[1, T], **forward_kwargs)`.
+    Attention metadata and the KV caches come from the thread-local KV-cache context, as for HF."""
+
+    def __init__(self, weights: StageWeights, pp_rank: int = 0, pp_size: int = 1):
+        self.runner = StageRunner(weights, {}, {}, pp_rank, pp_size)
+        self.config = None
+        self.layer_ids = range(weights.start_layer, weights.end_layer)
+
+    def eval(self):
+        return self
+
+    def forward(self, input_ids=None, intermediate_tensors=None, position_ids=None, **_unused) -> StageOutput:
+        from .kv_cache_context import get_kv_cache_context
+
+        ctx = get_kv_cache_context()
+        if ctx is None or not ctx.is_paged_attn:
+            raise ValueError("a paged KV-cache context is required (set_kv_cache_context(is_paged_attn=True, ...))")
+        r = self.runner
+        r.key_cache, r.value_cache = ctx.key_cache, ctx.value_cache
+        T = position_ids.shape[-1]
+        inp = StepInputs(
+            input_ids=input_ids.reshape(-1) if r.is_first else None,
+            hidden_in=None if r.is_first else intermediate_tensors.reshape(T, -1),
+            positions=position_ids.reshape(-1), slot_mapping=ctx.slot_mapping, query_start_loc=ctx.query_start_loc,
+            context_lens=ctx.context_lens, block_tables=ctx.block_tables,
+            max_seqlen_q=int(ctx.max_seqlen_q) if ctx.max_seqlen_q else T)
+        r.prepare(T, position_ids.device)
+        h = r.forward(inp)
+        out = StageOutput(hidden_states=h[None])
+        if r.is_last:
+            out.last_logits = r.last_token_logits(h, inp)
+        return out
+
+    __call__ = forward
+
+
+class HFModel:
+    """An HF `*ForCausalLM` module behind the same forward keywords (single pipeline stage): the module
+    runs on this library's operators through `enable_batch_invariant_mode()`, the registered attention
+    function and `register_models()`.  The reference's wrapper for this is `TransformersForCausalLM`
+    (model_loader.py:218); its pipeline slicing is what `StageModel` does natively."""
+
+    def __init__(self, hf_model):
+        self.hf_model = hf_model
+        self.config = hf_model.config
+
+    def eval(self):
+        self.hf_model.eval()
+        return self
+
+    def forward(self, input_ids=None, intermediate_tensors=None, position_ids=None, **_unused) -> StageOutput:
+        if intermediate_tensors is not None and input_ids is None:
+            raise NotImplementedError("an HF module runs as a single stage; use StageModel for pipeline ranks")
+        out = self.hf_model(input_ids=input_ids, position_ids=position_ids, use_cache=False,
+                            output_hidden_states=True, return_dict=True)
+        return StageOutput(hidden_states=out.hidden_states[-1], logits=out.logits)
+
+    __call__ = forward
+
+
+class Inferencer:
+    """One forward + token selection per scheduler step, with the pipeline send / receive choreography.
+
+    Same constructor, `infer(requests, recv_infer_out)` contract and helper names as the reference class
+    (vexact/inferencer/inferencer.py:58-449).  `model` is a `StageModel` or an HF module running on this
+    library's operators; `config` carries `.model` (hf_config, max_model_len, enforce_eager,
+    use_fp32_logits), `.cache` (page_size, max_cache_blocks) and `.scheduler` (max_num_seqs,
+    max_num_batched_tokens).  Requests are the scheduler's objects: `input_ids_list`, `tokens_this_step`,
+    `num_computed_tokens`, `block_ids`, `generated_tokens`, `generation_config`.
+
+    What differs inside: the first rank builds the step's buffers on the device from per-request
+    counters (`b200_prepare_step`) instead of per-token host loops, block lists are uploaded as deltas
+    for requests that stay in their row, and token selection is one kernel."""
+
+    def __init__(self, model, config, pp_info, pp_messager, device, enable_batch_invariant: bool = True) -> None:
+        from .batch_invariant_ops import enable_batch_invariant_mode, is_batch_invariant_mode_enabled
+        from .cudagraph_utils import CudaGraphManager
+        from .kv_cache_context import KVCacheStore
+        from .runtime_data import InputBuffers
+        from .step_inputs import StepBuffers
+
+        self.model = model
+        self.device = torch.device(device)
+        self._pp_info = pp_info
+        self._pp_messager = pp_messager
+        self.cache_config = config.cache
+        self.forward_kwargs = dict(use_cache=False, return_dict=True, output_hidden_states=True, use_fused_lce=False)
+        self.use_fp32_logits = bool(getattr(config.model, "use_fp32_logits", False))
+        self.page_size = self.cache_config.page_size
+        hf_config = config.model.hf_config
+        self.cache_store = KVCacheStore(hf_config, self.cache_config, self.device,
+                                        layer_ids=getattr(model, "layer_ids", None))
+        if enable_batch_invariant and not is_batch_invariant_mode_enabled():
+            enable_batch_invariant_mode()
+        self.input_buffers = InputBuffers(
+            device=self.device, max_num_seqs=config.scheduler.max_num_seqs,
+            max_num_batched_tokens=config.scheduler.max_num_batched_tokens,
+            max_blocks_per_req=(config.model.max_model_len + self.page_size - 1) // self.page_size,
+            hidden_size=hf_config.hidden_size)
+        # first rank: the static buffers are written by the step kernel (same tensors, no extra copy)
+        self._step_buffers = None
+        if pp_info.is_first_rank:
+            self._step_buffers = StepBuffers(self.device, config.scheduler.max_num_seqs,
+                                             config.scheduler.max_num_batched_tokens,
+                                             self.input_buffers.max_blocks_per_req, self.page_size,
+                                             buffers=self.input_buffers)
+        self._rows: list = []          # per batch row: (request_id, blocks uploaded so far)
+        self._cudagraph_mgr: Optional[CudaGraphManager] = None
+        if not getattr(config.model, "enforce_eager", False):
+            if getattr(config.model, "attn_impl", "fa-invariant") == "flex":
+                raise RuntimeError("Cuda graph is enabled but flex attention is not supported for CUDA graph replay.")
+            self._cudagraph_mgr = CudaGraphManager(
+                model=self.model, device=self.device, cache_store=self.cache_store,
+                max_size=config.scheduler.max_num_batched_tokens, cache_config=self.cache_config,
+                forward_kwargs=self.forward_kwargs, input_buffers=self.input_buffers)
+            self._cudagraph_mgr.capture_graphs()
+
+    # ------------------------------------------------------------------ one scheduler step
+    def infer(self, requests, recv_infer_out: bool = False):
+        """| pp rank | gen_ctx | forward | infer_out | gen_ctx |
+           | first   | build   | yes     | recv      | send    |
+           | middle  | recv    | yes     | -         | send    |
+           | last    | recv    | yes     | send      | -       |"""
+        from .kv_cache_context import set_kv_cache_context
+        from .runtime_data import GenerationContext, InferencerOutput
+
+        pp, gen_ctx, outputs = self._pp_info, None, None
+        if pp.is_first_rank:
+            if len(requests) > 0:
+                gen_ctx = self._prepare_gen_ctx(requests)
+        else:
+            gen_ctx = self._pp_messager.recv_gen_ctx()
+            set_kv_cache_context(is_paged_attn=True, key_cache=self.cache_store.key_cache,
+                                 value_cache=self.cache_store.value_cache, block_tables=gen_ctx.block_tables,
+                                 context_lens=gen_ctx.context_lens, slot_mapping=gen_ctx.slot_mapping,
+                                 query_start_loc=gen_ctx.query_start_loc, max_seqlen_q=gen_ctx.max_seqlen_q)
+        if gen_ctx is not None:
+            outputs = self._forward(gen_ctx)
+        final_output = None
+        if pp.is_last_rank and gen_ctx is not None:
+            token_ids, logits, logprobs = self._select_tokens(gen_ctx.generation_configs, gen_ctx.tokens_generated,
+                                                              outputs, gen_ctx)
+            final_output = InferencerOutput(token_ids=token_ids, logits=logits, logprobs=logprobs)
+            if pp.is_first_rank:
+                return final_output
+            self._pp_messager.send_infer_out(final_output)
+            final_output = None
+        if pp.is_first_rank and recv_infer_out:
+            final_output = self._pp_messager.recv_infer_out()
+        if not pp.is_last_rank and gen_ctx is not None:
+            num_tokens = gen_ctx.batch_position_ids.shape[1]
+            self._pp_messager.send_gen_ctx(GenerationContext(
+                batch_input_ids=None, intermediate_tensors=outputs.hidden_states[:, :num_tokens, :],
+                query_start_loc=gen_ctx.query_start_loc, batch_position_ids=gen_ctx.batch_position_ids,
+                block_tables=gen_ctx.block_tables, context_lens=gen_ctx.context_lens,
+                slot_mapping=gen_ctx.slot_mapping, max_seqlen_q=gen_ctx.max_seqlen_q,
+                generation_configs=gen_ctx.generation_configs, tokens_generated=gen_ctx.tokens_generated))
+        return final_output
+
+    # ------------------------------------------------------------------ first rank: requests -> buffers
+    def _upload_block_lists(self, requests) -> None:
+        """Keep `request_blocks[row]` equal to each request's block list, uploading only what changed:
+        a request that kept its row since the last step sends the blocks it gained."""
+        sb = self._step_buffers
+        rows, cols, vals = [], [], []
+        for row, req in enumerate(requests):
+            blocks = req.block_ids
+            known = self._rows[row] if row < len(self._rows) else None
+            rid = getattr(req, "request_id", id(req))
+            if known is not None and known[0] == rid and known[1] <= len(blocks):
+                for c in range(known[1], len(blocks)):
+                    rows.append(row)
+                    cols.append(c)
+                    vals.append(blocks[c])
+            else:
+                sb.set_request_blocks(row, blocks)
+            if row < len(self._rows):
+                self._rows[row] = (rid, len(blocks))
+            else:
+                self._rows.append((rid, len(blocks)))
+        del self._rows[len(requests):]
+        for i in range(0, len(rows), sb.max_num_seqs * 2):
+            j = i + sb.max_num_seqs * 2
+            sb.append_blocks(rows[i:j], cols[i:j], vals[i:j])
+
+    def _prepare_gen_ctx(self, requests):
+        from .kv_cache_context import set_kv_cache_context
+        from .runtime_data import GenerationContext
+
+        sb = self._step_buffers
+        num_seqs = len(requests)
+        computed = [int(r.num_computed_tokens) for r in requests]
+        this_step = [int(r.tokens_this_step) for r in requests]
+        total = sum(this_step)
+        chunks = {}
+        for row, req in enumerate(requests):
+            start = computed[row] - this_step[row]
+            assert start >= 0
+            if start < len(req.input_ids_list):       # prefill, or re-prefill after a preemption
+                chunks[row] = req.input_ids_list[start:computed[row]]
+            else:                                      # decode: the last generated token
+                chunks[row] = [req.generated_tokens[-1]]
+        self._upload_block_lists(requests)
+        max_q = max(this_step) if this_step else 0
+        desc = self._cudagraph_mgr.dispatch(num_seqs, total, max_q) if self._cudagraph_mgr else None
+        if self._cudagraph_mgr and desc is None:
+            raise RuntimeError(f"Cuda graph is enabled but no captured descriptor can cover {num_seqs} sequences "
+                               f"and {total} tokens. Available descriptors: {list(self._cudagraph_mgr.graphs)}")
+        self._graph_desc = desc
+        graph_seqs, cap_tokens = (desc.num_seqs, desc.num_tokens) if desc else (num_seqs, total)
+        inp = sb.prepare(computed, this_step, chunks, graph_seqs, cap_tokens)
+        # the (padded) static views are what the forward reads; the context handed on holds the real sizes
+        set_kv_cache_context(is_paged_attn=True, key_cache=self.cache_store.key_cache,
+                             value_cache=self.cache_store.value_cache, block_tables=inp.block_tables,
+                             context_lens=inp.context_lens, slot_mapping=inp.slot_mapping,
+                             query_start_loc=inp.query_start_loc, max_seqlen_q=max_q)
+        return GenerationContext(
+            batch_input_ids=sb.input_ids[:, :total], intermediate_tensors=None,
+            query_start_loc=sb.query_start_loc[: num_seqs + 1], batch_position_ids=sb.position_ids[:, :total],
+            block_tables=sb.request_blocks[:num_seqs], context_lens=sb.context_lens[:num_seqs],
+            slot_mapping=sb.slot_mapping[:total], max_seqlen_q=max_q,
+            generation_configs=[r.generation_config for r in requests],
+            tokens_generated=[len(r.generated_tokens) for r in requests])
+
+    # ------------------------------------------------------------------ later ranks: ctx -> static buffers
+    def _prepare_input_buffers_from_gen_ctx(self, gen_ctx, graph_desc) -> None:
+        from .kv_cache_context import set_kv_cache_context
+
+        buf = self.input_buffers
+        cap, gseqs = graph_desc.num_tokens, graph_desc.num_seqs
+        num_seqs = gen_ctx.context_lens.size(0)
+        total = gen_ctx.batch_position_ids.size(1)
+        if total > cap:
+            raise ValueError(f"total_tokens exceeds capture_tokens: {total} > {cap}")
+        if gseqs < num_seqs:
+            raise ValueError(f"graph_num_seqs cannot be smaller than num_seqs: {gseqs} < {num_seqs}")
+        if not self._pp_info.is_first_rank:
+            # (the first rank's step kernel has already written the padded buffers in place)
+            buf.input_ids.gpu[:, :cap].zero_()
+            buf.position_ids.gpu[:, :cap].zero_()
+            buf.intermediate_tensors.gpu[:, total:cap, :].zero_()
+            buf.block_tables.gpu[:gseqs].zero_()
+            buf.context_lens.gpu[:gseqs].zero_()
+            buf.slot_mapping.gpu[:cap].fill_(-1)
+            buf.block_tables.gpu[:num_seqs, : gen_ctx.block_tables.shape[1]].copy_(gen_ctx.block_tables)
+            buf.context_lens.gpu[:num_seqs].copy_(gen_ctx.context_lens)
+            buf.slot_mapping.gpu[:total].copy_(gen_ctx.slot_mapping)
+            buf.query_start_loc.gpu[: num_seqs + 1].copy_(gen_ctx.query_start_loc)
+            if gseqs > num_seqs:      # padded requests: zero-length, placed after the real tokens
+                buf.query_start_loc.gpu[num_seqs + 1: gseqs + 1] = total
+            if gen_ctx.batch_input_ids is not None:
+                buf.input_ids.gpu[:, :total].copy_(gen_ctx.batch_input_ids)
+            buf.position_ids.gpu[:, :total].copy_(gen_ctx.batch_position_ids)
+            if gen_ctx.intermediate_tensors is not None:
+                buf.intermediate_tensors.gpu[:, :total, :].copy_(gen_ctx.intermediate_tensors)
+        block_tables, context_lens, slot_mapping, query_start_loc = buf.get_kv_context_tensors(gseqs, cap)
+        set_kv_cache_context(is_paged_attn=True, key_cache=self.cache_store.key_cache,
+                             value_cache=self.cache_store.value_cache, block_tables=block_tables,
+                             context_lens=context_lens, slot_mapping=slot_mapping, query_start_loc=query_start_loc,
+                             max_seqlen_q=gen_ctx.max_seqlen_q)
+
+    @torch.inference_mode()
+    def _forward(self, gen_ctx):
+        if self._cudagraph_mgr:
+            total = (gen_ctx.batch_input_ids if gen_ctx.batch_input_ids is not None
+                     else gen_ctx.intermediate_tensors).size(1)
+            num_seqs = gen_ctx.context_lens.size(0)
+            desc = getattr(self, "_graph_desc", None) if self._pp_info.is_first_rank else None
+            if desc is None:
+                desc = self._cudagraph_mgr.dispatch(num_seqs, total, gen_ctx.max_seqlen_q)
+            if desc is None:
+                raise RuntimeError(f"Cuda graph is enabled but no captured descriptor can cover {num_seqs} sequences "
+                                   f"and {total} tokens. Available descriptors: {list(self._cudagraph_mgr.graphs)}")
+            self._prepare_input_buffers_from_gen_ctx(gen_ctx, desc)
+            with torch.cuda.nvtx.range("model_forward_cudagraph"):
+                return self._cudagraph_mgr.replay(desc)
+        return self._forward_eager(gen_ctx)
+
+    @torch.inference_mode()
+    def _forward_eager(self, gen_ctx):
+        with torch.cuda.nvtx.range("model_forward_eager"):
+            return self.model(input_ids=gen_ctx.batch_input_ids, intermediate_tensors=gen_ctx.intermediate_tensors,
+                              position_ids=gen_ctx.batch_position_ids, **self.forward_kwargs)
+
+    # ------------------------------------------------------------------ last rank: logits -> tokens
+    @torch.inference_mode()
+    def _select_tokens(self, gen_configs, tokens_generated, outputs, gen_ctx):
+        num_seqs = gen_ctx.context_lens.size(0)
+        last_logits = getattr(outputs, "last_logits", None)
+        if last_logits is not None:
+            batched_logits = last_logits[:num_seqs]
+        else:   # an HF module: logits of every packed token, gather the last one of each request
+            last = (gen_ctx.query_start_loc[1:] - 1).to(dtype=torch.long)
+            batched_logits = outputs.logits[0, last, :]
+        ref = gen_configs[0]
+        uniform = all((g.do_sample == ref.do_sample and g.temperature == ref.temperature and g.top_k == ref.top_k
+                       and g.top_p == ref.top_p) for g in gen_configs)
+        assert uniform
+        if any(getattr(g, "seed", None) is not None for g in gen_configs):
+            raise NotImplementedError("per-request seeds need the seeded sampler, which this library does not have")
+        scored = self.use_fp32_logits and batched_logits.dtype != torch.float32
+        sample_logits = batched_logits.float() if scored else batched_logits
+        assert ref.top_p is not None, "top_p must be set (use 1.0 to disable)"
+        do_sample = bool(ref.do_sample) and (ref.temperature or 0) > 0 and float(ref.top_p) > 0
+        if do_sample:
+            tokens, logprobs = sample_token_and_logprob(sample_logits, float(ref.temperature), ref.top_k,
+                                                        float(ref.top_p))
+        else:
+            tokens, logprobs = greedy_token_and_logprob(sample_logits)
+        logits = batched_logits.detach() if getattr(ref, "output_logits", False) else torch.empty(0, device=self.device)
+        want = [i for i, g in enumerate(gen_configs) if getattr(g, "output_scores", False)]
+        if not want:
+            logprobs = torch.empty(0, device=self.device)
+        elif len(want) != len(gen_configs):
+            logprobs = logprobs.index_select(0, torch.tensor(want, dtype=torch.long).to(self.device, non_blocking=True))
+        return tokens, logits, logprobs

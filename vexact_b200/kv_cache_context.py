@@ -123,23 +123,35 @@ class KVCacheManager:
 
 
 class KVCacheStore:
-    """Owns the per-layer K / V cache tensors, [max_blocks, page, kv_heads, dim].
+    """Owns the per-layer K / V cache tensors, [max_cache_blocks, page_size, kv_heads, dim].
 
-    Unlike the reference (which allocates every layer on every pipeline rank), only
-    `layer_ids` are allocated, so a stage holds the cache of its own layers.
+    Same constructor as the reference class (kv_cache_context.py:223): `(hf_config, cache_config,
+    device)`; key dim = `qk_head_dim` when the config has one (MLA: 192) else `head_dim`, value dim =
+    `v_head_dim` when present.  The reference allocates every layer on every pipeline rank; pass
+    `layer_ids` (the rank's own layers, e.g. `range(*get_pp_indices(...))`) to allocate only those.
     """
 
-    def __init__(self, num_kv_heads: int, k_head_dim: int, v_head_dim: int, page_size: int, max_blocks: int,
-                 layer_ids, device, dtype=torch.bfloat16):
-        self.page_size = page_size
-        self.max_blocks = max_blocks
+    def __init__(self, hf_config, cache_config, device, layer_ids=None):
+        self.hf_config = hf_config
+        self.cache_config = cache_config
+        self.device = torch.device(device)
+        self.page_size = cache_config.page_size
+        self.max_blocks = cache_config.max_cache_blocks
+        num_kv_heads = hf_config.num_key_value_heads
+        head_dim = getattr(hf_config, "head_dim", None) or hf_config.hidden_size // hf_config.num_attention_heads
+        k_dim = getattr(hf_config, "qk_head_dim", None) or head_dim
+        v_dim = getattr(hf_config, "v_head_dim", None) or k_dim
+        dtype = getattr(hf_config, "dtype", None) or vars(hf_config).get("torch_dtype") or torch.bfloat16
+        if not isinstance(dtype, torch.dtype):
+            dtype = getattr(torch, str(dtype).replace("torch.", ""), torch.bfloat16)
+        layers = range(hf_config.num_hidden_layers) if layer_ids is None else layer_ids
         self.key_cache: dict[int, torch.Tensor] = {}
         self.value_cache: dict[int, torch.Tensor] = {}
-        for li in layer_ids:
-            self.key_cache[li] = torch.zeros((max_blocks, page_size, num_kv_heads, k_head_dim), device=device,
-                                             dtype=dtype)
-            self.value_cache[li] = torch.zeros((max_blocks, page_size, num_kv_heads, v_head_dim), device=device,
-                                               dtype=dtype)
+        for li in layers:
+            self.key_cache[li] = torch.zeros((self.max_blocks, self.page_size, num_kv_heads, k_dim),
+                                             device=self.device, dtype=dtype)
+            self.value_cache[li] = torch.zeros((self.max_blocks, self.page_size, num_kv_heads, v_dim),
+                                               device=self.device, dtype=dtype)
 
 
 def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -24,7 +24,9 @@ class StepBuffers:
     """Static step-input buffers (mirror of `InputBuffers`) plus per-request state on the device."""
 
     def __init__(self, device, max_num_seqs: int, max_num_batched_tokens: int, max_blocks_per_req: int,
-                 page_size: int):
+                 page_size: int, buffers=None):
+        """`buffers` (an `InputBuffers`, optional): write the step into its device tensors instead of
+        allocating a second set, so that graphs captured over those buffers read what this kernel writes."""
         if max_num_seqs > 8192:
             raise ValueError("at most 8192 requests per step")
         self.device = torch.device(device)
@@ -34,12 +36,19 @@ class StepBuffers:
         self.page_size = page_size
         dev, S, T, B = self.device, max_num_seqs, max_num_batched_tokens, max_blocks_per_req
         # what a captured step reads (same shapes and fills as InputBuffers)
-        self.slot_mapping = torch.full((T,), -1, dtype=torch.int32, device=dev)
-        self.context_lens = torch.zeros(S, dtype=torch.int32, device=dev)
-        self.query_start_loc = torch.zeros(S + 1, dtype=torch.int32, device=dev)
-        self.block_tables = torch.full((S, B), -1, dtype=torch.int32, device=dev)
-        self.input_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
-        self.position_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
+        if buffers is not None:
+            if (buffers.max_num_seqs, buffers.max_num_batched_tokens, buffers.max_blocks_per_req) != (S, T, B):
+                raise ValueError("the InputBuffers were sized for other maxima")
+            self.slot_mapping, self.context_lens = buffers.slot_mapping.gpu, buffers.context_lens.gpu
+            self.query_start_loc, self.block_tables = buffers.query_start_loc.gpu, buffers.block_tables.gpu
+            self.input_ids, self.position_ids = buffers.input_ids.gpu, buffers.position_ids.gpu
+        else:
+            self.slot_mapping = torch.full((T,), -1, dtype=torch.int32, device=dev)
+            self.context_lens = torch.zeros(S, dtype=torch.int32, device=dev)
+            self.query_start_loc = torch.zeros(S + 1, dtype=torch.int32, device=dev)
+            self.block_tables = torch.full((S, B), -1, dtype=torch.int32, device=dev)
+            self.input_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
+            self.position_ids = torch.zeros(1, T, dtype=torch.long, device=dev)
         self.step_info = torch.zeros(2, dtype=torch.int32, device=dev)
         self.seq_order = torch.arange(S, dtype=torch.int32, device=dev)   # requests by descending context
         self._order_host = torch.empty(S, dtype=torch.int32, pin_memory=self.device.type == "cuda")
