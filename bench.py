@@ -9,8 +9,13 @@ N(0, 0.02) bf16; decode at batch 512 with a 2048-token paged context (16-token p
 table = seeded random permutation).  A "step" is one decode step of one 512-sequence batch:
 embedding -> 48 decoder layers -> final norm -> lm_head -> greedy token + its logprob.
 With N > 1 GPUs the layers are split evenly over N pipeline stages and N batches are in
-flight (one per stage), hidden states handed over with NCCL send/recv: per-GPU work is
-fixed, so scaling is "weak" and a step advances all N in-flight batches by one token.
+flight (one per stage).  Every hand-off goes through the library's PPMessager
+(send_gen_ctx / recv_gen_ctx / send_infer_out / recv_infer_out): hidden states AND the step's
+metadata (positions, slot mapping, query_start_loc, context lengths, block-table deltas) travel
+every step, nothing is pre-resident on later stages.  Per-GPU work is fixed, so scaling is
+"weak" and a step advances all N in-flight batches by one token.  The pipeline is kept full
+across the timed region: warm-up steps run straight into the timed ones and each rank times
+its own K steps with CUDA events (max over ranks).
 
 Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in HBM;
 `e2e` uploads each step's per-request counters from pinned host memory, builds the step's input
@@ -556,14 +561,23 @@ def main():
 
     weights = StageWeights.random_init(shape, rank, pp, device=device, seed=0)
     n_inflight = pp
-    runners, graphs, outs, dev_inputs, host_inputs, step_inputs, step_bufs = [], [], [], [], [], [], []
+    msg = None
+    if pp > 1:
+        from vexact_b200.config import PPInfo
+        from vexact_b200.pp_messager import GenerationContext, InferencerOutput, PPMessager
+
+        # one receive slot per batch in flight: batch b of every round lands at the same addresses, so
+        # each later stage captures its graph directly on the received views (no copy on arrival)
+        msg = PPMessager(PPInfo(pp, rank), None, device, recv_slots=n_inflight, send_slots=2)
+    runners, graphs, outs, step_inputs, step_bufs, kv_blocks = [], [], [], [], [], []
     computed_host, tts_host = [args.ctx] * S, [1] * S    # per-request counters of a decode step
-    hidden_in = [torch.zeros((S, H), device=device, dtype=torch.bfloat16) for _ in range(n_inflight)]
+    first_ctx = [None] * n_inflight                       # stages > 0: the context a batch's graph was captured on
     for b in range(n_inflight):
         host, dev, nblocks = build_inputs(args, shape, seed=100 + b, device=device)
         kc, vc = allocate_kv_cache(shape, weights.start_layer, weights.end_layer, nblocks, args.page, device=device,
                                    fill_std=1.0, seed=b)
-        r = StageRunner(weights, kc, vc, rank, pp)
+        runners.append(StageRunner(weights, kc, vc, rank, pp))
+        kv_blocks.append(nblocks)
         if rank == 0:
             # first stage: the step's buffers are built on the device from per-request counters
             # (b200_prepare_step); block tables and the previous step's tokens stay in HBM
@@ -573,29 +587,53 @@ def main():
             # values in every step so that the e2e leg routes tokens exactly as the device-timed leg does
             sb.last_tokens.copy_(dev["input_ids"])
             inp = sb.prepare([args.ctx] * S, [1] * S, None, S, S)
-            inp.hidden_in = hidden_in[b]
             for name, built in [("positions", inp.positions), ("slot_mapping", inp.slot_mapping),
                                 ("query_start_loc", inp.query_start_loc), ("context_lens", inp.context_lens),
                                 ("block_tables", inp.block_tables), ("input_ids", inp.input_ids)]:
                 if not torch.equal(built, dev[name]):
                     raise SystemExit(f"device-built {name} differs from the host-built one")
             step_bufs.append(sb)
-        else:
-            inp = StepInputs(input_ids=dev["input_ids"], hidden_in=hidden_in[b], positions=dev["positions"],
-                             slot_mapping=dev["slot_mapping"], query_start_loc=dev["query_start_loc"],
-                             context_lens=dev["context_lens"], block_tables=dev["block_tables"], max_seqlen_q=1)
-        runners.append(r)
-        host_inputs.append(host)
-        dev_inputs.append(dev)
-        step_inputs.append(inp)
+            step_inputs.append(inp)
+    if pp > 1:
+        W = (args.ctx + args.page - 1) // args.page
+        msg.reserve(H, S, S, W, 0)
     torch.cuda.synchronize()
 
-    # count our kernel launches in one eager step, then capture
-    _lib.reset_launch_count()
-    runners[0].step(step_inputs[0])
-    torch.cuda.synchronize()
-    launches_per_step = _lib.launch_count()
+    def ctx_of(inp, hidden):
+        """The context a stage hands on: its output hidden states plus the step's metadata."""
+        return GenerationContext(batch_input_ids=None, intermediate_tensors=hidden[None],
+                                 query_start_loc=inp.query_start_loc, batch_position_ids=inp.positions[None],
+                                 block_tables=inp.block_tables, context_lens=inp.context_lens,
+                                 slot_mapping=inp.slot_mapping, max_seqlen_q=1)
+
+    no_delta = tuple(torch.empty(0, dtype=torch.int32, device=device) for _ in range(3))
+
+    def hand_on(b, inp, out, first):
+        """Stage output -> next stage (context) or, on the last stage, tokens + logprobs -> first stage."""
+        if rank < pp - 1:
+            # the block table travels whole once per batch slot, then as deltas (none in a decode step
+            # that stays inside its last page)
+            msg.send_gen_ctx(ctx_of(inp, out), slot=b, block_delta=None if first else no_delta)
+        else:
+            msg.send_infer_out(InferencerOutput(token_ids=out[0], logits=torch.empty(0, device=device),
+                                                logprobs=out[1]))
+
+    def inputs_from(ctx):
+        return StepInputs(input_ids=None, hidden_in=ctx.intermediate_tensors[0], positions=ctx.batch_position_ids[0],
+                          slot_mapping=ctx.slot_mapping, query_start_loc=ctx.query_start_loc,
+                          context_lens=ctx.context_lens, block_tables=ctx.block_tables, max_seqlen_q=1)
+
+    # ---- set-up round: one eager step per batch flows down the pipeline; every stage counts its launches
+    # and captures its graph on the buffers the step arrived in
+    launches_per_step = 0
     for b in range(n_inflight):
+        if rank > 0:
+            first_ctx[b] = msg.recv_gen_ctx()
+            step_inputs.append(inputs_from(first_ctx[b]))
+        _lib.reset_launch_count()
+        out = runners[b].step(step_inputs[b])
+        torch.cuda.synchronize()
+        launches_per_step = _lib.launch_count()
         if args.no_graph:
             graphs.append(None)
             outs.append(None)
@@ -603,6 +641,10 @@ def main():
             gr, out = runners[b].capture(step_inputs[b])
             graphs.append(gr)
             outs.append(out)
+            gr.replay()
+        if pp > 1:
+            hand_on(b, step_inputs[b], out, first=True)
+    pending = [pp > 1 and rank == 0] * n_inflight   # rank 0: a token message of the batch's previous step is owed
     status = _lib.read_status()
     if status[0] != 0:
         raise SystemExit(f"device status word reports {status}")
@@ -613,58 +655,38 @@ def main():
             return outs[b]
         return runners[b].step(step_inputs[b])
 
-    # Hidden states travel r -> r+1 on a group of their own per adjacent pair (as the reference's
-    # PPMessager builds them), and the sampled token ids close the ring (last -> first) on another
-    # group: every direction has its own communicator and stream, so a stage can receive the next
-    # batch, send the previous one and return tokens at the same time.  All transfers are
-    # asynchronous; a buffer's transfer is waited for only where the buffer is next touched.
     # e2e results land in two pinned buffers in turn: the host reads step N's tokens while step N + 1
     # runs (its inputs need only the requests' lengths; the token ids themselves stay on the device)
     tok_host = [torch.empty(S, dtype=torch.int64).pin_memory() for _ in range(2)]
     lp_host = [torch.empty(S, dtype=torch.float32).pin_memory() for _ in range(2)]
     e2e_done = [torch.cuda.Event(), torch.cuda.Event()]
     e2e_count = [0]
-    pair_groups = [dist.new_group(ranks=[i, i + 1]) for i in range(pp - 1)] if pp > 1 else []
-    fb_group = dist.new_group(ranks=list(range(pp))) if pp > 1 else None
-    g_prev = pair_groups[rank - 1] if rank > 0 else None
-    g_next = pair_groups[rank] if rank < pp - 1 else None
-    recv_tok = [torch.zeros(S, dtype=torch.int64, device=device) for _ in range(n_inflight)]
-    pending = [False] * n_inflight     # rank 0: a token message of the batch's previous step is outstanding
-    send_h = [None] * n_inflight       # sends whose source buffer the next replay overwrites
-
     trace = [] if os.environ.get("B200_BENCH_TRACE") else None
 
     def global_step(e2e=False):
         """Advance every in-flight batch by one token through this rank's stage."""
         for b in range(n_inflight):
             if rank == 0:
-                if pp > 1 and pending[b]:       # tokens of this batch's previous step, received only now:
-                    # a receive posted earlier would poll on the GPU all through the stages in between
-                    dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
+                if pending[b]:                  # tokens + logprobs of this batch's previous step
+                    msg.recv_infer_out()
                     pending[b] = False
                 if e2e:                         # counters up, one kernel builds the step's buffers
                     step_bufs[b].prepare(computed_host, tts_host, None, S, S)
             else:
-                # posted only now: the receive kernel starts when the previous stage ends, so it does
-                # not sit on the GPU polling while that stage computes
-                dist.irecv(hidden_in[b], src=rank - 1, group=g_prev).wait()
-            if send_h[b] is not None:           # the previous step's send reads this graph's output
-                send_h[b].wait()
-                send_h[b] = None
+                ctx = msg.recv_gen_ctx()        # lands where this batch's graph reads its inputs
+                if ctx.intermediate_tensors.data_ptr() != first_ctx[b].intermediate_tensors.data_ptr():
+                    raise SystemExit("a batch's context arrived at another address than its graph was captured on")
             if trace is not None:
                 trace.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
                 trace[-1][0].record()
             out = run_stage(b)
             if trace is not None:
                 trace[-1][1].record()
-            if rank < pp - 1:
-                send_h[b] = dist.isend(out, dst=rank + 1, group=g_next)
-            else:
-                if e2e:
-                    tok_host[e2e_count[0] & 1].copy_(out[0], non_blocking=True)
-                    lp_host[e2e_count[0] & 1].copy_(out[1], non_blocking=True)
-                if pp > 1:
-                    send_h[b] = dist.isend(out[0], dst=0, group=fb_group)
+            if pp > 1:
+                hand_on(b, step_inputs[b], out, first=False)
+            if rank == pp - 1 and e2e:
+                tok_host[e2e_count[0] & 1].copy_(out[0], non_blocking=True)
+                lp_host[e2e_count[0] & 1].copy_(out[1], non_blocking=True)
             if pp > 1 and rank == 0:
                 pending[b] = True               # one token message is now owed to this batch
         if e2e:
@@ -675,12 +697,11 @@ def main():
 
     def drain():
         for b in range(n_inflight):
-            if pp > 1 and rank == 0 and pending[b]:
-                dist.irecv(recv_tok[b], src=pp - 1, group=fb_group).wait()
+            if pending[b]:
+                msg.recv_infer_out()
                 pending[b] = False
-            if send_h[b] is not None:
-                send_h[b].wait()
-                send_h[b] = None
+        if msg is not None:
+            msg.flush()
 
     def sync_all():
         drain()
@@ -693,11 +714,15 @@ def main():
     if not args.quick:
         sampler.start()
         sampler.wait_first_sample()
+    sync_all()
     for _ in range(max(args.warmup, 3) if not args.quick else args.warmup):
         global_step()
-    sync_all()
+    if pp == 1:
+        sync_all()
 
-    # ---- device-timed run (inputs resident in HBM; weights + KV >> L2, so every step is cold)
+    # ---- device-timed run (inputs resident in HBM; weights + KV >> L2, so every step is cold).
+    # With pipeline stages the warm-up steps run straight into the timed ones (no drain in between), so
+    # the pipeline is full when a rank's first timed stage starts; each rank times its own K steps.
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first_sample = sampler.mark()
     ev0.record()
@@ -731,12 +756,19 @@ def main():
 
     for _ in range(2):
         e2e_step()
-    sync_all()
+    if pp == 1:
+        sync_all()
+    else:
+        torch.cuda.synchronize()   # this rank's own queue only: the pipeline stays full
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()
-    sync_all()
+    if pp == 1:
+        sync_all()
+    else:
+        torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
+    sync_all()
     if trace is not None:
         tail = trace[-args.steps * n_inflight:]
         st = [a.elapsed_time(b) for a, b in tail]
@@ -750,6 +782,8 @@ def main():
     # ---- dominant kernel alone (paged decode attention over every local layer's cache)
     att = {}
     r0 = runners[0]
+    if rank > 0:   # later stages: their metadata arrived over the wire
+        step_inputs[0] = inputs_from(first_ctx[0])
     q = torch.randn(S, shape.num_q_heads, shape.head_dim, device=device).to(torch.bfloat16)
     layers = list(range(weights.start_layer, weights.end_layer))
     reps = max(2, min(args.steps, 5))
@@ -796,7 +830,11 @@ def main():
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload_name(args, shape), "pipeline_stages": pp, "batches_in_flight": n_inflight,
                    "l2": "inputs (weights + KV, >100 GB per GPU) far exceed L2; no flush needed",
-                   "cuda_graph": not args.no_graph, "e2e": "per step: H2D of per-request counters, device-built inputs, graph replay, D2H of tokens + logprobs; the host reads step N's results while step N+1 runs"},
+                   "cuda_graph": not args.no_graph,
+                   "handoff": ("PPMessager.send_gen_ctx / recv_gen_ctx / send_infer_out: hidden states + step metadata "
+                               "(positions, slot mapping, query_start_loc, context lengths, block-table deltas) every step; "
+                               "pipeline kept full across the timed region, each rank times its own steps") if pp > 1 else "none",
+                   "e2e": "per step: H2D of per-request counters, device-built inputs, graph replay, D2H of tokens + logprobs; the host reads step N's results while step N+1 runs"},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * n_inflight,
                 "d2h_bytes_per_step": d2h * n_inflight, "ms_per_step": e2e_ms / args.steps},

@@ -109,6 +109,7 @@ def _worker(rank, world, port, fail_q):
             want[1, 2], want[3, 5] = 41, 42
             assert torch.equal(m.recv_gen_ctx().block_tables, want)
             assert torch.equal(m.recv_gen_ctx().block_tables, want)
+        m.flush()
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
     except Exception as e:  # surface the failure to the parent

@@ -18,7 +18,11 @@ The wire format differs:
 
 Returned tensors are views into the receive staging buffers.  Each direction has `recv_slots` (default
 2) buffers used in turn, so a received context or output stays valid until `recv_slots` further
-messages of the same kind have been received; clone what must live longer.
+messages of the same kind have been received; clone what must live longer.  With `recv_slots` equal to
+the number of batches in flight and `reserve()` called up front, batch b of every round lands at the
+same addresses, so a CUDA graph can be captured directly on the received views.
+Sends are asynchronous: a payload is packed into one of `send_slots` staging buffers and the transfer
+is waited for only when that buffer comes round again.
 """
 from __future__ import annotations
 
@@ -51,7 +55,7 @@ def _esize(dtype) -> int:
 
 class PPMessager:
     def __init__(self, pp_info, parallel_config=None, device=None, *, backend: Optional[str] = None,
-                 recv_slots: int = 2, init_timeout: timedelta = timedelta(minutes=30),
+                 recv_slots: int = 2, send_slots: int = 2, init_timeout: timedelta = timedelta(minutes=30),
                  group_timeout: timedelta = timedelta(days=7)):
         """`pp_info`: PPInfo(pp_size, pp_rank); `parallel_config`: address / port of the rendezvous when
         this call has to initialise torch.distributed; `device`: where payloads live.  `backend` defaults
@@ -72,7 +76,10 @@ class PPMessager:
         else:
             self._init_pp_groups_within_world()
         self._recv_slots = max(1, int(recv_slots))
-        self._send_buf = torch.empty(0, dtype=torch.uint8, device=self._device)
+        self._send_slots = max(1, int(send_slots))
+        self._send_bufs = [torch.empty(0, dtype=torch.uint8, device=self._device) for _ in range(self._send_slots)]
+        self._send_work = [None] * self._send_slots
+        self._send_turn = 0
         self._recv_bufs = {kind: [torch.empty(0, dtype=torch.uint8, device=self._device)
                                   for _ in range(self._recv_slots)] for kind in ("ctx", "out")}
         self._recv_turn = {"ctx": 0, "out": 0}
@@ -113,15 +120,32 @@ class PPMessager:
         """Size the staging buffers once for the configured maxima (otherwise they grow on demand)."""
         ctx = self._ctx_layout(max_tokens, max_seqs, max_blocks_per_seq, hidden_size, True, 0, False)[1]
         out = _align16(max_seqs * 8) + _align16(max_seqs * 4) + _align16(max_seqs * vocab_size * 2)
-        self._grow_send(max(ctx, out))
+        for i in range(self._send_slots):
+            self._grow_send(max(ctx, out), i)
         for i in range(self._recv_slots):
             self._grow_recv("ctx", i, ctx)
             self._grow_recv("out", i, out)
 
-    def _grow_send(self, n: int) -> torch.Tensor:
-        if self._send_buf.numel() < n:
-            self._send_buf = torch.empty(n, dtype=torch.uint8, device=self._device)
-        return self._send_buf
+    def _grow_send(self, n: int, i: int) -> torch.Tensor:
+        if self._send_bufs[i].numel() < n:
+            self._send_bufs[i] = torch.empty(max(n, 16), dtype=torch.uint8, device=self._device)
+        return self._send_bufs[i]
+
+    def _next_send(self, n: int) -> tuple[int, torch.Tensor]:
+        """The staging buffer of this message; the transfer that last used it is waited for first."""
+        i = self._send_turn
+        self._send_turn = (i + 1) % self._send_slots
+        if self._send_work[i] is not None:
+            self._send_work[i].wait()
+            self._send_work[i] = None
+        return i, self._grow_send(n, i)
+
+    def flush(self) -> None:
+        """Wait for every payload still in flight (call before tearing the process group down)."""
+        for i, w in enumerate(self._send_work):
+            if w is not None:
+                w.wait()
+                self._send_work[i] = None
 
     def _grow_recv(self, kind: str, i: int, n: int) -> torch.Tensor:
         bufs = self._recv_bufs[kind]
@@ -228,7 +252,7 @@ class PPMessager:
             raise ValueError("block_delta needs the batch slot it applies to")
         n_delta = int(block_delta[0].numel()) if delta_mode else 0
         secs, total = self._ctx_layout(T, S, W, H, has_hidden, n_delta, delta_mode)
-        buf = self._grow_send(total)
+        turn, buf = self._next_send(total)
         for name, dtype, shape, off in secs:
             dst = self._view(buf, dtype, shape, off)
             if name == "block_delta":
@@ -245,7 +269,7 @@ class PPMessager:
         dist.send(hdr, dst=self._next_rank, group=self._next_cpu)
         if rec is not None:
             dist.send(rec, dst=self._next_rank, group=self._next_cpu)
-        self._wait([dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)])
+        self._send_work[turn] = dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)
         self.bytes_sent_last = total + hdr.numel() * 8 + (rec.numel() * 8 if rec is not None else 0)
 
     def recv_gen_ctx(self) -> GenerationContext:
@@ -296,7 +320,7 @@ class PPMessager:
         o_lp = _align16(S * 8)
         o_logits = o_lp + _align16(S * 4)
         total = o_logits + _align16(S * V * esz)
-        buf = self._grow_send(total)
+        turn, buf = self._next_send(total)
         self._view(buf, torch.int64, (S,), 0).copy_(out.token_ids)
         if has_lp:
             self._view(buf, torch.float32, (S,), o_lp).copy_(out.logprobs)
@@ -305,7 +329,7 @@ class PPMessager:
         hdr = torch.zeros(HEADER_WORDS, dtype=torch.int64)
         hdr[:6] = torch.tensor([MAGIC_OUT, S, V, has_lp, total, 1 if (V and out.logits.dtype == torch.float32) else 0])
         dist.send(hdr, dst=self._next_rank, group=self._next_cpu)
-        self._wait([dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)])
+        self._send_work[turn] = dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)
         self.bytes_sent_last = total + hdr.numel() * 8
 
     def recv_infer_out(self) -> InferencerOutput:
