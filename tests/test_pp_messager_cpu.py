@@ -164,3 +164,84 @@ def test_block_manager_matches_reference_fixture():
     a4 = mgr.allocate_blocks(16 * 9)
     assert (a1, a2, a3, a4) == (want["a1"], want["a2"], want["a3"], want["a4"])
     assert mgr.num_free_blocks() == want["free"] and mgr.num_allocated_blocks() == want["allocated"]
+
+
+def _pipeline_worker(rank, pp, port, fail_q):
+    """The benchmark's choreography with stand-in stages: a set-up round in which every stage sends before
+    it receives its feedback, then steady-state steps with `pp` batches in flight, feedback last -> first."""
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import torch.distributed as dist
+
+        from vexact_b200.config import PPInfo
+        from vexact_b200.pp_messager import GenerationContext, InferencerOutput, PPMessager
+
+        dist.init_process_group("gloo", rank=rank, world_size=pp)      # the world exists before the messager
+        S, H, W = 8, 16, 4
+        msg = PPMessager(PPInfo(pp, rank), None, torch.device("cpu"), recv_slots=pp, send_slots=2)
+        msg.reserve(H, S, S, W, 0)
+        no_delta = tuple(torch.empty(0, dtype=torch.int32) for _ in range(3))
+        mine = [GenerationContext(None, torch.full((1, S, H), float(b), dtype=torch.bfloat16),
+                                  torch.arange(S + 1, dtype=torch.int32), torch.zeros(1, S, dtype=torch.long),
+                                  torch.full((S, W), b, dtype=torch.int32), torch.ones(S, dtype=torch.int32),
+                                  torch.zeros(S, dtype=torch.int32), 1) for b in range(pp)]
+        first = [None] * pp
+
+        def hand_on(b, ctx, opening):
+            if rank < pp - 1:
+                msg.send_gen_ctx(ctx, slot=b, block_delta=None if opening else no_delta)
+            else:
+                msg.send_infer_out(InferencerOutput(torch.full((S,), b), torch.empty(0), torch.zeros(S)))
+
+        for b in range(pp):                       # set-up round
+            if rank > 0:
+                first[b] = msg.recv_gen_ctx()
+                mine[b] = first[b]
+            hand_on(b, mine[b], True)
+        pending = [rank == 0] * pp
+        for _ in range(6):                        # steady state
+            for b in range(pp):
+                if rank == 0:
+                    if pending[b]:
+                        assert int(msg.recv_infer_out().token_ids[0]) == b
+                    pending[b] = True
+                else:
+                    got = msg.recv_gen_ctx()
+                    # batch b of every round lands where its first message landed (graphs capture on these views)
+                    assert got.intermediate_tensors.data_ptr() == first[b].intermediate_tensors.data_ptr()
+                    assert got.block_tables.data_ptr() == first[b].block_tables.data_ptr()
+                    assert float(got.intermediate_tensors[0, 0, 0]) == b and int(got.block_tables[0, 0]) == b
+                hand_on(b, mine[b], False)
+        for b in range(pp):
+            if rank == 0 and pending[b]:
+                msg.recv_infer_out()
+        msg.flush()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        fail_q.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_pipeline_ring_where_every_stage_sends_before_it_receives(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pipeline_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    errs = []
+    while not q.empty():
+        errs.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append("a rank did not finish in time (a send blocked on its receiver?)")
+    assert not errs, "\n".join(errs)
+    assert all(p.exitcode == 0 for p in procs)

@@ -78,7 +78,8 @@ class PPMessager:
         self._recv_slots = max(1, int(recv_slots))
         self._send_slots = max(1, int(send_slots))
         self._send_bufs = [torch.empty(0, dtype=torch.uint8, device=self._device) for _ in range(self._send_slots)]
-        self._send_work = [None] * self._send_slots
+        self._send_work = [None] * self._send_slots     # per staging buffer: the transfers that read it
+        self._send_keep = [None] * self._send_slots
         self._send_turn = 0
         self._recv_bufs = {kind: [torch.empty(0, dtype=torch.uint8, device=self._device)
                                   for _ in range(self._recv_slots)] for kind in ("ctx", "out")}
@@ -135,17 +136,18 @@ class PPMessager:
         """The staging buffer of this message; the transfer that last used it is waited for first."""
         i = self._send_turn
         self._send_turn = (i + 1) % self._send_slots
-        if self._send_work[i] is not None:
-            self._send_work[i].wait()
-            self._send_work[i] = None
+        self._wait_slot(i)
         return i, self._grow_send(n, i)
+
+    def _wait_slot(self, i: int) -> None:
+        for w in self._send_work[i] or ():
+            w.wait()
+        self._send_work[i] = None
 
     def flush(self) -> None:
         """Wait for every payload still in flight (call before tearing the process group down)."""
-        for i, w in enumerate(self._send_work):
-            if w is not None:
-                w.wait()
-                self._send_work[i] = None
+        for i in range(self._send_slots):
+            self._wait_slot(i)
 
     def _grow_recv(self, kind: str, i: int, n: int) -> torch.Tensor:
         bufs = self._recv_bufs[kind]
@@ -266,10 +268,14 @@ class PPMessager:
                                  int(has_hidden), total, H, -1 if slot is None else int(slot), int(delta_mode), n_delta,
                                  int(rec is not None), int(bool(ctx.generation_configs)),
                                  int(ctx.tokens_generated is not None)], dtype=torch.int64)
-        dist.send(hdr, dst=self._next_rank, group=self._next_cpu)
+        # nothing here blocks on the receiver: header, record and payload are all posted asynchronously
+        # (a blocking header send deadlocks a ring in which every rank sends before it receives)
+        work = [dist.isend(hdr, dst=self._next_rank, group=self._next_cpu)]
         if rec is not None:
-            dist.send(rec, dst=self._next_rank, group=self._next_cpu)
-        self._send_work[turn] = dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)
+            work.append(dist.isend(rec, dst=self._next_rank, group=self._next_cpu))
+        work.append(dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev))
+        self._send_work[turn] = work
+        self._send_keep[turn] = (hdr, rec)     # the CPU tensors must outlive their transfers
         self.bytes_sent_last = total + hdr.numel() * 8 + (rec.numel() * 8 if rec is not None else 0)
 
     def recv_gen_ctx(self) -> GenerationContext:
@@ -328,8 +334,9 @@ class PPMessager:
             self._view(buf, out.logits.dtype, (S, V), o_logits).copy_(out.logits)
         hdr = torch.zeros(HEADER_WORDS, dtype=torch.int64)
         hdr[:6] = torch.tensor([MAGIC_OUT, S, V, has_lp, total, 1 if (V and out.logits.dtype == torch.float32) else 0])
-        dist.send(hdr, dst=self._next_rank, group=self._next_cpu)
-        self._send_work[turn] = dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)
+        self._send_work[turn] = [dist.isend(hdr, dst=self._next_rank, group=self._next_cpu),
+                                 dist.isend(buf[:total], dst=self._next_rank, group=self._next_dev)]
+        self._send_keep[turn] = (hdr, None)
         self.bytes_sent_last = total + hdr.numel() * 8
 
     def recv_infer_out(self) -> InferencerOutput:
