@@ -64,6 +64,8 @@ def parse_args():
                     help="side measurement: one chunked-prefill step of TOKENS prompt tokens after --ctx cached ones")
     ap.add_argument("--ragged-attention", action="store_true",
                     help="side measurement: decode attention over a ragged batch, with / without sequence order")
+    ap.add_argument("--unfused-head", action="store_true",
+                    help="materialise the [batch, vocab] logits and select tokens with a second kernel")
     ap.add_argument("--skew", action="store_true",
                     help="side measurement: one MoE layer of the model with near-uniform routing and with a "
                          "Zipf(1.1) router bias: rows per expert, token tiles, fc1 / fc2 time")
@@ -577,6 +579,7 @@ def main():
         kc, vc = allocate_kv_cache(shape, weights.start_layer, weights.end_layer, nblocks, args.page, device=device,
                                    fill_std=1.0, seed=b)
         runners.append(StageRunner(weights, kc, vc, rank, pp))
+        runners[-1].fused_head = not args.unfused_head   # greedy token + logprob straight from the lm_head GEMM
         kv_blocks.append(nblocks)
         if rank == 0:
             # first stage: the step's buffers are built on the device from per-request counters

@@ -90,6 +90,15 @@ int b200_gather_logprob(const void* logits, const void* labels, void* out, long 
 int b200_greedy_logprob(const void* logits, void* tokens_i64, void* logprobs_f32, long long rows, int n,
                         long long row_stride, int dtype, void* stream);
 
+/* ---- vexact/inferencer/inferencer.py:393-449 _select_tokens for greedy requests, fused with the lm_head
+ *      projection (model_loader.py:267-268): tokens[t] = argmax_v(bf16(x[t] . w[v])) (lowest index on ties),
+ *      logprobs[t] = that logit's log-softmax, without storing the [T, V] logits.  `partials` is scratch of
+ *      T * ceil(V / 128) * 16 bytes (device).  Two launches: the GEMM with a reducing epilogue, then a fold
+ *      per token in a fixed order (results do not depend on T).  Same token as b200_gemm_bf16 +
+ *      b200_greedy_logprob; log-probability within 2e-5 of theirs. */
+int b200_lm_head_greedy(const void* x, const void* w, void* partials, void* tokens_i64, void* logprobs_f32,
+                        long long T, int V, int K, long long x_row_stride, long long w_row_stride, void* stream);
+
 /* ---- vexact/inferencer/sampler.py:32-87 Sampler.batch_sample_token with uniform sampling
  *      parameters (temperature, top-k :168-173, top-p :175-181, arg-max of probs / q :146), fused
  *      with the chosen token's log-probability on the raw logits (inferencer.py:436-441).

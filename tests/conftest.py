@@ -27,3 +27,25 @@ def lib():
 
     build.build()
     return _lib.load()
+
+
+@pytest.fixture(autouse=True)
+def _device_status_word_stays_clean(request):
+    """Every GPU test must leave the device status word at zero (no bounded wait expired, no index out of
+    range): it is read before and after each test so that a report is pinned to the test that caused it."""
+    if request.node.get_closest_marker("gpu") is None:
+        yield
+        return
+    import torch
+
+    if not torch.cuda.is_available():
+        yield
+        return
+    from vexact_b200 import _lib
+
+    before = _lib.read_status()
+    assert before[0] == 0, f"status word {before} was left behind by an earlier test"
+    yield
+    torch.cuda.synchronize()
+    after = _lib.read_status()
+    assert after[0] == 0, f"{request.node.name} left the device status word at {after} (code, detail, block, -)"

@@ -111,3 +111,31 @@ def test_gemm_f32_router(vb):
 def test_status_word_clean(vb):
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+@pytest.mark.gpu
+def test_fused_lm_head_greedy_matches_two_kernel_path_and_is_batch_invariant():
+    """lm_head -> greedy token + logprob without the logits tensor: same tokens as GEMM + greedy_logprob,
+    log-probabilities within 2e-5, and a token's (token, logprob) are the same bits at batch 1 and 512."""
+    import vexact_b200 as vb
+    from vexact_b200.standalone_logprobs import greedy_token_and_logprob, lm_head_greedy
+
+    g = torch.Generator().manual_seed(21)
+    for (T, K, V) in [(512, 2048, 151936), (300, 512, 4097), (7, 256, 130)]:
+        x = torch.randn(T, K, generator=g).to(BF).cuda()
+        w = (torch.randn(V, K, generator=g) * 0.02).to(BF).cuda()
+        tok, lp = lm_head_greedy(x, w)
+        tok_ref, lp_ref = greedy_token_and_logprob(vb.linear(x, w))
+        assert torch.equal(tok, tok_ref), f"{(T, K, V)}: {(tok != tok_ref).sum().item()} tokens differ"
+        torch.testing.assert_close(lp, lp_ref, rtol=0, atol=2e-5)
+        for sub in ([0], [T - 1], list(range(0, T, max(1, T // 5)))):
+            t1, l1 = lm_head_greedy(x[sub].contiguous(), w)
+            assert torch.equal(t1, tok[sub]) and torch.equal(l1, lp[sub]), f"{(T, K, V)}: rows {sub} depend on the batch"
+    # a tie: two identical weight rows give identical logits; the lower vocabulary index wins
+    w[100] = w[3]
+    x1 = (w[3].float() * 50).to(BF)[None].contiguous()
+    t1, _ = lm_head_greedy(x1, w)
+    tr, _ = greedy_token_and_logprob(vb.linear(x1, w))
+    assert t1.item() == tr.item()
+    from vexact_b200 import _lib
+    assert _lib.read_status()[0] == 0

@@ -185,3 +185,25 @@ def test_fc1_routes_agree_bitwise(vb):
     big = vb.fused_moe_forward(E, rw, sel, x, fc2_weight=w2, fc1_1_2_weight=w13)
     small = vb.fused_moe_forward(E, rw[:100], sel[:100], x[:100], fc2_weight=w2, fc1_1_2_weight=w13)   # 25 per expert: fused
     assert torch.equal(big[:100], small)
+
+
+@pytest.mark.gpu
+def test_routing_of_nan_rows_stays_in_range():
+    """Padded tokens of a captured batch carry undefined (possibly NaN) hidden states; their routing must
+    still name experts inside [0, E) so that nothing downstream indexes out of range."""
+    import vexact_b200 as vb
+
+    E, k = 64, 6
+    logits = torch.randn(5, E, device="cuda")
+    logits[1] = float("nan")
+    logits[3, 7] = float("nan")
+    _, sel = vb.route_softmax_topk(logits, k, True)
+    assert int(sel.min()) >= 0 and int(sel.max()) < E
+    idx, _ = vb.route_sigmoid_group_topk(logits, torch.zeros(E, device="cuda"), 4, 2, k, True, 2.5)
+    assert int(idx.min()) >= 0 and int(idx.max()) < E
+    # rows without NaN are untouched by the guard
+    clean = logits[[0, 2, 4]].contiguous()
+    _, sel_c = vb.route_softmax_topk(clean, k, True)
+    assert torch.equal(sel_c, sel[[0, 2, 4]])
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0

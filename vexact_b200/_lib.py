@@ -28,6 +28,7 @@ SIGNATURES = {
     "b200_log_softmax_f32": [P, P, LL, I, LL, LL, P],
     "b200_gather_logprob": [P, P, P, LL, I, LL, I, LL, P],
     "b200_greedy_logprob": [P, P, P, LL, I, LL, I, P],
+    "b200_lm_head_greedy": [P, P, P, P, P, LL, I, I, LL, LL, P],
     "b200_sample_token": [P, P, P, P, LL, I, LL, LL, I, F, I, F, P],
     "b200_selftest_wait_expiry": [I, P, P],
     "b200_prepare_step": [P, P, P, P, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P],
@@ -113,7 +114,7 @@ def load() -> C.CDLL:
 
 
 # Kernels launched by one successful call of each entry point (for launch accounting).
-_KERNELS_PER_CALL = {"b200_moe_permute": 2, "b200_status_read": 0, "b200_abi_version": 0}
+_KERNELS_PER_CALL = {"b200_moe_permute": 2, "b200_lm_head_greedy": 2, "b200_status_read": 0, "b200_abi_version": 0}
 _launches = 0
 
 

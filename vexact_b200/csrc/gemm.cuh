@@ -68,8 +68,23 @@ struct GemmParams {
   int out_f32;
   const __nv_bfloat16* bias;       // [n_w] or null (plain mode)
   const __nv_bfloat16* row_scale;  // [rows] or null (SwiGLU mode: routing weight of each permuted row)
+  float4* head_part;               // head mode: [t_rows, w_tiles] per-tile {max, sum exp(x - max), argmax, 0}
   uint64_t w_policy;
 };
+
+// Epilogue modes of gemm_ws_kernel.
+constexpr int GEMM_PLAIN = 0;   // out = acc (+ bias)
+constexpr int GEMM_SWIGLU = 1;  // gate / up rows stacked on M, out = silu(gate) * up * row_scale
+constexpr int GEMM_HEAD = 2;    // lm_head: no logits are stored; per (token, weight tile) the maximum, the sum of
+                                // exp(x - max) and the arg-max of the tile's 128 bf16-rounded logits
+constexpr float kLog2e = 1.4426950408889634f;
+
+// 2^x on the special-function unit (relative error below 2^-22; results below the normal range flush to zero).
+__device__ __forceinline__ float gemm_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct GemmTile {
   int group, row0, n, wt;
@@ -92,10 +107,12 @@ __device__ __forceinline__ bool gemm_tile(const GemmParams& p, int t_tiles, long
   return true;
 }
 
-template <bool SWIGLU>
+template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                const GemmParams p) {
+  constexpr bool SWIGLU = MODE == GEMM_SWIGLU;
+  constexpr bool HEAD = MODE == GEMM_HEAD;
   extern __shared__ uint8_t smem_raw[];
   // Control block, then 1024-byte aligned stages (the 128-byte swizzle repeats every 1024 B).
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
@@ -226,7 +243,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (!gemm_tile(p, t_tiles, lin, t)) break;
       const int buf = tile_it & 1;
       const bool ready = ptx::mbar_wait(tfull_bar(buf), (tile_it >> 1) & 1, abort_flag, 400 + buf);
-      if (SWIGLU) {
+      if (SWIGLU || HEAD) {
         // The four epilogue warps meet at named barriers below, so they must leave together: a wait
         // that gave up has raised the abort flag before its warp arrives here, and everyone reads
         // the flag after this barrier.
@@ -238,7 +255,86 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.xrows_max);
       const int ncol = ((t.n + 15) / 16) * 16;
-      if (!SWIGLU) {
+      if (HEAD) {
+        // Thread = vocabulary row f of the tile; columns = tokens.  Per 16 columns: every logit is rounded
+        // to bf16 (the logits tensor the reference materialises is bf16), then per column the warp's
+        // maximum (redux.sync), sum of exp(x - max) (a halving butterfly: 16 shuffles for 16 columns, the
+        // same tree for every column) and lowest row holding the maximum.  The four warps' partials meet
+        // in shared memory in row order.  Nothing here depends on how many tokens share the tile.
+        const int f = t.wt * GEMM_WTILE + q * 32 + lane;
+        const bool fvalid = f < p.n_w;
+        float* hs_m = reinterpret_cast<float*>(exch);           // [4][xrows_max]
+        float* hs_s = hs_m + 4 * p.xrows_max;
+        int* hs_i = reinterpret_cast<int*>(hs_s + 4 * p.xrows_max);
+        const int mycol = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+        for (int c0 = 0; c0 < ncol; c0 += 16) {
+          uint32_t r[16];
+          ptx::tmem_ld16(taddr + c0, r);
+          ptx::tmem_ld_wait();
+          float v[16], e[16];
+          float my_m = -INFINITY;
+          int my_i = 0;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            v[j] = fvalid ? round_bf(__uint_as_float(r[j])) : -INFINITY;
+            float m;
+            asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(m) : "f"(v[j]));
+            const unsigned hit = __ballot_sync(0xffffffffu, v[j] == m);
+            e[j] = v[j] == -INFINITY ? 0.f : gemm_ex2((v[j] - m) * kLog2e);
+            if (j == mycol) {
+              my_m = m;
+              my_i = __ffs(hit) - 1;
+            }
+          }
+          // sum over the 32 rows of each of the 16 columns
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const bool up = lane & 16;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? e[i] : e[i + 8], 16);
+            e[i] = (up ? e[i + 8] : e[i]) + got;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const bool up = lane & 8;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? e[i] : e[i + 4], 8);
+            e[i] = (up ? e[i + 4] : e[i]) + got;
+          }
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const bool up = lane & 4;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? e[i] : e[i + 2], 4);
+            e[i] = (up ? e[i + 2] : e[i]) + got;
+          }
+          {
+            const bool up = lane & 2;
+            const float got = __shfl_xor_sync(0xffffffffu, up ? e[0] : e[1], 2);
+            e[0] = (up ? e[1] : e[0]) + got;
+          }
+          e[0] += __shfl_xor_sync(0xffffffffu, e[0], 1);
+          if ((lane & 1) == 0) {
+            const int c = c0 + mycol;
+            hs_m[q * p.xrows_max + c] = my_m;
+            hs_s[q * p.xrows_max + c] = e[0];
+            hs_i[q * p.xrows_max + c] = t.wt * GEMM_WTILE + q * 32 + my_i;
+          }
+        }
+        ptx::named_barrier_sync(1, 128);
+        for (int c = q * 32 + lane; c < t.n; c += 128) {
+          float m = -INFINITY;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) m = fmaxf(m, hs_m[w * p.xrows_max + c]);
+          float sum = 0.f;
+          int idx = 0x7fffffff;
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {   // rows ascend with w: the first warp holding the maximum has the lowest row
+            const float mw = hs_m[w * p.xrows_max + c];
+            if (mw != -INFINITY) sum += hs_s[w * p.xrows_max + c] * gemm_ex2((mw - m) * kLog2e);
+            if (mw == m && idx == 0x7fffffff) idx = hs_i[w * p.xrows_max + c];
+          }
+          p.head_part[(long long)(t.row0 + c) * p.w_tiles + t.wt] = make_float4(m, sum, __int_as_float(idx), 0.f);
+        }
+        ptx::named_barrier_sync(1, 128);  // the partial arrays are reused by the next tile
+      } else if (!SWIGLU) {
         const int f = t.wt * GEMM_WTILE + q * 32 + lane;
         const bool fvalid = f < p.n_w;
         const float bias = (p.bias && fvalid) ? bf2f(p.bias[f]) : 0.f;
@@ -349,13 +445,16 @@ inline int env_int(const char* name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-template <bool SWIGLU>
+template <int MODE>
 inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams& p, long long max_tiles,
                        cudaStream_t st) {
+  constexpr bool SWIGLU = MODE == GEMM_SWIGLU;
   static PerDeviceFlags attr_set;
-  if (int rc = set_max_dyn_smem_once(attr_set, gemm_ws_kernel<SWIGLU>, GEMM_SMEM_BUDGET)) return rc;
+  if (int rc = set_max_dyn_smem_once(attr_set, gemm_ws_kernel<MODE>, GEMM_SMEM_BUDGET)) return rc;
   const int atom_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
-  const int exch_bytes_pre = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
+  // epilogue scratch after the stages: the SwiGLU exchange buffer, or the head mode's per-warp partials
+  const int exch_bytes_pre = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2
+                                    : (MODE == GEMM_HEAD ? 3 * 4 * p.xrows_max * 4 : 0);
   // K atoms per stage: fewer, larger stages cut the per-stage barrier round trips; keep >= 3 stages.
   static const int ka_env = env_int("B200_GEMM_KATOMS", 2);
   int ka = (ka_env == 1 || ka_env == 2 || ka_env == 4) ? ka_env : 2;
@@ -364,7 +463,7 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
     ka >>= 1;
   p.katoms = ka;
   const int stage_bytes = atom_bytes * ka;
-  const int exch_bytes = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2 : 0;
+  const int exch_bytes = exch_bytes_pre;
   int stages = (GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes) / stage_bytes;
   if (stages > GEMM_MAX_STAGES) stages = GEMM_MAX_STAGES;
   {
@@ -380,7 +479,7 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   const size_t smem = 256 + 1024 + (size_t)stages * stage_bytes + exch_bytes;
   long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid <= 0) return B200_OK;
-  launch_k(gemm_ws_kernel<SWIGLU>, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, st, tw, tx, p);
+  launch_k(gemm_ws_kernel<MODE>, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, st, tw, tx, p);
   return launch_status();
 }
 
@@ -474,7 +573,104 @@ extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, vo
   if (rc) return rc;
   rc = make_tmap_2d(&tx, x, (uint64_t)T, (uint64_t)K, (uint64_t)x_row_stride, (uint32_t)p.xbox);
   if (rc) return rc;
-  return gemm_launch<false>(tw, tx, p, (long long)p.w_tiles * p.dense_t_tiles, (cudaStream_t)stream);
+  return gemm_launch<GEMM_PLAIN>(tw, tx, p, (long long)p.w_tiles * p.dense_t_tiles, (cudaStream_t)stream);
+}
+
+namespace b200 {
+// Second half of the fused lm_head -> greedy token + log-probability: one warp per token folds the
+// token's per-tile {max, sum exp(x - max), argmax} partials in a fixed order (lane l takes tiles l, l + 32,
+// ... in ascending order, then a butterfly over the lanes), so the result depends on the vocabulary size
+// alone.  token = lowest index holding the row maximum; logprob = max - logsumexp = -ln(sum exp(x - max)).
+struct HeadAcc {
+  float m, s;
+  int i;
+};
+__device__ __forceinline__ HeadAcc head_join(const HeadAcc& a, const HeadAcc& b) {
+  HeadAcc r;
+  r.m = fmaxf(a.m, b.m);
+  const float sa = a.m == -INFINITY ? 0.f : a.s * gemm_ex2((a.m - r.m) * kLog2e);
+  const float sb = b.m == -INFINITY ? 0.f : b.s * gemm_ex2((b.m - r.m) * kLog2e);
+  r.s = sa + sb;
+  r.i = a.m == b.m ? min(a.i, b.i) : (a.m > b.m ? a.i : b.i);
+  return r;
+}
+__global__ void __launch_bounds__(256)
+lm_head_combine_kernel(const float4* __restrict__ part, int w_tiles, long long T, long long* __restrict__ tokens,
+                       float* __restrict__ logprobs) {
+  pdl_trigger();
+  pdl_wait();
+  const long long tkn = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tkn >= T) return;
+  const int lane = threadIdx.x & 31;
+  HeadAcc acc = {-INFINITY, 0.f, 0x7fffffff};
+  for (int w = lane; w < w_tiles; w += 32) {
+    const float4 v = part[tkn * w_tiles + w];
+    acc = head_join(acc, HeadAcc{v.x, v.y, __float_as_int(v.z)});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    HeadAcc other;
+    other.m = __shfl_xor_sync(0xffffffffu, acc.m, o);
+    other.s = __shfl_xor_sync(0xffffffffu, acc.s, o);
+    other.i = __shfl_xor_sync(0xffffffffu, acc.i, o);
+    acc = head_join(acc, other);
+  }
+  if (lane == 0) {
+    tokens[tkn] = acc.i == 0x7fffffff ? 0 : acc.i;
+    logprobs[tkn] = -logf(acc.s);
+  }
+}
+}  // namespace b200
+
+// Fused lm_head -> greedy token + its log-probability without materialising the [T, V] logits
+// (vexact/inferencer/inferencer.py:393-449 for greedy requests that want scores but not logits):
+// the lm_head GEMM's epilogue reduces each 128-row weight tile to {max, sum exp, argmax} per token
+// (bf16-rounded logits, as the reference's logits tensor holds them) into `partials`
+// ([T, ceil(V / 128)] float4, caller-provided scratch), and a second kernel folds them per token.
+extern "C" int b200_lm_head_greedy(const void* x, const void* w, void* partials, void* tokens_i64,
+                                   void* logprobs_f32, long long T, int V, int K, long long x_row_stride,
+                                   long long w_row_stride, void* stream) {
+  using namespace b200;
+  if (!x || !w || !partials || !tokens_i64 || !logprobs_f32 || T < 0 || V <= 0 || K <= 0) return B200_ERR_ARG;
+  if (K % 8 != 0 || x_row_stride % 8 != 0 || w_row_stride % 8 != 0) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  if (T > 0x7fffffffLL) return B200_ERR_SHAPE;
+  GemmParams p{};
+  p.n_w = V;
+  p.k = K;
+  p.w_tiles = (V + GEMM_WTILE - 1) / GEMM_WTILE;
+  p.w_rows_per_group = V;
+  p.t_rows = (int)T;
+  {   // token tiling: the dense GEMM's cost model (a token's arithmetic does not depend on its tile)
+    const int sms = sm_count();
+    const int min_tiles = (int)((T + 255) / 256), max_tiles = (int)((T + 15) / 16);
+    long long best_cost = -1;
+    for (int tt = min_tiles; tt <= max_tiles; ++tt) {
+      const int rows = round_up((int)((T + tt - 1) / tt), 16);
+      const int tiles_t = (int)((T + rows - 1) / rows);
+      const long long rounds = ((long long)tiles_t * p.w_tiles + sms - 1) / sms;
+      const long long cost = rounds * (GEMM_WBYTES + rows * GEMM_BK * 2);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        p.rows_per_tile = rows;
+        p.dense_t_tiles = tiles_t;
+      }
+    }
+  }
+  p.xbox = p.rows_per_tile;
+  p.xrows_max = p.rows_per_tile;
+  p.head_part = (float4*)partials;
+  p.w_policy = p.dense_t_tiles == 1 ? ptx::kEvictFirst : ptx::kEvictNormal;
+  CUtensorMap tw, tx;
+  int rc = make_tmap_2d(&tw, w, (uint64_t)V, (uint64_t)K, (uint64_t)w_row_stride, GEMM_WTILE);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, x, (uint64_t)T, (uint64_t)K, (uint64_t)x_row_stride, (uint32_t)p.xbox);
+  if (rc) return rc;
+  rc = gemm_launch<GEMM_HEAD>(tw, tx, p, (long long)p.w_tiles * p.dense_t_tiles, (cudaStream_t)stream);
+  if (rc) return rc;
+  launch_k(lm_head_combine_kernel, dim3((unsigned)((T + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+           (const float4*)partials, p.w_tiles, T, (long long*)tokens_i64, (float*)logprobs_f32);
+  return launch_status();
 }
 
 // Grouped GEMM over expert-sorted rows.
@@ -519,6 +715,6 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* r
   rc = make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, (uint32_t)p.xbox);
   if (rc) return rc;
   const long long tiles = (long long)max_tiles * p.w_tiles;
-  if (mode == 1) return gemm_launch<true>(tw, tx, p, tiles, (cudaStream_t)stream);
-  return gemm_launch<false>(tw, tx, p, tiles, (cudaStream_t)stream);
+  if (mode == 1) return gemm_launch<GEMM_SWIGLU>(tw, tx, p, tiles, (cudaStream_t)stream);
+  return gemm_launch<GEMM_PLAIN>(tw, tx, p, tiles, (cudaStream_t)stream);
 }

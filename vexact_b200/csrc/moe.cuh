@@ -50,7 +50,12 @@ __device__ __forceinline__ void route_softmax_topk_token(const TIn* __restrict__
   }
   sum = warp_sum(sum);
 #pragma unroll
-  for (int i = 0; i < PER; ++i) v[i] = v[i] / sum;  // softmax probabilities (fp32)
+  for (int i = 0; i < PER; ++i) {
+    v[i] = v[i] / sum;  // softmax probabilities (fp32)
+    // A row of NaN logits (a padded token of a captured batch: its hidden state is never defined) must
+    // still select experts inside [0, E): NaN compares false with everything, so it counts as 0 here.
+    if (!(v[i] == v[i])) v[i] = 0.f;
+  }
 
   float sel_w[MOE_MAX_TOPK];
   int sel_e[MOE_MAX_TOPK];
@@ -75,6 +80,7 @@ __device__ __forceinline__ void route_softmax_topk_token(const TIn* __restrict__
         be = oe;
       }
     }
+    if (be < 0 || be >= E) be = 0;  // unreachable for topk <= E
     sel_w[k] = bv;
     sel_e[k] = be;
     if ((be & 31) == lane) {
@@ -138,9 +144,14 @@ moe_route_sigmoid_group_topk_kernel(const float* __restrict__ logits, long long 
   float* sig = s_sig[wib];
   float* choice = s_choice[wib];
   for (int e = lane; e < E; e += 32) {
-    const float s = 1.0f / (1.0f + expf(-row[e]));
+    float s = 1.0f / (1.0f + expf(-row[e]));
+    // NaN logits (a padded token of a captured batch) count as score 0, so that the selection below
+    // always finds candidates inside [0, E)
+    if (!(s == s)) s = 0.f;
+    float c = s + (bias ? bias[e] : 0.f);
+    if (!(c == c)) c = 0.f;
     sig[e] = s;
-    choice[e] = s + (bias ? bias[e] : 0.f);
+    choice[e] = c;
   }
   __syncwarp();
   const int gsize = E / n_group;
@@ -197,6 +208,7 @@ moe_route_sigmoid_group_topk_kernel(const float* __restrict__ logits, long long 
         be = oe;
       }
     }
+    if (be < 0 || be >= E) be = 0;  // unreachable for topk <= E; keeps the shared-memory accesses in range regardless
     sel_e[k] = be;
     sel_w[k] = sig[be];
     __syncwarp();

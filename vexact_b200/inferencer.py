@@ -25,7 +25,7 @@ from .attention import paged_attention
 from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
 from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
                         route_softmax_topk)
-from .standalone_logprobs import greedy_token_and_logprob
+from .standalone_logprobs import greedy_token_and_logprob, lm_head_greedy
 from .sampler import sample_token_and_logprob
 
 BF = torch.bfloat16
@@ -263,6 +263,9 @@ class StageRunner:
         self._dense_tiles: dict = {}
         # None = greedy; else dict(temperature=..., top_k=..., top_p=...) applied to every request
         self.sampling: Optional[dict] = None
+        # greedy decoding without the [num_seqs, vocab] logits: lm_head and token selection fused
+        # (`select_tokens` then returns None for the logits)
+        self.fused_head = False
 
     # -- dense MLP through the grouped-GEMM kernel's fused SwiGLU epilogue (one group)
     def _dense_plan(self, T: int, device):
@@ -394,13 +397,17 @@ class StageRunner:
         (The reference runs lm_head over every packed token and gathers afterwards,
         model_loader.py:267-268 + inferencer.py:403-404; the GEMM is row-invariant, so gathering first
         gives the same rows.)"""
+        return linear(self.last_token_hidden(h, inp), self.w.lm_head)
+
+    def last_token_hidden(self, h: torch.Tensor, inp: StepInputs) -> torch.Tensor:
         last = (inp.query_start_loc[1:] - 1).to(torch.long)
-        rows = h.index_select(0, last.clamp(min=0))
-        xn = self._norm(rows, self.w.final_norm)
-        return linear(xn, self.w.lm_head)
+        return self._norm(h.index_select(0, last.clamp(min=0)), self.w.final_norm)
 
     def select_tokens(self, h: torch.Tensor, inp: StepInputs):
         """Last stage: last-token logits -> greedy (or sampled) token + its logprob."""
+        if self.fused_head and self.sampling is None:
+            tokens, logprobs = lm_head_greedy(self.last_token_hidden(h, inp), self.w.lm_head)
+            return tokens, logprobs, None
         logits = self.last_token_logits(h, inp)
         if self.sampling is None:
             tokens, logprobs = greedy_token_and_logprob(logits)
@@ -458,6 +465,8 @@ class StageOutput:
     hidden_states: Optional[torch.Tensor] = None   # [1, T, H]
     logits: Optional[torch.Tensor] = None          # never materialised for all tokens here
     last_logits: Optional[torch.Tensor] = None     # [num_seqs, vocab] (last stage)
+    greedy_tokens: Optional[torch.Tensor] = None   # [num_seqs] int64 (last stage, fused head)
+    greedy_logprobs: Optional[torch.Tensor] = None  # [num_seqs] fp32
 
 
 class StageModel:
@@ -466,8 +475,11 @@ class StageModel:
     `model(input_ids=[1, T], intermediate_tensors=[1, T, H], position_ids=[1, T], **forward_kwargs)`.
     Attention metadata and the KV caches come from the thread-local KV-cache context, as for HF."""
 
-    def __init__(self, weights: StageWeights, pp_rank: int = 0, pp_size: int = 1):
+    def __init__(self, weights: StageWeights, pp_rank: int = 0, pp_size: int = 1, fused_greedy: bool = False):
+        """fused_greedy: the last stage returns greedy tokens + log-probabilities from the fused lm_head
+        instead of last-token logits (for deployments that only decode greedily and never return logits)."""
         self.runner = StageRunner(weights, {}, {}, pp_rank, pp_size)
+        self.fused_greedy = fused_greedy
         self.config = None
         self.layer_ids = range(weights.start_layer, weights.end_layer)
 
@@ -493,7 +505,10 @@ class StageModel:
         h = r.forward(inp)
         out = StageOutput(hidden_states=h[None])
         if r.is_last:
-            out.last_logits = r.last_token_logits(h, inp)
+            if self.fused_greedy:
+                out.greedy_tokens, out.greedy_logprobs = lm_head_greedy(r.last_token_hidden(h, inp), r.w.lm_head)
+            else:
+                out.last_logits = r.last_token_logits(h, inp)
         return out
 
     __call__ = forward
@@ -752,6 +767,15 @@ class Inferencer:
     def _select_tokens(self, gen_configs, tokens_generated, outputs, gen_ctx):
         num_seqs = gen_ctx.context_lens.size(0)
         last_logits = getattr(outputs, "last_logits", None)
+        if getattr(outputs, "greedy_tokens", None) is not None:
+            # fused head: tokens and log-probabilities came out of the forward; nothing else is available
+            ref = gen_configs[0]
+            if any(g.do_sample and (g.temperature or 0) > 0 for g in gen_configs) or getattr(ref, "output_logits", False):
+                raise RuntimeError("the model was built with fused_greedy: sampling and output_logits need logits")
+            logprobs = outputs.greedy_logprobs[:num_seqs]
+            if not any(getattr(g, "output_scores", False) for g in gen_configs):
+                logprobs = torch.empty(0, device=self.device)
+            return outputs.greedy_tokens[:num_seqs], torch.empty(0, device=self.device), logprobs
         if last_logits is not None:
             batched_logits = last_logits[:num_seqs]
         else:   # an HF module: logits of every packed token, gather the last one of each request

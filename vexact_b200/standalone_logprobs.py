@@ -58,3 +58,31 @@ def greedy_token_and_logprob(logits: torch.Tensor):
         "b200_greedy_logprob",
     )
     return tokens.reshape(logits.shape[:-1]), lp.reshape(logits.shape[:-1])
+
+
+def lm_head_greedy(hidden: torch.Tensor, lm_head_weight: torch.Tensor):
+    """(argmax token ids int64 [T], their log-probabilities fp32 [T]) of `hidden @ lm_head_weight.T` without
+    materialising the [T, vocab] logits: the lm_head GEMM reduces every 128-row weight tile to a
+    (max, sum exp, argmax) triple per token in its epilogue and a second kernel folds the triples in a
+    fixed order.  Same tokens as `linear` + `greedy_token_and_logprob` (logits rounded to bf16, lowest
+    index on ties); log-probabilities within 2e-5 of theirs; a token's result does not depend on T."""
+    if not hidden.is_cuda or not lm_head_weight.is_cuda:
+        raise ValueError("hidden and lm_head_weight must be CUDA tensors")
+    if hidden.dtype != torch.bfloat16 or lm_head_weight.dtype != torch.bfloat16:
+        raise NotImplementedError("the fused head is implemented for bf16")
+    x = hidden.reshape(-1, hidden.shape[-1])
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    w = lm_head_weight if lm_head_weight.stride(-1) == 1 else lm_head_weight.contiguous()
+    T, K = x.shape
+    V = w.shape[0]
+    assert w.shape[1] == K, "Incompatible dimensions"
+    partials = torch.empty((T, (V + 127) // 128, 4), device=x.device, dtype=torch.float32)
+    tokens = torch.empty((T,), device=x.device, dtype=torch.int64)
+    lp = torch.empty((T,), device=x.device, dtype=torch.float32)
+    _lib.check(
+        _lib.load().b200_lm_head_greedy(x.data_ptr(), w.data_ptr(), partials.data_ptr(), tokens.data_ptr(),
+                                        lp.data_ptr(), T, V, K, x.stride(0), w.stride(0), _lib.current_stream()),
+        "b200_lm_head_greedy",
+    )
+    return tokens, lp
