@@ -2,6 +2,8 @@
 ground truth the reference tests use, and the bitwise invariance properties of
 tests/batch_invariant_ops/test_triton_attention_varlen.py:398-558 (batched == single sequence,
 prefill last token == decode, chunked == full prefill, MLA head dims)."""
+import os
+
 import pytest
 import torch
 
@@ -221,3 +223,33 @@ def test_sequence_order_changes_no_result(vb):
     with pytest.raises(ValueError):
         vb.paged_attention(q, kc, vc, cu, used, table, d ** -0.5, int(qlens.max()),
                            seq_order=torch.arange(S - 1).int().cuda())
+
+
+def test_rows_kernel_and_columns_kernel_give_the_same_bits(vb):
+    """Head dim 128 prefill runs the rows-on-lanes kernel; B200_ATTN_PREFILL=cols runs the keys-on-lanes
+    kernel on the same step.  Both are written to perform the same operations per (position, head), so a
+    mixed prefill / chunk / decode batch must come out bit-identical (and equal to decode steps, which
+    test_prefill_chunked_decode_bitwise checks against whichever prefill kernel is active)."""
+    g = torch.Generator().manual_seed(77)
+    for (hq, hkv, page, q_lens, ctx) in [(32, 4, 16, [130, 40, 1, 7], [130, 200, 257, 7]),
+                                         (16, 8, 256, [300, 1], [300, 513]),
+                                         (12, 2, 16, [257, 64], [1000, 64]),
+                                         (16, 1, 16, [70], [70])]:
+        S, d = len(ctx), 128
+        pages = max((c + page - 1) // page for c in ctx)
+        kc = torch.randn(S * pages + 1, page, hkv, d, generator=g).to(BF).cuda()
+        vc = torch.randn(S * pages + 1, page, hkv, d, generator=g).to(BF).cuda()
+        table = torch.randperm(S * pages, generator=g).view(S, pages).to(torch.int32).cuda()
+        q = torch.randn(sum(q_lens), hq, d, generator=g).to(BF).cuda()
+        cu = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32).cuda()
+        used = torch.tensor(ctx, dtype=torch.int32).cuda()
+        kw = dict(cu_seqlens_q=cu, max_seqlen_q=max(q_lens), seqused_k=used, page_table=table,
+                  softmax_scale=d ** -0.5, causal=True)
+        rows, _ = vb.flash_attn_varlen_func(q, kc, vc, **kw)
+        os.environ["B200_ATTN_PREFILL"] = "cols"
+        try:
+            cols, _ = vb.flash_attn_varlen_func(q, kc, vc, **kw)
+        finally:
+            del os.environ["B200_ATTN_PREFILL"]
+        torch.cuda.synchronize()
+        assert torch.equal(rows, cols), f"{(hq, hkv, page, q_lens)}: max diff {(rows.float() - cols.float()).abs().max()}"

@@ -390,6 +390,13 @@ inline bool attn_use_tensor_memory() {
 }
 int attn_tc_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid, int dk, int nc,
                      cudaStream_t st);
+int attn_rows_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t st);
+// Prefill tiles of head dim 128: rows-on-lanes kernel unless B200_ATTN_PREFILL=cols.
+// (Read at every call, so that a test can run both kernels in one process and compare their bits.)
+inline bool attn_prefill_rows() {
+  const char* v = getenv("B200_ATTN_PREFILL");
+  return !(v && v[0] == 'c');
+}
 
 }  // namespace b200
 
@@ -486,8 +493,12 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
   const int hh = group < 8 ? group : 8;
   if (attn_use_tensor_memory() && dv == 128 && (dk == 128 || dk == 192) && q_tok_stride % 8 == 0 &&
       q_head_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0) {
-    // tcgen05 kernel: NC columns per CTA; a decode step (one query per sequence) uses the narrow tile
-    const int nc = max_seqlen_q == 1 ? 16 : (dk == 128 ? 64 : 32);
+    // tcgen05 kernels.  A decode step (one query per sequence) uses the narrow keys-on-lanes tile (16
+    // columns); steps with longer query runs use 128-row tiles with a row per thread (attn_rows.cuh) for
+    // head dim 128 and the 32-column keys-on-lanes tile for the 192 / 128 dims.  B200_ATTN_PREFILL=cols
+    // keeps the 64-column keys-on-lanes tile for head dim 128 (the same bits, for cross-checks).
+    const bool rows = max_seqlen_q > 1 && dk == 128 && attn_prefill_rows();
+    const int nc = max_seqlen_q == 1 ? 16 : (dk == 128 ? (rows ? 128 : 64) : 32);
     p.pos_per_tile = nc / hh;
     dim3 grid((unsigned)((max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile),
               (unsigned)(num_kv_heads * p.head_chunks), (unsigned)num_seqs);
@@ -501,6 +512,7 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
     }
     p.num_seqs = num_seqs;
     p.seq_order = (const int*)seq_order;
+    if (rows) return attn_rows_dispatch(tk, tv, p, st);
     return attn_tc_dispatch(tk, tv, p, grid, dk, nc, st);
   }
   const int q_tiles = (max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile;

@@ -22,9 +22,10 @@
 // value dim tl when it reads O^T - for half of the columns (the two warps of a lane quadrant split
 // the column groups of four): two warps per scheduler hide each other's latencies.  Per block it
 // publishes its warp's per-column maximum (redux.sync), takes the new running maximum, writes
-// p = 2^(s - m) as bf16 into the P^T tile, adds p to its own per-key share of the row sum and folds the
-// previous block's O^T into its fp32 accumulators; the 128 shares of a row sum meet at the end of
-// the tile in a fixed tree.
+// p = 2^(s - m) as bf16 into the P^T tile, adds the block's p over its warp's 32 keys (a butterfly, xor
+// 16 / 8 / 4 / 2 / 1) into that key group's running row sum (l_g = l_g * alpha + s_g) and folds the previous
+// block's O^T into its fp32 accumulators; the four group sums of a row meet at the end of the tile as
+// (l_0 + l_1) + (l_2 + l_3).  attn_rows.cuh performs the same operations with a row per thread.
 //
 // Invariance: a column's arithmetic (block order, rescale, bf16 rounding of P before the PV product
 // and before the row sum, the row-sum tree) does not depend on NC, on the other columns or on the
@@ -62,6 +63,43 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Sums N per-lane values over the 32 lanes of a warp for N columns at once: at each butterfly step a lane
+// keeps half of its columns and hands the other half to its partner, so N columns cost N - 1 + (5 - log2 N)
+// shuffles instead of 5 N.  Every column is added in the plain butterfly order (xor 16, 8, 4, 2, 1).  On
+// return e[0] holds the sum of column `halving_col<N>(lane)`.
+template <int N>
+__device__ __forceinline__ int halving_col(int lane) {
+  int col = 0, cnt = N;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    if (cnt > 1) {
+      cnt >>= 1;
+      if (lane & o) col += cnt;
+    }
+  }
+  return col;
+}
+template <int N>
+__device__ __forceinline__ void halving_warp_sum(float (&e)[N], int lane) {
+  int cnt = N;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    if (cnt > 1) {
+      cnt >>= 1;
+      const bool up = lane & o;
+#pragma unroll
+      for (int i = 0; i < N / 2; ++i) {
+        if (i < cnt) {
+          const float got = __shfl_xor_sync(0xffffffffu, up ? e[i] : e[i + cnt], o);
+          e[i] = (up ? e[i + cnt] : e[i]) + got;
+        }
+      }
+    } else {
+      e[0] += __shfl_xor_sync(0xffffffffu, e[0], o);
+    }
+  }
 }
 
 // One unit of work: NC columns of one (sequence, KV head[, head chunk]) pair.
@@ -408,6 +446,7 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
     const int tl = q4 * 32 + lane;     // TMEM lane
     const uint32_t lane_addr = (uint32_t)(q4 * 32) << 16;
     auto gcol = [&](int lg) { return (2 * lg + hsel) * 4; };  // first column of my group lg
+    const int mycol = halving_col<NCL>(lane);                 // the local column whose row sum I end up holding
     // my key's 2-byte slot in row c of the P^T tile (K-major, 128-byte swizzle) is
     // p_mine + c*128 + ((p_ch ^ (c&7)) << 4); for column i of my group lg that is p_slot[i] + lg*1024
     uint8_t* p_mine = p_ptr + (tl >> 6) * (NC * 128) + (tl & 7) * 2;
@@ -440,12 +479,12 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       ptx::named_barrier_sync(3, NCT);
       if (*abort_flag) break;
 
-      float o_acc[NCL], l_part[NCL];
+      float o_acc[NCL];
+      float l_w = 0.f;   // running row sum of my warp's 32 keys for local column `mycol`
       float m_run[LOCAL_M ? NCL : 1];
 #pragma unroll
       for (int c = 0; c < NCL; ++c) {
         o_acc[c] = 0.f;
-        l_part[c] = 0.f;
         if constexpr (LOCAL_M) m_run[c] = -INFINITY;
       }
       // scale and causal mask of four raw scores of my key, columns gc..gc+3
@@ -524,6 +563,10 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         if (j > 0) go = __all_sync(0xffffffffu, ptx::mbar_wait(ofull_bar, (g - 1) & 1, abort_flag, 650));
         if (go) {
           ptx::tc_fence_after();
+          float pfl[NCL];       // this block's bf16-rounded p of my key, per local column
+          float a_mine = 0.f;   // alpha of local column `mycol`
+#pragma unroll
+          for (int c = 0; c < NCL; ++c) pfl[c] = 0.f;
 #pragma unroll
           for (int ch0 = 0; ch0 < NG; ch0 += CHG) {
             uint32_t rc[CHG][4], ro[CHG][4];
@@ -576,7 +619,8 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
                     m_run[lc] = mv[k][i];
                   }
                   pb[k][i] = f2bf(fast_exp2(v[k][i] - mv[k][i]));
-                  l_part[lc] = l_part[lc] * av[k][i] + bf2f(pb[k][i]);
+                  pfl[lc] = bf2f(pb[k][i]);
+                  if (lc == mycol) a_mine = av[k][i];
                   // (the first block finds o = 0 and no O^T yet: the product below is 0 either way)
                   o_acc[lc] += j > 0 ? __uint_as_float(ro[k][i]) : 0.f;
                   o_acc[lc] *= av[k][i];
@@ -594,6 +638,9 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
               }
             }
           }
+          // the block's p summed over my warp's 32 keys, every column in butterfly order
+          halving_warp_sum<NCL>(pfl, lane);
+          l_w = l_w * a_mine + pfl[0];
           // every thread orders its own tensor-memory reads and shared-memory writes, then one lane
           // per warp arrives (256 arrivals on one barrier word would serialise)
           ptx::tc_fence_before();
@@ -627,23 +674,9 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ofree_bar);
-        // row sums: the 128 per-key shares are added in a fixed tree (5 butterfly steps, then 4 warps)
-#pragma unroll
-        for (int lg = 0; lg < NG; ++lg) {
-          const int gc = gcol(lg);
-          if (live(gc)) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              float v = l_part[lg * 4 + i];
-              v += __shfl_xor_sync(0xffffffffu, v, 16);
-              v += __shfl_xor_sync(0xffffffffu, v, 8);
-              v += __shfl_xor_sync(0xffffffffu, v, 4);
-              v += __shfl_xor_sync(0xffffffffu, v, 2);
-              v += __shfl_xor_sync(0xffffffffu, v, 1);
-              if (lane == i) s_lred[gc + i][q4] = v;
-            }
-          }
-        }
+        // row sums: each warp publishes its key group's sum of every column it holds; the four groups
+        // are added as (l_0 + l_1) + (l_2 + l_3) below
+        s_lred[gcol(mycol >> 2) + (mycol & 3)][q4] = l_w;
       }
       ptx::named_barrier_sync(3, NCT);
       if (*abort_flag) break;  // uniform over the compute threads: read after a common barrier

@@ -6,6 +6,7 @@
 #include "gemm.cuh"
 #include "attn.cuh"
 #include "attn_tc.cuh"
+#include "attn_rows.cuh"
 #include "moe.cuh"
 #include "noalloc.cuh"
 #include "step.cuh"

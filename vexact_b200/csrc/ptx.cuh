@@ -78,6 +78,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-level bounded wait: lane 0 polls the barrier, the warp then re-converges.  One poller per warp instead
+// of 32 keeps the barrier word free for the arrivals it is waiting for (hundreds of threads polling one word
+// delay every arrive / commit on it).  __all_sync orders the other lanes' later reads after lane 0's acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, id);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Same, for long waits: backs off with nanosleep so that a waiting warp leaves the issue slots and
 // the barrier unit to the warps that are working.
 __device__ __forceinline__ bool mbar_wait_sleep(uint32_t bar, uint32_t parity, volatile int* abort_flag, int id) {
