@@ -396,12 +396,16 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
           }
           ptx::tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[16];
-            ptx::tmem_ld16(o_addr + c * 16, r);
+          for (int c = 0; c < 2; ++c) {   // two 16-column loads in flight per wait
+            uint32_t r0[16], r1[16];
+            ptx::tmem_ld16(o_addr + c * 32, r0);
+            ptx::tmem_ld16(o_addr + c * 32 + 16, r1);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[c * 16 + i] = (o[c * 16 + i] + __uint_as_float(r[i])) * alpha;
+            for (int i = 0; i < 16; ++i) {
+              o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(r0[i])) * alpha;
+              o[c * 32 + 16 + i] = (o[c * 32 + 16 + i] + __uint_as_float(r1[i])) * alpha;
+            }
           }
           ptx::tc_fence_before();
           __syncwarp();

@@ -113,8 +113,11 @@ struct AtcRaw {
   int q_start, q_end, kv_len, seq, eff;
 };
 
-// Tiles are numbered with the query tile fastest, then the KV head, then the sequence slot; slot i is
-// sequence seq_order[i] when the caller gives an order (longest contexts first), else sequence i.
+// Tiles are numbered with the KV head fastest, then the sequence slot, then the query tile from the LAST
+// tile of a sequence down to the first: under the causal mask a later query tile walks more key blocks,
+// so the numbering runs from the most expensive tiles to the cheapest and the round-by-round dealing below
+// hands every CTA a similar total.  Slot i is sequence seq_order[i] when the caller gives an order
+// (longest contexts first), else sequence i.
 // The persistent CTAs take the tiles round by round, every other round in reverse ("snake"): with a
 // longest-first order the CTAs' totals then differ by about one tile however ragged the batch is.
 // Position `lin` of a CTA's walk (blockIdx.x + round * gridDim.x) maps to tile `eff`, or to none in the
@@ -130,7 +133,7 @@ __device__ __forceinline__ AtcRaw atc_raw(const AttnParams& p, int lin) {
   AtcRaw r = {0, 0, 0, 0, -1};
   r.eff = atc_eff(p, lin);
   if (r.eff < 0) return r;
-  const int slot = r.eff / (p.tc_q_tiles * p.tc_hy);
+  const int slot = (r.eff % (p.tc_hy * p.num_seqs)) / p.tc_hy;
   r.seq = p.seq_order ? p.seq_order[slot] : slot;
   if (r.seq < 0 || r.seq >= p.num_seqs) {  // a bad order entry: skip the tile, flag it
     report_status(B200_STATUS_BAD_INDEX, r.seq);
@@ -152,9 +155,8 @@ __device__ __forceinline__ AtcRaw atc_raw(const AttnParams& p, int lin) {
 template <int NC>
 __device__ __forceinline__ void atc_make(const AttnParams& p, int lin, const AtcRaw& r, AtcTile& t) {
   const int eff = r.eff < 0 ? 0 : r.eff;
-  const int x = eff % p.tc_q_tiles;
-  const int rest = eff / p.tc_q_tiles;
-  const int y = rest % p.tc_hy;
+  const int x = p.tc_q_tiles - 1 - eff / (p.tc_hy * p.num_seqs);
+  const int y = eff % p.tc_hy;
   t.seq = r.seq;
   t.kvh = y / p.head_chunks;
   t.hchunk = y % p.head_chunks;
