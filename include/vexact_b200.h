@@ -57,12 +57,24 @@ int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, lo
 int b200_gemm_f32(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
                   long long x_row_stride, long long w_row_stride, long long out_row_stride, void* stream);
 
+/* Same product on bf16 tensors widened to fp32 on the fly: bit-identical to b200_gemm_f32 on x.float(),
+ * w.float() (the router module's casts), without the fp32 copies. */
+int b200_gemm_f32_from_bf16(const void* x, const void* w, void* out, long long T, int N, int K,
+                            long long x_row_stride, long long w_row_stride, long long out_row_stride, void* stream);
+
 /* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:728 batch_invariant_rms_norm (mode 0:
  *      fp32 math, one rounding) and the HF eager RMSNorm the reference reaches through its
  *      aten::mean.dim override, :619 mean_batch_invariant (mode 1: x*rsqrt(var+eps) rounded to
  *      bf16, then multiplied by the weight). */
 int b200_rmsnorm(const void* x, const void* weight, void* out, long long rows, int n, long long x_row_stride,
                  long long out_row_stride, float eps, int mode, void* stream);
+
+/* ---- vexact/batch_invariant_ops/batch_invariant_ops.py:701-725 BatchInvariantRMSNormFunction.backward (the
+ *      training-side twin of mode 0): grad_in = inv * (d - normed * mean(d * normed)) with d = grad_out * w,
+ *      grad_weight = sum over rows of grad_out * normed, reduced in a fixed order (64-row partials, then the
+ *      partials ascending).  All tensors bf16 contiguous; scratch_f32 holds rows + ceil(rows / 64) * n floats. */
+int b200_rmsnorm_backward(const void* x, const void* weight, const void* grad_out, void* grad_in, void* grad_weight,
+                          void* scratch_f32, long long rows, int n, float eps, void* stream);
 
 /* sum_out = bf16(residual + x); out = rmsnorm(sum_out).  All tensors [rows, n] contiguous.
  * The decoder layer's "residual add, then norm" (HF Qwen3DecoderLayer.forward) in one pass. */

@@ -253,3 +253,35 @@ def test_rows_kernel_and_columns_kernel_give_the_same_bits(vb):
             del os.environ["B200_ATTN_PREFILL"]
         torch.cuda.synchronize()
         assert torch.equal(rows, cols), f"{(hq, hkv, page, q_lens)}: max diff {(rows.float() - cols.float()).abs().max()}"
+
+
+def test_packed_varlen_forward_equals_paged_prefill_bitwise(vb):
+    """The training-side packed call (no page table) must give the rollout's bits: same tokens through the
+    packed path and through a paged prefill with another page size and a shuffled page table."""
+    g = torch.Generator().manual_seed(91)
+    hq, hkv, d = 16, 8, 128
+    lens = [70, 1, 300, 33]
+    total = sum(lens)
+    q = torch.randn(total, hq, d, generator=g).to(BF).cuda()
+    k = torch.randn(total, hkv, d, generator=g).to(BF).cuda()
+    v = torch.randn(total, hkv, d, generator=g).to(BF).cuda()
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32).cuda()
+    packed, _ = vb.flash_attn_varlen_func(q, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
+                                          max_seqlen_k=max(lens), causal=True)
+    page = 64
+    pages = max((n + page - 1) // page for n in lens)
+    table = torch.randperm(len(lens) * pages, generator=g).view(len(lens), pages).to(torch.int32)
+    kc = torch.zeros(len(lens) * pages, page, hkv, d, dtype=BF).cuda()
+    vc = torch.zeros_like(kc)
+    slots = torch.cat([table[s, torch.arange(n) // page].long() * page + torch.arange(n) % page
+                       for s, n in enumerate(lens)]).to(torch.int32).cuda()
+    vb.store_kvcache(k, v, kc, vc, slots)
+    paged, _ = vb.flash_attn_varlen_func(q, kc, vc, cu_seqlens_q=cu, max_seqlen_q=max(lens),
+                                         seqused_k=torch.tensor(lens, dtype=torch.int32).cuda(),
+                                         page_table=table.cuda(), causal=True)
+    assert torch.equal(packed, paged)
+    with pytest.raises(NotImplementedError):
+        qq = q.clone().requires_grad_(True)
+        out, _ = vb.flash_attn_varlen_func(qq, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
+                                           max_seqlen_k=max(lens), causal=True)
+        out.float().sum().backward()

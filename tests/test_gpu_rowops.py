@@ -221,3 +221,30 @@ def test_mla_rope_store(vb):
 def test_status_word_clean(vb):
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+@pytest.mark.gpu
+def test_rms_norm_backward_matches_reference_formula_and_is_row_invariant():
+    """BatchInvariantRMSNormFunction.backward (batch_invariant_ops.py:701-725) restated in fp32 torch."""
+    import vexact_b200 as vb
+
+    g = torch.Generator().manual_seed(5)
+    rows, n, eps = 200, 2048, 1e-6
+    x = torch.randn(rows, n, generator=g).to(BF).cuda().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(n, generator=g)).to(BF).cuda().requires_grad_(True)
+    go = torch.randn(rows, n, generator=g).to(BF).cuda()
+    y = vb.batch_invariant_rms_norm(x, w, eps)
+    y.backward(go)
+    xf, wf, gf = x.detach().float(), w.detach().float(), go.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    normed = xf * inv
+    d = gf * wf
+    gx_ref = inv * (d - normed * (d * normed).mean(-1, keepdim=True))
+    gw_ref = (gf * normed).sum(0)
+    torch.testing.assert_close(x.grad.float(), gx_ref, rtol=2 ** -7, atol=2e-3)
+    torch.testing.assert_close(w.grad.float(), gw_ref, rtol=2 ** -6, atol=5e-2)
+    # a row's input gradient does not depend on the batch it is in
+    x1 = x.detach()[7:8].clone().requires_grad_(True)
+    w1 = w.detach().clone().requires_grad_(True)
+    vb.batch_invariant_rms_norm(x1, w1, eps).backward(go[7:8])
+    assert torch.equal(x1.grad[0], x.grad[7])

@@ -138,3 +138,19 @@ def test_block_table_deltas_and_device_resident_tokens():
         buf.prepare([9, 3], [1, 1], None, graph_num_seqs=1, capture_tokens=4)
     with pytest.raises(ValueError):
         buf.prepare([9, 3], [1, 1], None, graph_num_seqs=2, capture_tokens=1)
+
+
+@pytest.mark.gpu
+def test_token_feedback_keeps_tokens_on_device_and_reads_them_with_one_wait():
+    from vexact_b200.step_inputs import StepBuffers, TokenFeedback
+
+    sb = StepBuffers("cuda", 8, 32, 4, 16)
+    fb = TokenFeedback(sb, depth=2)
+    t1 = torch.tensor([5, 6, 7], device="cuda")
+    t2 = torch.tensor([8, 9, 10], device="cuda")
+    k1 = fb.push(t1, torch.tensor([-0.5, -1.0, -1.5], device="cuda"))
+    assert torch.equal(sb.last_tokens[:3], t1)
+    k2 = fb.push(t2)                       # the next step is queued before the first one is read
+    assert fb.pop(k1) == ([5, 6, 7], [-0.5, -1.0, -1.5])
+    assert fb.pop(k2) == ([8, 9, 10], None)
+    assert torch.equal(sb.last_tokens[:3], t2)

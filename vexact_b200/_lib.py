@@ -22,7 +22,9 @@ SIGNATURES = {
     "b200_status_read": [C.POINTER(C.c_int), P],
     "b200_gemm_bf16": [P, P, P, P, LL, I, I, LL, LL, LL, I, P],
     "b200_gemm_f32": [P, P, P, P, LL, I, I, LL, LL, LL, P],
+    "b200_gemm_f32_from_bf16": [P, P, P, LL, I, I, LL, LL, LL, P],
     "b200_rmsnorm": [P, P, P, LL, I, LL, LL, F, I, P],
+    "b200_rmsnorm_backward": [P, P, P, P, P, P, LL, I, F, P],
     "b200_add_rmsnorm": [P, P, P, P, P, LL, I, F, I, P],
     "b200_mean_lastdim": [P, P, LL, I, LL, I, P],
     "b200_log_softmax_f32": [P, P, LL, I, LL, LL, P],
@@ -114,7 +116,7 @@ def load() -> C.CDLL:
 
 
 # Kernels launched by one successful call of each entry point (for launch accounting).
-_KERNELS_PER_CALL = {"b200_moe_permute": 2, "b200_lm_head_greedy": 2, "b200_status_read": 0, "b200_abi_version": 0}
+_KERNELS_PER_CALL = {"b200_moe_permute": 2, "b200_lm_head_greedy": 2, "b200_rmsnorm_backward": 3, "b200_status_read": 0, "b200_abi_version": 0}
 _launches = 0
 
 

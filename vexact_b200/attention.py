@@ -100,8 +100,13 @@ def flash_attn_varlen_func(
     cache_seqlens: Optional[torch.Tensor] = None,
     **kwargs,
 ):
-    """FlashAttention-style varlen call; returns (out, None).  Paged KV only."""
-    del alibi_slopes, deterministic, return_attn_probs, kwargs, cu_seqlens_k, max_seqlen_k
+    """FlashAttention-style varlen call; returns (out, None).
+
+    With `page_table` / `block_table`: the paged rollout path.  Without: the packed path the training side
+    uses (triton_invariant_attention.py:48-192, forward only): K / V are laid into a temporary paged cache
+    and run through the same kernel, so a token gets the same bits from the packed call as from the rollout's
+    paged prefill.  The packed backward kernels (:194-431) are not part of this library: gradients raise."""
+    del alibi_slopes, deterministic, return_attn_probs, kwargs
     if dropout_p != 0.0:
         raise NotImplementedError("dropout is not supported")
     if softcap not in (None, 0.0):
@@ -112,8 +117,19 @@ def flash_attn_varlen_func(
         raise ValueError("pass only one of page_table or block_table")
     table = page_table if page_table is not None else block_table
     if table is None:
-        raise NotImplementedError(
-            "the packed (non-paged) varlen path is the training-side twin and is not part of this library")
+        if cu_seqlens_q is None:
+            raise ValueError("cu_seqlens_q is required when page_table/block_table is not provided")
+        if cu_seqlens_k is None:
+            raise ValueError("cu_seqlens_k is required when page_table/block_table is not provided")
+        if max_seqlen_k is None:
+            raise ValueError("max_seqlen_k is required when page_table/block_table is not provided")
+        if max_seqlen_q is None:
+            raise ValueError("max_seqlen_q is required when page_table/block_table is not provided")
+        if not causal:
+            raise NotImplementedError("the packed path supports causal=True only")
+        scale = softmax_scale if softmax_scale is not None else q.shape[-1] ** -0.5
+        return _PackedVarlenForward.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, float(scale), int(max_seqlen_q),
+                                          int(max_seqlen_k)), None
     lens = seqused_k if seqused_k is not None else cache_seqlens
     if lens is None:
         raise ValueError("seqused_k or cache_seqlens is required when page_table/block_table is provided")
@@ -124,6 +140,50 @@ def flash_attn_varlen_func(
         # The reference kernel ignores max_seqlen_q; this one sizes its grid with it.
         max_seqlen_q = q.shape[0]
     return paged_attention(q, k, v, cu_seqlens_q, lens, table, scale, int(max_seqlen_q)), None
+
+
+PACKED_PAGE = 16   # page size of the temporary cache behind the packed path
+
+
+def packed_to_paged(k: torch.Tensor, v: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_k: int,
+                    page: int = PACKED_PAGE):
+    """Packed K / V [total_k, kv_heads, d] -> (k_cache, v_cache, page_table [S, W], kv_lens [S]): every
+    sequence gets its own consecutive pages.  All index math runs on the device (no host sync); the block
+    count is the host-side upper bound total_k / page + S."""
+    total_k, hkv, dk = k.shape
+    S = cu_seqlens_k.numel() - 1
+    dev = k.device
+    cu = cu_seqlens_k.to(torch.int64)
+    lens = cu[1:] - cu[:-1]
+    pages = (lens + page - 1) // page
+    base = torch.cumsum(pages, 0) - pages                               # first page of each sequence
+    W = max(1, (int(max_seqlen_k) + page - 1) // page)
+    cols = torch.arange(W, device=dev)
+    table = torch.where(cols[None, :] < pages[:, None], base[:, None] + cols[None, :],
+                        torch.full((), -1, device=dev, dtype=torch.int64)).to(torch.int32).contiguous()
+    tok = torch.arange(total_k, device=dev)
+    seq = torch.searchsorted(cu[1:].contiguous(), tok, right=True).clamp_(max=S - 1)
+    pos = tok - cu[seq]
+    slots = ((base[seq] + pos // page) * page + pos % page).to(torch.int32)
+    nblocks = total_k // page + S + 1
+    k_cache = torch.empty((nblocks, page, hkv, dk), device=dev, dtype=k.dtype)
+    v_cache = torch.empty((nblocks, page, hkv, v.shape[-1]), device=dev, dtype=v.dtype)
+    store_kvcache(k.contiguous(), v.contiguous(), k_cache, v_cache, slots)
+    return k_cache, v_cache, table, lens.to(torch.int32)
+
+
+class _PackedVarlenForward(torch.autograd.Function):
+    """Forward of the packed path; its backward kernels are the training side's and are not built here."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, scale, max_seqlen_q, max_seqlen_k):
+        k_cache, v_cache, table, lens = packed_to_paged(k, v, cu_seqlens_k, max_seqlen_k)
+        cu_q = cu_seqlens_q if cu_seqlens_q.dtype == torch.int32 else cu_seqlens_q.to(torch.int32)
+        return paged_attention(q, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        raise NotImplementedError("the packed varlen backward (dq / dkv kernels) is not part of this library")
 
 
 def flash_attention_forward(

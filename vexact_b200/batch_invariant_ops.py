@@ -30,6 +30,7 @@ __all__ = [
     "hf_rms_norm",
     "add_rms_norm",
     "linear",
+    "linear_f32_from_bf16",
 ]
 
 RMS_SINGLE_ROUND = 0
@@ -84,6 +85,29 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         )
     else:
         raise NotImplementedError(f"matmul for dtype {x.dtype} is not implemented")
+    return out.reshape(*x.shape[:-1], N)
+
+
+def linear_f32_from_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """`F.linear(x.float(), weight.float())` for bf16 tensors without the fp32 copies (same bits): the
+    DeepSeek-V3 router projection (modeling_deepseek_v3.py:97-100)."""
+    _require_cuda("x", x)
+    _require_cuda("weight", weight)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return linear(x.float(), weight.float())
+    K, N = x.shape[-1], weight.shape[0]
+    assert weight.shape[1] == K, "Incompatible dimensions"
+    x2 = x.reshape(-1, K)
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    if weight.stride(-1) != 1:
+        weight = weight.contiguous()
+    out = torch.empty((x2.shape[0], N), device=x.device, dtype=torch.float32)
+    _lib.check(
+        _lib.load().b200_gemm_f32_from_bf16(x2.data_ptr(), weight.data_ptr(), out.data_ptr(), x2.shape[0], N, K,
+                                            x2.stride(0), weight.stride(0), out.stride(0), _lib.current_stream()),
+        "b200_gemm_f32_from_bf16",
+    )
     return out.reshape(*x.shape[:-1], N)
 
 
@@ -171,8 +195,43 @@ def _rms_norm(input: torch.Tensor, weight: torch.Tensor, eps: float, mode: int) 
     return out.reshape(input.shape)
 
 
+class BatchInvariantRMSNormFunction(torch.autograd.Function):
+    """Batch-invariant RMSNorm with the backward the training side needs.
+    Reference: batch_invariant_ops.py:691-725 (same saved tensors, same formulas)."""
+
+    @staticmethod
+    def forward(ctx, input, weight, eps):
+        output = _rms_norm(input, weight, eps, RMS_SINGLE_ROUND)
+        ctx.save_for_backward(input, weight)
+        ctx.eps = eps
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight = ctx.saved_tensors
+        n = input.shape[-1]
+        if input.dtype != torch.bfloat16:
+            raise NotImplementedError("the RMSNorm backward kernel is implemented for bf16")
+        x2 = input.reshape(-1, n).contiguous()
+        g2 = grad_output.reshape(-1, n).to(torch.bfloat16).contiguous()
+        w = weight.to(torch.bfloat16).contiguous()
+        rows = x2.shape[0]
+        gx = torch.empty_like(x2)
+        gw = torch.empty_like(w)
+        scratch = torch.empty(rows + (rows + 63) // 64 * n, device=x2.device, dtype=torch.float32)
+        _lib.check(
+            _lib.load().b200_rmsnorm_backward(x2.data_ptr(), w.data_ptr(), g2.data_ptr(), gx.data_ptr(), gw.data_ptr(),
+                                              scratch.data_ptr(), rows, n, float(ctx.eps), _lib.current_stream()),
+            "b200_rmsnorm_backward",
+        )
+        return gx.reshape(input.shape), gw.to(weight.dtype), None
+
+
 def batch_invariant_rms_norm(input: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
-    """fp32 math, one rounding.  Reference: batch_invariant_ops.py:728 (forward only)."""
+    """fp32 math, one rounding.  Reference: batch_invariant_ops.py:728 (an autograd Function there and here;
+    without gradients in play this is a plain kernel call)."""
+    if torch.is_grad_enabled() and (input.requires_grad or weight.requires_grad):
+        return BatchInvariantRMSNormFunction.apply(input, weight, eps)
     return _rms_norm(input, weight, eps, RMS_SINGLE_ROUND)
 
 

@@ -489,19 +489,24 @@ namespace b200 {
 // fp32 GEMM for the DeepSeek-V3 router (modeling_deepseek_v3.py:97-100 runs F.linear in fp32):
 // one warp per output element, lanes stride over K, fixed butterfly.  Exact fp32 FMA arithmetic
 // (the reference's Triton path feeds tl.dot fp32 operands, i.e. TF32 inputs).
+// TIn = float, or __nv_bfloat16 operands widened to fp32 on the fly: the same arithmetic as converting the
+// tensors first (x.float() @ w.float().T), without the two conversion kernels and their copies.
+template <typename TIn>
 __global__ void __launch_bounds__(256)
-gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+gemm_f32_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const float* __restrict__ bias,
                 float* __restrict__ out, long long T, int N, int K, long long x_stride, long long w_stride,
                 long long out_stride) {
+  pdl_trigger();
+  pdl_wait();
   const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (wid >= T * N) return;
   const int lane = threadIdx.x & 31;
   const long long t = wid / N;
   const int n = (int)(wid % N);
-  const float* xr = x + t * x_stride;
-  const float* wr = w + (long long)n * w_stride;
+  const TIn* xr = x + t * x_stride;
+  const TIn* wr = w + (long long)n * w_stride;
   float acc = 0.f;
-  for (int k = lane; k < K; k += 32) acc = fmaf(xr[k], wr[k], acc);
+  for (int k = lane; k < K; k += 32) acc = fmaf((float)xr[k], (float)wr[k], acc);
   acc = warp_sum(acc);
   if (lane == 0) out[t * out_stride + n] = acc + (bias ? bias[n] : 0.f);
 }
@@ -514,9 +519,25 @@ extern "C" int b200_gemm_f32(const void* x, const void* w, const void* bias, voi
   if (!x || !w || !out || T < 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
   if (T == 0) return B200_OK;
   const long long warps = T * N;
-  gemm_f32_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-      (const float*)x, (const float*)w, (const float*)bias, (float*)out, T, N, K, x_row_stride, w_row_stride,
-      out_row_stride);
+  launch_k(gemm_f32_kernel<float>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+           (const float*)x, (const float*)w, (const float*)bias, (float*)out, T, N, K, x_row_stride, w_row_stride,
+           out_row_stride);
+  return launch_status();
+}
+
+// The DeepSeek-V3 router on bf16 tensors: out_f32[T, N] = float(x) @ float(w)^T, bit-identical to
+// b200_gemm_f32 on x.float() and w.float() (what PatchDeepseekV3TopkRouter.forward computes,
+// modeling_deepseek_v3.py:97-100) without materialising the fp32 copies every step.
+extern "C" int b200_gemm_f32_from_bf16(const void* x, const void* w, void* out, long long T, int N, int K,
+                                       long long x_row_stride, long long w_row_stride, long long out_row_stride,
+                                       void* stream) {
+  using namespace b200;
+  if (!x || !w || !out || T < 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
+  if (T == 0) return B200_OK;
+  const long long warps = T * N;
+  launch_k(gemm_f32_kernel<__nv_bfloat16>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream,
+           (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)nullptr, (float*)out, T, N, K,
+           x_row_stride, w_row_stride, out_row_stride);
   return launch_status();
 }
 

@@ -252,3 +252,95 @@ extern "C" int b200_mean_lastdim(const void* x, void* out, long long rows, int n
   }
   return launch_status();
 }
+
+// ------------------------------------------------------------------ RMSNorm backward (training-side twin)
+// Follows BatchInvariantRMSNormFunction.backward (vexact/batch_invariant_ops/batch_invariant_ops.py:701-725):
+//   inv = rsqrt(mean(x^2) + eps); normed = x * inv; d = g * w
+//   grad_x = inv * (d - normed * mean(d * normed))                       (per row: batch invariant)
+//   grad_w = sum over rows of g * normed                                 (fixed order: see below)
+// grad_w is reduced in two fixed stages, 64 consecutive rows per partial and then the partials in ascending
+// order, so the result depends on the row count only (the reference's torch .sum(0) leaves its order to
+// the library).
+namespace b200 {
+
+constexpr int RMSB_ROWS_PER_PARTIAL = 64;
+
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                       const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ gx,
+                       float* __restrict__ inv_out, int n, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * n;
+  const __nv_bfloat16* gr = g + row * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = bf2f(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum(ss, scratch) / (float)n + eps);
+  float dot = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float d = bf2f(gr[i]) * bf2f(w[i]);
+    dot = fmaf(d, bf2f(xr[i]) * inv, dot);
+  }
+  const float c = block_sum(dot, scratch) / (float)n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float normed = bf2f(xr[i]) * inv;
+    const float d = bf2f(gr[i]) * bf2f(w[i]);
+    gx[row * n + i] = f2bf(inv * (d - normed * c));
+  }
+  if (threadIdx.x == 0) inv_out[row] = inv;
+}
+
+// partial[blk][col] = sum over the block's rows (ascending) of g * x * inv
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_wpartial_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ g,
+                            const float* __restrict__ inv, float* __restrict__ partial, long long rows, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  const long long r0 = (long long)blockIdx.y * RMSB_ROWS_PER_PARTIAL;
+  const long long r1 = r0 + RMSB_ROWS_PER_PARTIAL < rows ? r0 + RMSB_ROWS_PER_PARTIAL : rows;
+  float acc = 0.f;
+  for (long long r = r0; r < r1; ++r) acc += bf2f(g[r * n + col]) * (bf2f(x[r * n + col]) * inv[r]);
+  partial[(long long)blockIdx.y * n + col] = acc;
+}
+
+__global__ void __launch_bounds__(256)
+rmsnorm_bwd_wfinal_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ gw, int nparts, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  float acc = 0.f;
+  for (int b = 0; b < nparts; ++b) acc += partial[(long long)b * n + col];
+  gw[col] = f2bf(acc);
+}
+
+}  // namespace b200
+
+// x, grad_out, grad_in [rows, n] bf16 contiguous; weight, grad_weight [n] bf16.
+// scratch: fp32, rows + ceil(rows / 64) * n elements (inverse norms, then the grad_weight partials).
+extern "C" int b200_rmsnorm_backward(const void* x, const void* weight, const void* grad_out, void* grad_in,
+                                     void* grad_weight, void* scratch_f32, long long rows, int n, float eps,
+                                     void* stream) {
+  using namespace b200;
+  if (!x || !weight || !grad_out || !grad_in || !grad_weight || !scratch_f32 || rows < 0 || n <= 0) return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  if (rows > 0x7fffffffLL) return B200_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  float* inv = (float*)scratch_f32;
+  float* partial = inv + rows;
+  const int nparts = (int)((rows + RMSB_ROWS_PER_PARTIAL - 1) / RMSB_ROWS_PER_PARTIAL);
+  launch_k(rmsnorm_bwd_row_kernel, dim3((unsigned)rows), dim3(256), 0, st, (const __nv_bfloat16*)x,
+           (const __nv_bfloat16*)weight, (const __nv_bfloat16*)grad_out, (__nv_bfloat16*)grad_in, inv, n, eps);
+  launch_k(rmsnorm_bwd_wpartial_kernel, dim3((unsigned)((n + 255) / 256), (unsigned)nparts), dim3(256), 0, st,
+           (const __nv_bfloat16*)x, (const __nv_bfloat16*)grad_out, (const float*)inv, partial, rows, n);
+  launch_k(rmsnorm_bwd_wfinal_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const float*)partial,
+           (__nv_bfloat16*)grad_weight, nparts, n);
+  return launch_status();
+}

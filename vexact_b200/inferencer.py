@@ -22,7 +22,7 @@ import torch
 
 from . import _lib
 from .attention import paged_attention
-from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear
+from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear, linear_f32_from_bf16
 from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
                         route_softmax_topk)
 from .standalone_logprobs import greedy_token_and_logprob, lm_head_greedy
@@ -360,7 +360,7 @@ class StageRunner:
         m = s.moe
         if m.scoring == "sigmoid_group":
             # PatchDeepseekV3TopkRouter: F.linear in fp32, then route_tokens_to_experts; experts + shared experts
-            logits = linear(xn.float(), lw.router.float())
+            logits = linear_f32_from_bf16(xn, lw.router)
             sel, rw = route_sigmoid_group_topk(logits, lw.router_bias, m.n_group, m.topk_group, m.top_k,
                                                m.norm_topk_prob, m.routed_scaling_factor)
             shared = None

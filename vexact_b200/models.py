@@ -67,7 +67,7 @@ def _deepseek_v3_moe_forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
     """fp32 router logits -> sigmoid / bias / group-limited top-k -> fused experts + shared experts."""
     lead = hidden_states.shape[:-1]
     x = hidden_states.reshape(-1, hidden_states.shape[-1])
-    logits = bio.linear(x.float(), self.gate.weight.float())          # F.linear in fp32 (the router module's cast)
+    logits = bio.linear_f32_from_bf16(x, self.gate.weight)            # F.linear in fp32 (the router module's casts)
     experts, weights = route_sigmoid_group_topk(logits, self.gate.e_score_correction_bias, self.n_group,
                                                 self.topk_group, self.top_k, bool(self.norm_topk_prob),
                                                 float(self.routed_scaling_factor))

@@ -151,3 +151,50 @@ class StepBuffers:
             self.step_info.data_ptr(), _lib.current_stream())
         _lib.check(rc, "b200_prepare_step")
 
+
+
+class TokenFeedback:
+    """The device half of `Scheduler.update` (vexact/core/scheduler.py:211-235).
+
+    The reference moves a step's tokens to the host with `.cpu()` and then reads them one `.item()` at a
+    time while the GPU idles.  Here a step's tokens (and log-probabilities) are (1) written into the step
+    buffers' `last_tokens`, so that the next decode step reads its input ids from device memory, and
+    (2) copied asynchronously into one of `depth` pinned host buffers; the scheduler collects a step's
+    results with ONE event wait, typically a step late, while the next step is already running.
+    """
+
+    def __init__(self, step_buffers: StepBuffers, depth: int = 2):
+        self.sb = step_buffers
+        S = step_buffers.max_num_seqs
+        pin = step_buffers.device.type == "cuda"
+        self._tok = [torch.empty(S, dtype=torch.long, pin_memory=pin) for _ in range(depth)]
+        self._lp = [torch.empty(S, dtype=torch.float32, pin_memory=pin) for _ in range(depth)]
+        self._ev = [torch.cuda.Event() if pin else None for _ in range(depth)]
+        self._n = [0] * depth
+        self._has_lp = [False] * depth
+        self._turn = 0
+
+    def push(self, tokens: torch.Tensor, logprobs: Optional[torch.Tensor] = None) -> int:
+        """Queue a step's results (row i = request i of the step); returns the ticket to `pop` them with."""
+        n = tokens.shape[0]
+        if n > self.sb.max_num_seqs:
+            raise ValueError("more tokens than requests the step buffers hold")
+        i = self._turn
+        self._turn = (i + 1) % len(self._tok)
+        self.sb.last_tokens[:n].copy_(tokens)                     # next decode step's input ids, on the device
+        self._tok[i][:n].copy_(tokens, non_blocking=True)
+        self._has_lp[i] = logprobs is not None and logprobs.numel() > 0
+        if self._has_lp[i]:
+            self._lp[i][:n].copy_(logprobs, non_blocking=True)
+        self._n[i] = n
+        if self._ev[i] is not None:
+            self._ev[i].record()
+        return i
+
+    def pop(self, ticket: int):
+        """(token ids, log-probabilities or None) of a queued step as Python lists: one wait for the batch."""
+        if self._ev[ticket] is not None:
+            self._ev[ticket].synchronize()
+        n = self._n[ticket]
+        lps = self._lp[ticket][:n].tolist() if self._has_lp[ticket] else None
+        return self._tok[ticket][:n].tolist(), lps
