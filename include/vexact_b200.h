@@ -122,6 +122,13 @@ int b200_sample_token(const void* logits, const void* noise_q_f32, void* tokens_
                       long long rows, int n, long long row_stride, long long q_row_stride, int dtype,
                       float temperature, int top_k, float top_p, void* stream);
 
+/* ---- vexact/inferencer/sampler.py:57-63, 90-118 seeded sampling (per-request seed, keyed by token position):
+ *      fills noise_q_f32 [rows, n] with Exp(1) draws from Philox4x32-10 (key = seeds[r], counter = (column / 4,
+ *      positions[r], 0)), to be passed to b200_sample_token.  A request's draws depend on its seed, the position
+ *      and the column only.  Same construction as the vLLM kernel the reference calls, not the same stream. */
+int b200_seeded_exponential(void* noise_q_f32, const void* seeds_i64, const void* positions_i64, long long rows,
+                            int n, long long q_row_stride, void* stream);
+
 /* ---- vexact/inferencer/inferencer.py:193-291 Inferencer._prepare_gen_ctx and :293-349
  *      _prepare_input_buffers_from_gen_ctx: one scheduler step's padded input buffers, built on the
  *      device from per-request counters instead of per-token host loops.

@@ -103,3 +103,65 @@ def test_sampling_frequencies_follow_the_distribution():
     probs = torch.softmax(logits[0], -1)
     assert (freq - probs).abs().max().item() < 0.015
     assert torch.allclose(lp, torch.log_softmax(logits[0], -1)[tok], atol=1e-5)
+
+
+def test_philox_restatement_known_answers():
+    """The published Philox4x32-10 known-answer vectors (Random123 kat_vectors: zero, all-ones and pi inputs)."""
+    import numpy as np
+
+    def run(c, k):
+        return tuple(int(w[0]) for w in oracle_sampler.philox4x32_10([np.array([v]) for v in c], [np.array([v]) for v in k]))
+
+    assert run((0, 0, 0, 0), (0, 0)) == (0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8)
+    assert run((0xFFFFFFFF,) * 4, (0xFFFFFFFF,) * 2) == (0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD)
+    assert run((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0)) == (
+        0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1)
+
+
+@pytest.mark.gpu
+def test_seeded_noise_matches_the_restatement_and_ignores_the_batch():
+    from vexact_b200.sampler import seeded_exponential_noise
+
+    vocab = 151936 + 3            # not a multiple of four: the last counter is used in part
+    seeds = torch.tensor([0, 1, 2**40 + 17, -5, 123456789], dtype=torch.int64)
+    pos = torch.tensor([0, 7, 2**33 + 1, 4095, 7], dtype=torch.int64)
+    q = seeded_exponential_noise(seeds.cuda(), pos.cuda(), vocab)
+    want = oracle_sampler.seeded_exponential(seeds.tolist(), pos.tolist(), vocab)
+    assert torch.isfinite(q).all() and (q > 0).all()
+    torch.testing.assert_close(q.cpu(), want, rtol=2e-6, atol=1e-7)      # logf against a rounded float64 log
+    # a request's noise depends on (seed, position) only: alone, reordered or repeated it is the same bits
+    alone = seeded_exponential_noise(seeds[2:3].cuda(), pos[2:3].cuda(), vocab)
+    assert torch.equal(alone[0], q[2])
+    perm = torch.tensor([4, 2, 0, 3, 1])
+    assert torch.equal(seeded_exponential_noise(seeds[perm].cuda(), pos[perm].cuda(), vocab), q[perm.cuda()])
+    assert not torch.equal(q[1, :64], q[4, :64])           # same position, different seed
+    assert abs(float(q.mean()) - 1.0) < 5e-3 and abs(float(q.var()) - 1.0) < 2e-2
+
+
+@pytest.mark.gpu
+def test_seeded_sampler_is_reproducible_per_request():
+    from types import SimpleNamespace
+
+    from vexact_b200.sampler import Sampler
+
+    torch.manual_seed(5)
+    logits = (torch.randn(6, 32000, device="cuda") * 3).to(torch.bfloat16)
+    cfgs = [SimpleNamespace(do_sample=True, temperature=0.8, top_k=50, top_p=0.95, seed=100 + i) for i in range(6)]
+    pos = torch.arange(10, 16, device="cuda")
+    s = Sampler()
+    t1, lp1 = s.batch_sample_token_and_logprob(logits, cfgs, pos)
+    t2, lp2 = s.batch_sample_token_and_logprob(logits, cfgs, pos)
+    assert torch.equal(t1, t2) and torch.equal(lp1, lp2)
+    sub = [4, 1]
+    t3, _ = s.batch_sample_token_and_logprob(logits[sub], [cfgs[i] for i in sub], pos[sub])
+    assert torch.equal(t3, t1[sub])
+    # against the restatement: the same noise through the reference's sampler arithmetic
+    noise = oracle_sampler.seeded_exponential([c.seed for c in cfgs], pos.tolist(), 32000)
+    want = oracle_sampler.sample(logits.cpu(), True, 0.8, 50, 0.95, noise)
+    assert (t1.cpu() == want).float().mean() >= 5 / 6          # an ulp of the logarithm may move a near tie
+    t4, _ = s.batch_sample_token_and_logprob(logits, cfgs, pos + 1)
+    assert not torch.equal(t4, t1)
+    with pytest.raises(ValueError):
+        s.batch_sample_token_and_logprob(logits, cfgs[:5] + [SimpleNamespace(**{**vars(cfgs[5]), "seed": None})], pos)
+    with pytest.raises(ValueError):
+        s.batch_sample_token_and_logprob(logits, cfgs, None)

@@ -293,3 +293,59 @@ extern "C" int b200_sample_token(const void* logits, const void* noise_q_f32, vo
     launch_k(sample_token_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(SMP_THREADS), 0, st, p);
   return launch_status();
 }
+
+// ------------------------------------------------------------------ per-request seeded noise
+// Seeded sampling (vexact/inferencer/sampler.py:57-63, 90-118) keys the random stream of a request by its
+// seed and by the absolute position of the token being sampled, so a request draws the same token whatever
+// batch it sits in.  The reference delegates this to vLLM's Gumbel kernel; here the Exp(1) noise the
+// sampling kernel consumes (token = argmax softmax / q) is generated with Philox4x32-10 (Salmon et al.,
+// "Parallel random numbers: as easy as 1, 2, 3", SC'11): key = the 64-bit seed, counter = (column / 4,
+// position low, position high, 0), four uniforms per counter, u = (x + 0.5) * 2^-32, q = -ln(u).  It is the
+// same construction, not the same stream: tokens differ from vLLM's for a given seed.
+namespace b200 {
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                                              uint32_t k1, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+    c0 = n0, c1 = n1, c2 = n2, c3 = n3;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0, out[1] = c1, out[2] = c2, out[3] = c3;
+}
+
+__global__ void __launch_bounds__(256)
+seeded_exponential_kernel(float* __restrict__ q, const long long* __restrict__ seeds,
+                          const long long* __restrict__ positions, int n, long long q_stride) {
+  pdl_trigger();
+  pdl_wait();
+  const long long row = blockIdx.y;
+  const unsigned long long seed = (unsigned long long)seeds[row], pos = (unsigned long long)positions[row];
+  const int quad = blockIdx.x * blockDim.x + threadIdx.x;   // columns 4 quad .. 4 quad + 3
+  if (quad * 4 >= n) return;
+  uint32_t x[4];
+  philox4x32_10((uint32_t)quad, (uint32_t)pos, (uint32_t)(pos >> 32), 0u, (uint32_t)seed, (uint32_t)(seed >> 32), x);
+  float* dst = q + row * q_stride + (long long)quad * 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    if (quad * 4 + i < n) dst[i] = -logf(((float)x[i] + 0.5f) * 2.3283064365386963e-10f);
+}
+
+}  // namespace b200
+
+extern "C" int b200_seeded_exponential(void* noise_q_f32, const void* seeds_i64, const void* positions_i64,
+                                       long long rows, int n, long long q_row_stride, void* stream) {
+  using namespace b200;
+  if (!noise_q_f32 || !seeds_i64 || !positions_i64 || rows < 0 || n <= 0) return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  if (rows > 65535) return B200_ERR_SHAPE;
+  const int quads = (n + 3) / 4;
+  launch_k(seeded_exponential_kernel, dim3((unsigned)((quads + 255) / 256), (unsigned)rows), dim3(256), 0,
+           (cudaStream_t)stream, (float*)noise_q_f32, (const long long*)seeds_i64, (const long long*)positions_i64, n,
+           q_row_stride);
+  return launch_status();
+}

@@ -785,15 +785,22 @@ class Inferencer:
         uniform = all((g.do_sample == ref.do_sample and g.temperature == ref.temperature and g.top_k == ref.top_k
                        and g.top_p == ref.top_p) for g in gen_configs)
         assert uniform
-        if any(getattr(g, "seed", None) is not None for g in gen_configs):
-            raise NotImplementedError("per-request seeds need the seeded sampler, which this library does not have")
         scored = self.use_fp32_logits and batched_logits.dtype != torch.float32
         sample_logits = batched_logits.float() if scored else batched_logits
         assert ref.top_p is not None, "top_p must be set (use 1.0 to disable)"
         do_sample = bool(ref.do_sample) and (ref.temperature or 0) > 0 and float(ref.top_p) > 0
         if do_sample:
+            noise = None
+            seeds = [getattr(g, "seed", None) for g in gen_configs]
+            if any(s is not None for s in seeds):     # vLLM-style: RNG keyed by request seed and token position
+                if not all(s is not None for s in seeds):
+                    raise ValueError("Seeded sampling requires every request in the batch to set seed.")
+                from .sampler import seeded_exponential_noise
+                seed_t = torch.tensor([int(s) for s in seeds], dtype=torch.int64).to(self.device, non_blocking=True)
+                noise = seeded_exponential_noise(seed_t, gen_ctx.context_lens.to(torch.long) - 1,
+                                                 sample_logits.shape[-1])
             tokens, logprobs = sample_token_and_logprob(sample_logits, float(ref.temperature), ref.top_k,
-                                                        float(ref.top_p))
+                                                        float(ref.top_p), True, noise)
         else:
             tokens, logprobs = greedy_token_and_logprob(sample_logits)
         logits = batched_logits.detach() if getattr(ref, "output_logits", False) else torch.empty(0, device=self.device)
