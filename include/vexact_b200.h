@@ -238,6 +238,23 @@ int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, v
                           int n_out, int K, long long out_row_stride, int max_tiles, int tile_rows_max, int mode,
                           void* stream);
 
+/* ---- vexact/batch_invariant_ops/fused_moe.py:268-292 _build_moe_indices + :319-322 quack gemm(A, ..., A_idx=):
+ *      the permutation without the permuted copy.  b200_moe_permute_index writes scatter_index, cu_seqlens and
+ *      the tile table like b200_moe_permute, plus gather_index [T*topk] i32 (sorted row -> token: the
+ *      reference's A_idx) and row_scale [T*topk] bf16 (routing weight of each sorted row; may be null), in one
+ *      launch.  b200_moe_grouped_gemm_gather is b200_moe_grouped_gemm reading sorted row r from
+ *      x[gather_index[r]] of the unpermuted x [T, K] (rows x_row_stride elements apart); same bits as the
+ *      GEMM on the permuted copy.  tile_rows_max <= 128. */
+int b200_moe_permute_index(const void* experts, int experts_dtype, const void* weights_bf16, void* scatter_index,
+                           void* cu_seqlens, void* gather_index, void* row_scale, void* tile_table,
+                           void* tile_count, long long T, int topk, int E, int tile_rows, int max_tiles,
+                           void* stream);
+int b200_moe_grouped_gemm_gather(const void* x, long long T, long long x_row_stride, const void* gather_index,
+                                 const void* w, const void* row_scale, void* out, const void* tile_table,
+                                 const void* tile_count, int num_groups, int n_out, int K,
+                                 long long out_row_stride, int max_tiles, int tile_rows_max, int mode,
+                                 void* stream);
+
 /* No counterpart in the reference.  b200_moe_grouped_gemm for callers that cannot allocate device
  * memory (a C/C++ host with statically owned buffers, a thread barred from cudaMalloc while a
  * stream capture is open, a service with a fixed memory budget): rows already sorted by group

@@ -187,6 +187,54 @@ def test_fc1_routes_agree_bitwise(vb):
     assert torch.equal(big[:100], small)
 
 
+@pytest.mark.parametrize("T,E,k,H,I,skew", [(1, 8, 2, 64, 32, False), (7, 16, 4, 256, 128, False),
+                                            (300, 8, 2, 512, 192, True), (512, 128, 8, 2048, 768, False),
+                                            (600, 8, 2, 256, 128, False)])
+def test_fc1_gathering_its_rows_equals_the_permuted_copy_bitwise(vb, monkeypatch, T, E, k, H, I, skew):
+    """fc1 reading x[gather_index[r]] (one-row TMA boxes, four rows per gather) against fc1 over the
+    expert-sorted copy of x: the same bytes land in the same shared-memory rows, so every output bit agrees;
+    with fused and with split fc1 weights, and from a strided view of the activations."""
+    hidden, gate_up, down, sel, rw = _moe_case(T, E, k, H, I, seed=11, skew=skew)
+    args = (E, rw.cuda(), sel.cuda())
+    wide = torch.zeros(T, H + 64, dtype=BF, device="cuda")
+    wide[:, :H] = hidden.cuda()
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("B200_MOE_GATHER", mode)
+        outs[mode] = (
+            vb.fused_moe_forward(*args, hidden.cuda(), fc2_weight=down.cuda(), fc1_1_2_weight=gate_up.cuda()),
+            vb.fused_moe_forward(*args, hidden.cuda(), gate_up[:, :I].contiguous().cuda(),
+                                 gate_up[:, I:].contiguous().cuda(), down.cuda()),
+            vb.fused_moe_forward(*args, wide[:, :H], fc2_weight=down.cuda(), fc1_1_2_weight=gate_up.cuda()),
+        )
+    for a, b in zip(outs["0"], outs["1"]):
+        assert torch.equal(a, b)
+    assert torch.equal(outs["1"][0], outs["1"][2])
+
+
+def test_gather_index_is_the_inverse_of_scatter_index(vb):
+    from vexact_b200.fused_moe import _permute
+
+    g = torch.Generator().manual_seed(5)
+    T, k, E = 333, 6, 64
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).cuda()
+    rw = torch.rand(T, k, generator=g).bfloat16().cuda()
+    plan = _permute(sel, rw, None, E, gather=True)
+    scatter = plan["scatter_index"].long()
+    n = T * k
+    assert torch.equal(scatter.sort().values, torch.arange(n, device="cuda"))
+    want = torch.empty(n, dtype=torch.int32, device="cuda")
+    want[scatter] = (torch.arange(n, device="cuda") // k).int()
+    assert torch.equal(plan["gather_index"], want)
+    scale = torch.empty(n, dtype=BF, device="cuda")
+    scale[scatter] = rw.flatten()
+    assert torch.equal(plan["row_scale"], scale)
+    # within an expert the rows keep token order (stable sort), as the reference's argsort(stable=True) gives
+    cu = plan["cu_seqlens"].tolist()
+    gi = plan["gather_index"].tolist()
+    assert all(gi[a:b] == sorted(gi[a:b]) for a, b in zip(cu[:-1], cu[1:]))
+
+
 @pytest.mark.gpu
 def test_routing_of_nan_rows_stays_in_range():
     """Padded tokens of a captured batch carry undefined (possibly NaN) hidden states; their routing must

@@ -42,7 +42,7 @@ def _same(a, b):
         x, y = getattr(a, name), getattr(b, name)
         assert (x is None) == (y is None), name
         if x is not None:
-            assert torch.equal(x.reshape(-1), y.reshape(-1)), name
+            assert torch.equal(x.reshape(-1).cpu(), y.reshape(-1).cpu()), name
     assert a.max_seqlen_q == b.max_seqlen_q
     assert a.tokens_generated == b.tokens_generated          # a list of ints, or None: the optional field survives
     assert len(a.generation_configs) == len(b.generation_configs)
@@ -51,7 +51,7 @@ def _same(a, b):
             assert getattr(x, f) == getattr(y, f), f
 
 
-def _worker(rank, world, port, fail_q):
+def _worker(rank, world, port, fail_q, use_cuda=False):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -59,8 +59,12 @@ def _worker(rank, world, port, fail_q):
         from vexact_b200.pp_messager import InferencerOutput, PPMessager
 
         H = 64
+        device = torch.device("cuda", rank) if use_cuda else torch.device("cpu")
+        if use_cuda:          # payloads over NCCL P2P; NVLS off: a test rank may exit while peers still hold buffers
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+            torch.cuda.set_device(device)
         # the reference's constructor: (pp_info, parallel_config, device)
-        m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), torch.device("cpu"))
+        m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), device)
         for step, (T, S, W) in enumerate([(8, 4, 5), (64, 8, 3), (2, 1, 1)]):
             req = step != 2          # the last step carries neither sampling configs nor tokens_generated
             # ring: rank r sends to r + 1; rank 0 sends token ids, the others hidden states
@@ -79,10 +83,11 @@ def _worker(rank, world, port, fail_q):
                 m.send_infer_out(out)
             if rank == 0:
                 got = m.recv_infer_out()
-                assert torch.equal(got.token_ids, out.token_ids) and torch.equal(got.logprobs, out.logprobs)
+                assert got.token_ids.device.type == device.type
+                assert torch.equal(got.token_ids.cpu(), out.token_ids) and torch.equal(got.logprobs.cpu(), out.logprobs)
                 assert got.logits.numel() == out.logits.numel()
                 if out.logits.numel():
-                    assert torch.equal(got.logits, out.logits)
+                    assert torch.equal(got.logits.cpu(), out.logits)
 
         # two contexts in flight: the first one received must survive the second receive (two slots)
         if rank == 0:
@@ -105,10 +110,10 @@ def _worker(rank, world, port, fail_q):
             m.send_gen_ctx(base, slot=7, block_delta=(rows[:0], cols[:0], vals[:0]))
         elif rank == 1:
             want = base.block_tables.clone()
-            assert torch.equal(m.recv_gen_ctx().block_tables, want)
+            assert torch.equal(m.recv_gen_ctx().block_tables.cpu(), want)
             want[1, 2], want[3, 5] = 41, 42
-            assert torch.equal(m.recv_gen_ctx().block_tables, want)
-            assert torch.equal(m.recv_gen_ctx().block_tables, want)
+            assert torch.equal(m.recv_gen_ctx().block_tables.cpu(), want)
+            assert torch.equal(m.recv_gen_ctx().block_tables.cpu(), want)
         m.flush()
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
@@ -119,12 +124,11 @@ def _worker(rank, world, port, fail_q):
         raise
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_ring_handoff_gloo(world):
+def _run_ring(world, use_cuda):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, use_cuda)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -138,6 +142,20 @@ def test_ring_handoff_gloo(world):
             errs.append("a rank did not finish in time")
     assert not errs, "\n".join(errs)
     assert all(p.exitcode == 0 for p in procs)
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_ring_handoff_gloo(world):
+    _run_ring(world, use_cuda=False)
+
+
+@pytest.mark.gpu
+def test_ring_handoff_nccl_two_gpus():
+    """The same exchange with device tensors: headers on gloo, payloads on the pair's NCCL group
+    (reference: tests/test_pp_messager.py:68-157).  Needs two GPUs; skipped on a one-GPU box."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run_ring(2, use_cuda=True)
 
 
 def test_layer_split_matches_oracle():

@@ -46,6 +46,8 @@ SIGNATURES = {
     "b200_moe_route_sigmoid_group_topk": [P, LL, P, P, P, P, LL, I, I, I, I, I, F, P],
     "b200_moe_permute": [P, I, P, P, LL, P, P, P, P, P, P, LL, I, I, I, I, I, P],
     "b200_moe_grouped_gemm": [P, P, P, P, P, P, LL, I, I, I, LL, I, I, I, P],
+    "b200_moe_permute_index": [P, I, P, P, P, P, P, P, P, LL, I, I, I, I, P],
+    "b200_moe_grouped_gemm_gather": [P, LL, LL, P, P, P, P, P, P, I, I, I, LL, I, I, I, P],
     "b200_moe_grouped_gemm_noalloc": [P, P, P, P, P, LL, I, I, I, LL, I, P],
     "b200_swiglu_scale": [P, P, P, P, LL, I, P],
     "b200_swiglu_scale_strided": [P, P, P, P, LL, I, LL, P],

@@ -56,6 +56,11 @@ struct GemmParams {
   int rows_per_tile;
   int dense_t_tiles;
   const int4* tile_table;
+  // Grouped GEMM over rows that were never permuted: row r of a tile is x[gather_idx[row0 + r]] (null: x is
+  // already in tile order).  The activation tensor map then has a one-row box and the producer warp fetches
+  // four rows per TMA gather.
+  const int* gather_idx;
+  int scalar_epilogue;  // development knob B200_GEMM_EPI_SCALAR=1: 2-byte stores in the plain epilogue
   const int* tile_count;
   int xbox;       // rows per activation TMA box (multiple of 16)
   int xrows_max;  // largest token count of any tile (multiple of xbox, <= 256)
@@ -86,6 +91,20 @@ __device__ __forceinline__ float gemm_ex2(float x) {
   return y;
 }
 
+// Development aid (off unless the library is compiled with -DB200_GEMM_TRACE): every CTA writes %globaltimer
+// stamps of its milestones; b200_debug_gemm_trace copies them out.
+#ifdef B200_GEMM_TRACE
+__device__ unsigned long long g_gemm_trace[256][8];
+#define GEMM_STAMP(ev)                                                              \
+  do {                                                                              \
+    if (blockIdx.x < 256) g_gemm_trace[blockIdx.x][ev] = global_timer_ns();         \
+  } while (0)
+#else
+#define GEMM_STAMP(ev) \
+  do {                 \
+  } while (0)
+#endif
+
 struct GemmTile {
   int group, row0, n, wt;
 };
@@ -114,6 +133,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   constexpr bool SWIGLU = MODE == GEMM_SWIGLU;
   constexpr bool HEAD = MODE == GEMM_HEAD;
   extern __shared__ uint8_t smem_raw[];
+  if (threadIdx.x == 0) GEMM_STAMP(0);   // CTA started
   // Control block, then 1024-byte aligned stages (the 128-byte swizzle repeats every 1024 B).
   // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty
   const int S = p.stages;
@@ -158,11 +178,63 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
   pdl_wait();  // everything above is set-up; inputs written by the previous kernel are read below
+  if (threadIdx.x == 0) GEMM_STAMP(1);   // set-up done
 
   const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
   const int num_kb = (p.k + GEMM_BK * KA - 1) / (GEMM_BK * KA);  // K beyond the tensor reads as zero
 
-  if (warp == 0) {
+  if (warp == 0 && p.gather_idx) {
+    // ------------------------------------------------------------ TMA producer, gathered activation rows
+    // The whole warp runs the loop: lane 0 arms the barrier and loads the weights, lane l fetches rows
+    // 4l .. 4l+3 of the tile by index.  Rows past the tile's end repeat its first row (their columns are
+    // never stored); rows past the last group of four keep whatever the stage held.
+    const int lane = threadIdx.x & 31;
+    uint32_t ph = 0;
+    int s = 0;
+    bool ok = true;
+    for (long long lin = blockIdx.x; ok; lin += gridDim.x) {
+      GemmTile t;
+      if (!gemm_tile(p, t_tiles, lin, t)) break;
+      const int ngrp = (t.n + 3) >> 2;
+      int ri[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = 4 * lane + j;
+        int v = lane < ngrp ? p.gather_idx[t.row0 + (r < t.n ? r : 0)] : 0;
+        if (v < 0 || v >= p.t_rows) {
+          report_status(B200_STATUS_BAD_INDEX, v);
+          v = 0;
+        }
+        ri[j] = v;
+      }
+      const uint32_t tx = GEMM_WBYTES + (uint32_t)ngrp * 4 * (GEMM_BK * 2);
+      const int wrow = t.group * p.w_rows_per_group + t.wt * (SWIGLU ? 64 : GEMM_WTILE);
+      for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
+        if (!ptx::mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, 100 + s)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) ptx::mbar_expect_tx(full_bar(s), tx * KA);
+        __syncwarp();   // the barrier is armed before any lane's copy can complete on it
+        for (int a = 0; a < KA; ++a) {
+          const uint32_t sw = stage_base + (uint32_t)s * stage_bytes + (uint32_t)a * atom_bytes;
+          const uint32_t sx = sw + GEMM_WBYTES;
+          const int kcol = (kb * KA + a) * GEMM_BK;
+          if (lane == 0) {
+            if (SWIGLU) {
+              ptx::tma_load_2d(sw, &tm_w, full_bar(s), kcol, wrow, p.w_policy);
+              ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kcol, wrow + p.up_offset, p.w_policy);
+            } else {
+              ptx::tma_load_2d(sw, &tm_w, full_bar(s), kcol, wrow, p.w_policy);
+            }
+          }
+          if (lane < ngrp)
+            ptx::tma_gather4_2d(sx + (uint32_t)lane * 4 * (GEMM_BK * 2), &tm_x, full_bar(s), kcol, ri[0], ri[1],
+                                ri[2], ri[3], ptx::kEvictLast);
+        }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (ptx::elect_one()) {
       uint32_t it = 0;   // running stage counter across tiles
@@ -220,6 +292,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             break;
           }
           ptx::tc_fence_after();
+          if (it == 0) GEMM_STAMP(2);    // first stage landed
           for (int a = 0; a < KA; ++a) {
             const uint32_t sw = stage_base + (uint32_t)s * stage_bytes + (uint32_t)a * atom_bytes;
             // descriptors differ only in the start-address field: +2 (32 bytes) per 16-element K step
@@ -232,6 +305,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           ptx::umma_commit(empty_bar(s));  // stage is free once these MMAs have read it
         }
         if (ok) ptx::umma_commit(tfull_bar(buf));
+        GEMM_STAMP(3);                   // last MMA of the tile issued
       }
     }
   } else {
@@ -253,6 +327,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         break;
       }
       ptx::tc_fence_after();
+      if (threadIdx.x == 64) GEMM_STAMP(4);   // accumulator complete
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * p.xrows_max);
       const int ncol = ((t.n + 15) / 16) * 16;
       if (HEAD) {
@@ -338,6 +413,32 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int f = t.wt * GEMM_WTILE + q * 32 + lane;
         const bool fvalid = f < p.n_w;
         const float bias = (p.bias && fvalid) ? bf2f(p.bias[f]) : 0.f;
+        // bf16 output whose rows allow 16-byte stores: each warp turns its 32 features x 16 tokens around in
+        // shared memory, so that a lane stores eight consecutive features of one token (16 bytes) and one
+        // instruction covers eight token rows, instead of one 2-byte store per (feature, token).
+        const bool vec_out = !p.scalar_epilogue && !p.out_f32 && (p.ldo & 7) == 0 && (p.n_w & 7) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        if (vec_out) {
+          __nv_bfloat16* stg = exch + q * (16 * 32);      // [16 tokens][32 features] per warp
+          const int part = lane & 3, rsub = lane >> 2;
+          const int f8 = t.wt * GEMM_WTILE + q * 32 + part * 8;
+          for (int c0 = 0; c0 < ncol; c0 += 16) {
+            uint32_t r[16];
+            ptx::tmem_ld16(taddr + c0, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = f2bf(__uint_as_float(r[j]) + bias);
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int row = h * 8 + rsub, c = c0 + row;
+              const uint4 v = *reinterpret_cast<const uint4*>(stg + row * 32 + part * 8);
+              if (c < t.n && f8 < p.n_w)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + (long long)(t.row0 + c) * p.ldo + f8) = v;
+            }
+            __syncwarp();
+          }
+        } else
         for (int c0 = 0; c0 < ncol; c0 += 16) {
           uint32_t r[16];
           ptx::tmem_ld16(taddr + c0, r);
@@ -399,6 +500,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       }
       ptx::tc_fence_before();
       ptx::mbar_arrive(tempty_bar(buf));
+      if (threadIdx.x == 64) GEMM_STAMP(5);   // tile stored
     }
   }
 
@@ -454,7 +556,7 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   const int atom_bytes = GEMM_WBYTES + p.xrows_max * GEMM_BK * 2;
   // epilogue scratch after the stages: the SwiGLU exchange buffer, or the head mode's per-warp partials
   const int exch_bytes_pre = SWIGLU ? 64 * (p.xrows_max + GEMM_EXCH_PAD) * 2
-                                    : (MODE == GEMM_HEAD ? 3 * 4 * p.xrows_max * 4 : 0);
+                                    : (MODE == GEMM_HEAD ? 3 * 4 * p.xrows_max * 4 : 4 * 16 * 32 * 2);
   // K atoms per stage: fewer, larger stages cut the per-stage barrier round trips; keep >= 3 stages.
   static const int ka_env = env_int("B200_GEMM_KATOMS", 2);
   int ka = (ka_env == 1 || ka_env == 2 || ka_env == 4) ? ka_env : 2;
@@ -462,6 +564,8 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
                     (p.k + GEMM_BK - 1) / GEMM_BK < ka))
     ka >>= 1;
   p.katoms = ka;
+  static const int epi_scalar = env_int("B200_GEMM_EPI_SCALAR", 0);
+  p.scalar_epilogue = epi_scalar;
   const int stage_bytes = atom_bytes * ka;
   const int exch_bytes = exch_bytes_pre;
   int stages = (GEMM_SMEM_BUDGET - 256 - 1024 - exch_bytes) / stage_bytes;
@@ -698,15 +802,18 @@ extern "C" int b200_lm_head_greedy(const void* x, const void* w, void* partials,
 //   mode 0: out[r, n] = x[r, :] . w[g(r), n, :]                      (w: [G, N, K])
 //   mode 1: out[r, i] = silu(x . w[g, i, :]) * (x . w[g, I + i, :]) * row_scale[r]   (w: [G, 2I, K], n_out = I)
 // tile_table / tile_count come from b200_moe_permute: every tile lies inside one group.
-extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, void* out,
-                                     const void* tile_table, const void* tile_count, long long x_rows,
-                                     int num_groups, int n_out, int K, long long out_row_stride,
-                                     int max_tiles, int tile_rows_max, int mode, void* stream) {
-  using namespace b200;
+namespace b200 {
+// gather_index == nullptr: x holds the expert-sorted rows ([x_rows, K], contiguous).  Otherwise x is the
+// unpermuted [x_rows, K] matrix with rows x_row_stride apart and sorted row r is x[gather_index[r]].
+inline int moe_grouped_gemm_impl(const void* x, long long x_rows, long long x_row_stride, const void* gather_index,
+                                 const void* w, const void* row_scale, void* out, const void* tile_table,
+                                 const void* tile_count, int num_groups, int n_out, int K, long long out_row_stride,
+                                 int max_tiles, int tile_rows_max, int mode, void* stream) {
   if (!x || !w || !out || !tile_table || !tile_count || x_rows < 0 || num_groups <= 0 || n_out <= 0 || K <= 0 ||
       max_tiles < 0 || (mode != 0 && mode != 1))
     return B200_ERR_ARG;
   if (K % 8 != 0 || tile_rows_max % 16 != 0 || tile_rows_max <= 0 || tile_rows_max > 256) return B200_ERR_SHAPE;
+  if (gather_index && (tile_rows_max > 128 || x_row_stride % 8 != 0 || x_rows > 0x7fffffffLL)) return B200_ERR_SHAPE;
   if (x_rows == 0 || max_tiles == 0) return B200_OK;
   GemmParams p{};
   p.n_w = n_out;
@@ -719,6 +826,7 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* r
   p.dense_t_tiles = 0;
   p.tile_table = (const int4*)tile_table;
   p.tile_count = (const int*)tile_count;
+  p.gather_idx = (const int*)gather_index;
   // One activation box per stage when the tile height allows it (fewer TMA issues per stage).
   static const int xbox_env = env_int("B200_GEMM_XBOX", 64);
   p.xbox = (xbox_env == 16 || xbox_env == 32 || xbox_env == 64) && tile_rows_max % xbox_env == 0 ? xbox_env : 16;
@@ -733,9 +841,44 @@ extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* r
   int rc = make_tmap_2d(&tw, w, (uint64_t)num_groups * p.w_rows_per_group, (uint64_t)K, (uint64_t)K,
                         mode == 1 ? 64 : GEMM_WTILE);
   if (rc) return rc;
-  rc = make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, (uint32_t)p.xbox);
+  rc = gather_index ? make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)x_row_stride, 1u)
+                    : make_tmap_2d(&tx, x, (uint64_t)x_rows, (uint64_t)K, (uint64_t)K, (uint32_t)p.xbox);
   if (rc) return rc;
   const long long tiles = (long long)max_tiles * p.w_tiles;
   if (mode == 1) return gemm_launch<GEMM_SWIGLU>(tw, tx, p, tiles, (cudaStream_t)stream);
   return gemm_launch<GEMM_PLAIN>(tw, tx, p, tiles, (cudaStream_t)stream);
 }
+}  // namespace b200
+
+extern "C" int b200_moe_grouped_gemm(const void* x, const void* w, const void* row_scale, void* out,
+                                     const void* tile_table, const void* tile_count, long long x_rows,
+                                     int num_groups, int n_out, int K, long long out_row_stride,
+                                     int max_tiles, int tile_rows_max, int mode, void* stream) {
+  return b200::moe_grouped_gemm_impl(x, x_rows, K, nullptr, w, row_scale, out, tile_table, tile_count, num_groups,
+                                     n_out, K, out_row_stride, max_tiles, tile_rows_max, mode, stream);
+}
+
+// The same GEMM reading its activation rows where they lie: x is the unpermuted [T, K] matrix and sorted row r
+// of the tile table is x[gather_index[r]] (quack's `A_idx`, fused_moe.py:319-322).  No permuted copy of the
+// activations is made; the result is the same bits as b200_moe_grouped_gemm on the permuted copy.
+// gather_index [sorted rows] i32 comes from b200_moe_permute_index.  tile_rows_max <= 128.
+extern "C" int b200_moe_grouped_gemm_gather(const void* x, long long T, long long x_row_stride,
+                                            const void* gather_index, const void* w, const void* row_scale,
+                                            void* out, const void* tile_table, const void* tile_count,
+                                            int num_groups, int n_out, int K, long long out_row_stride,
+                                            int max_tiles, int tile_rows_max, int mode, void* stream) {
+  if (!gather_index) return B200_ERR_ARG;
+  return b200::moe_grouped_gemm_impl(x, T, x_row_stride, gather_index, w, row_scale, out, tile_table, tile_count,
+                                     num_groups, n_out, K, out_row_stride, max_tiles, tile_rows_max, mode, stream);
+}
+
+#ifdef B200_GEMM_TRACE
+extern "C" int b200_debug_gemm_trace(long long* host_out /* [256][8] */) {
+  cudaDeviceSynchronize();
+  const size_t bytes = sizeof(unsigned long long) * 256 * 8;
+  if (cudaMemcpyFromSymbol(host_out, b200::g_gemm_trace, bytes) != cudaSuccess) return -1;
+  void* dev = nullptr;
+  if (cudaGetSymbolAddress(&dev, b200::g_gemm_trace) != cudaSuccess) return -1;
+  return cudaMemset(dev, 0, bytes) == cudaSuccess ? 0 : -1;   // the next launch starts from a clean slate
+}
+#endif

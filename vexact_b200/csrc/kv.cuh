@@ -67,6 +67,21 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
   // (cos, sin) pairs are computed once into shared memory instead of once per head.
   __shared__ float s_cos[64], s_sin[64];
   const bool one_token = heads_total % 8 == 0;
+  // This warp's head: its 8-byte slice per lane and (for K / V) the cache slot are requested first, so that
+  // the loads are in flight while the CTA computes the token's cos / sin table.
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const bool valid = wid < num_tokens * heads_total;
+  const int lane = threadIdx.x & 31;
+  const long long tok = valid ? wid / heads_total : 0;
+  const int head = valid ? (int)(wid % heads_total) : 0;
+  const bool is_q = head < num_q_heads;
+  const bool is_k = !is_q && head < num_q_heads + num_kv_heads;
+  uint2 raw = make_uint2(0u, 0u);
+  long long slot = -1;
+  if (valid) {
+    raw = *reinterpret_cast<const uint2*>(qkv + tok * qkv_stride + (long long)head * D + lane * 4);
+    if (!is_q) slot = slot_mapping[tok];
+  }
   if (one_token) {
     const long long tok0 = (long long)blockIdx.x * 8 / heads_total;
     if (threadIdx.x < 64 && tok0 < num_tokens) {
@@ -76,19 +91,8 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
     }
     __syncthreads();
   }
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (wid >= num_tokens * heads_total) return;
-  const int lane = threadIdx.x & 31;
-  const long long tok = wid / heads_total;
-  const int head = (int)(wid % heads_total);
-  const __nv_bfloat16* src = qkv + tok * qkv_stride + (long long)head * D + lane * 4;
-  const uint2 raw = *reinterpret_cast<const uint2*>(src);
-
-  const bool is_q = head < num_q_heads;
-  const bool is_k = !is_q && head < num_q_heads + num_kv_heads;
-  long long slot = -1;
+  if (!valid) return;
   if (!is_q) {
-    slot = slot_mapping[tok];
     if (slot < 0) return;  // padded token: nothing to cache
     if (slot >= num_slots) {
       if (lane == 0) report_status(B200_STATUS_BAD_INDEX, (int)slot);

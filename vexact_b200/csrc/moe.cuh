@@ -247,7 +247,8 @@ template <typename TIdx>
 __global__ void __launch_bounds__(1024)
 moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_rows,
                  int* __restrict__ scatter_index, int* __restrict__ cu_seqlens, int4* __restrict__ tile_table,
-                 int* __restrict__ tile_count, int max_tiles) {
+                 int* __restrict__ tile_count, int max_tiles, int topk, int* __restrict__ gather_index,
+                 const __nv_bfloat16* __restrict__ weights, __nv_bfloat16* __restrict__ row_scale) {
   pdl_trigger();
   pdl_wait();
   __shared__ int cnt[32][MOE_MAX_EXPERTS];  // per-warp counts, then per-warp exclusive offsets
@@ -342,7 +343,14 @@ moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_
     const long long i = w0 + o + lane;
     if (i < n) {
       const long long ev = (long long)experts[i];
-      if (ev >= 0 && ev < E) scatter_index[i] += base[(int)ev] + cnt[warp][(int)ev];
+      if (ev >= 0 && ev < E) {
+        const int pos = scatter_index[i] + base[(int)ev] + cnt[warp][(int)ev];
+        scatter_index[i] = pos;
+        // the inverse map for a GEMM that gathers its rows (sorted row -> token), and the routing weight
+        // of each sorted row, so that no permuted copy of the activations has to be made
+        if (gather_index) gather_index[pos] = (int)(i / topk);
+        if (row_scale) row_scale[pos] = weights[i];
+      }
     }
   }
 }
@@ -363,6 +371,51 @@ moe_scatter_rows_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
   for (int i = threadIdx.x; i < (H >> 3); i += 128)
     reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
   if (threadIdx.x == 0 && row_scale && weights) row_scale[pos] = weights[f];
+}
+
+// Sum of a token's top-k expert rows (16-byte vector v of each) in k order, fp32.  For topk <= 8 the k row
+// positions are read first and the k row loads are issued together, so the chain is two memory latencies
+// instead of 2k; the additions run in k order either way (same bits).
+__device__ __forceinline__ void moe_topk_row_sum(const __nv_bfloat16* __restrict__ y,
+                                                 const int* __restrict__ scatter_index, long long t, int topk,
+                                                 int H, int v, float (&acc)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (topk <= 8) {
+    int pos[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) pos[k] = k < topk ? scatter_index[t * topk + k] : -1;
+    uint4 r[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      r[k] = pos[k] >= 0 ? reinterpret_cast<const uint4*>(y + (long long)pos[k] * H)[v] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (pos[k] < 0) continue;
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r[k]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a, b;
+        unpack_bf2(rp[j], a, b);
+        acc[2 * j] += a;
+        acc[2 * j + 1] += b;
+      }
+    }
+    return;
+  }
+  for (int k = 0; k < topk; ++k) {
+    const int pos = scatter_index[t * topk + k];
+    if (pos < 0) continue;
+    const uint4 r = reinterpret_cast<const uint4*>(y + (long long)pos * H)[v];
+    const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a, b;
+      unpack_bf2(rp[j], a, b);
+      acc[2 * j] += a;
+      acc[2 * j + 1] += b;
+    }
+  }
 }
 
 // The top-k sum below followed, in the same launch, by the residual add and the RMSNorm that the next
@@ -387,21 +440,7 @@ moe_unpermute_add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const int*
     const int v = threadIdx.x + i * THREADS;
     if (v < nvec) {
       float acc[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int k = 0; k < topk; ++k) {
-        const int pos = scatter_index[t * topk + k];
-        if (pos < 0) continue;
-        const uint4 r = reinterpret_cast<const uint4*>(y + (long long)pos * H)[v];
-        const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float a, b;
-          unpack_bf2(rp[j], a, b);
-          acc[2 * j] += a;
-          acc[2 * j + 1] += b;
-        }
-      }
+      moe_topk_row_sum(y, scatter_index, t, topk, H, v, acc);
       if (addend) {
         const uint4 r = reinterpret_cast<const uint4*>(addend + t * H)[v];
         const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
@@ -470,21 +509,7 @@ moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __re
   const long long t = blockIdx.x;
   for (int v = threadIdx.x; v < (H >> 3); v += 256) {
     float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int k = 0; k < topk; ++k) {
-      const int pos = scatter_index[t * topk + k];
-      if (pos < 0) continue;
-      const uint4 r = reinterpret_cast<const uint4*>(y + (long long)pos * H)[v];
-      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float a, b;
-        unpack_bf2(rp[j], a, b);
-        acc[2 * j] += a;
-        acc[2 * j + 1] += b;
-      }
-    }
+    moe_topk_row_sum(y, scatter_index, t, topk, H, v, acc);
     if (addend) {
       const uint4 r = reinterpret_cast<const uint4*>(addend + t * H)[v];
       const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
@@ -586,11 +611,12 @@ extern "C" int b200_moe_permute(const void* experts, int experts_dtype /*0 = i32
   const long long n = T * topk;
   if (experts_dtype == 0)
     launch_k(moe_index_kernel<int>, dim3(1), dim3(1024), 0, st, (const int*)experts, n, E, tile_rows, (int*)scatter_index,
-                                              (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles);
+             (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles, 1, (int*)nullptr,
+             (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)nullptr);
   else if (experts_dtype == 1)
     launch_k(moe_index_kernel<long long>, dim3(1), dim3(1024), 0, st, (const long long*)experts, n, E, tile_rows,
-                                                    (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table,
-                                                    (int*)tile_count, max_tiles);
+             (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles, 1,
+             (int*)nullptr, (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)nullptr);
   else
     return B200_ERR_ARG;
   int rc = launch_status();
@@ -599,6 +625,33 @@ extern "C" int b200_moe_permute(const void* experts, int experts_dtype /*0 = i32
                                                        (const __nv_bfloat16*)weights_bf16,
                                                        (const int*)scatter_index, (__nv_bfloat16*)x_perm,
                                                        (__nv_bfloat16*)row_scale, H, topk);
+  return launch_status();
+}
+
+// b200_moe_permute without the permuted copy: the index arrays, plus gather_index [T * topk] i32 (sorted row
+// -> token, the reference's `A_idx = order // topk`, fused_moe.py:285) and row_scale (routing weight per sorted
+// row) for b200_moe_grouped_gemm_gather.  One launch.
+extern "C" int b200_moe_permute_index(const void* experts, int experts_dtype /*0 = i32, 1 = i64*/,
+                                      const void* weights_bf16, void* scatter_index, void* cu_seqlens,
+                                      void* gather_index, void* row_scale, void* tile_table, void* tile_count,
+                                      long long T, int topk, int E, int tile_rows, int max_tiles, void* stream) {
+  using namespace b200;
+  if (!experts || !scatter_index || !cu_seqlens || !gather_index || !tile_table || !tile_count || T < 0 ||
+      topk <= 0 || E <= 0 || tile_rows <= 0 || max_tiles <= 0 || (row_scale && !weights_bf16))
+    return B200_ERR_ARG;
+  if (E > MOE_MAX_EXPERTS) return B200_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long n = T * topk;
+  if (experts_dtype == 0)
+    launch_k(moe_index_kernel<int>, dim3(1), dim3(1024), 0, st, (const int*)experts, n, E, tile_rows,
+             (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles, topk,
+             (int*)gather_index, (const __nv_bfloat16*)weights_bf16, (__nv_bfloat16*)row_scale);
+  else if (experts_dtype == 1)
+    launch_k(moe_index_kernel<long long>, dim3(1), dim3(1024), 0, st, (const long long*)experts, n, E, tile_rows,
+             (int*)scatter_index, (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, max_tiles, topk,
+             (int*)gather_index, (const __nv_bfloat16*)weights_bf16, (__nv_bfloat16*)row_scale);
+  else
+    return B200_ERR_ARG;
   return launch_status();
 }
 

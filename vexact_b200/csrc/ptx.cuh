@@ -132,6 +132,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, uint
       : "memory");
 }
 
+// Four rows of a 2-D tensor, picked by index, into four consecutive (swizzled) rows of shared memory:
+// the tensor map's box is {columns, 1 row}; x is the column coordinate (16-byte aligned like any TMA x),
+// r0..r3 the row coordinates.  Completes 4 x box bytes on the barrier.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const void* tmap, uint32_t bar, int x, int r0, int r1,
+                                               int r2, int r3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6, %7}], [%2], %8;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3),
+      "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, uint32_t bar, int c0, int c1,
                                             int c2, int c3, uint64_t policy) {
   asm volatile(

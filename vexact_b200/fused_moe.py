@@ -14,6 +14,7 @@ Pipeline (all on the caller's stream, scratch from torch's caching allocator):
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -81,16 +82,22 @@ def route_sigmoid_group_topk(router_logits: torch.Tensor, e_score_correction_bia
 def build_moe_indices(expert_index: torch.Tensor, num_experts: int):
     """(cu_seqlens_m [E+1], A_idx [T*k], scatter_index [T, k]) as fused_moe.py:268 returns them."""
     T, k = expert_index.shape
-    plan = _permute(expert_index, None, None, num_experts)
-    scatter = plan["scatter_index"].view(T, k)
-    n = T * k
-    a_idx = torch.empty(n, device=expert_index.device, dtype=torch.int32)
-    a_idx[scatter.flatten().long()] = torch.arange(n, device=expert_index.device, dtype=torch.int32) // k
-    return plan["cu_seqlens"], a_idx, scatter
+    plan = _permute(expert_index, None, None, num_experts, gather=True)
+    return plan["cu_seqlens"], plan["gather_index"], plan["scatter_index"].view(T, k)
+
+
+def _gather_default() -> bool:
+    """B200_MOE_GATHER=1: fc1 reads its activation rows through the gather index and no permuted copy of the
+    activations is made (16 MB less scratch at 512 tokens x top-8 x 2048).  Off by default: one TMA gather moves
+    four rows, so a 64-row stage takes 32 TMA instructions instead of 2, and the decode-shaped fc1 measured
+    209 us against 126 us over the permuted copy plus 7 us for making it."""
+    return os.environ.get("B200_MOE_GATHER", "0") == "1"
 
 
 def _permute(expert_index: torch.Tensor, routing_weights: Optional[torch.Tensor],
-             hidden_states: Optional[torch.Tensor], num_experts: int):
+             hidden_states: Optional[torch.Tensor], num_experts: int, gather: bool = False):
+    """Index arrays + token-tile table of one routing.  gather=False also writes the expert-sorted copy of the
+    activations (`x_perm`); gather=True writes `gather_index` (sorted row -> token) instead, in one launch."""
     dev = expert_index.device
     T, k = expert_index.shape
     n = T * k
@@ -103,6 +110,21 @@ def _permute(expert_index: torch.Tensor, routing_weights: Optional[torch.Tensor]
     tile_table = torch.empty((max_tiles, 4), device=dev, dtype=torch.int32)
     tile_count = torch.empty(1, device=dev, dtype=torch.int32)
     x_perm = row_scale = None
+    if gather:
+        gather_index = torch.empty(n, device=dev, dtype=torch.int32)
+        if routing_weights is not None:
+            row_scale = torch.empty(n, device=dev, dtype=torch.bfloat16)
+        _lib.check(
+            _lib.load().b200_moe_permute_index(
+                expert_index.data_ptr(), 0 if expert_index.dtype == torch.int32 else 1, _lib.ptr(routing_weights),
+                scatter_index.data_ptr(), cu_seqlens.data_ptr(), gather_index.data_ptr(), _lib.ptr(row_scale),
+                tile_table.data_ptr(), tile_count.data_ptr(), T, k, num_experts, TILE_ROWS, max_tiles,
+                _lib.current_stream()),
+            "b200_moe_permute_index",
+        )
+        return dict(scatter_index=scatter_index, cu_seqlens=cu_seqlens, tile_table=tile_table, tile_count=tile_count,
+                    x_perm=None, x=hidden_states, gather_index=gather_index, row_scale=row_scale,
+                    max_tiles=max_tiles)
     H = 8
     x_stride = 8
     if hidden_states is not None:
@@ -121,6 +143,22 @@ def _permute(expert_index: torch.Tensor, routing_weights: Optional[torch.Tensor]
     )
     return dict(scatter_index=scatter_index, cu_seqlens=cu_seqlens, tile_table=tile_table,
                 tile_count=tile_count, x_perm=x_perm, row_scale=row_scale, max_tiles=max_tiles)
+
+
+def _grouped_gemm_fc1(w, row_scale, plan, n_out, mode):
+    """The first grouped GEMM of the MoE: over the permuted copy, or gathering rows of the unpermuted input."""
+    if plan.get("gather_index") is None:
+        return _grouped_gemm(plan["x_perm"], w, row_scale, plan, n_out, mode)
+    x, idx = plan["x"], plan["gather_index"]
+    out = torch.empty((idx.numel(), n_out), device=x.device, dtype=torch.bfloat16)
+    _lib.check(
+        _lib.load().b200_moe_grouped_gemm_gather(
+            x.data_ptr(), x.shape[0], x.stride(0), idx.data_ptr(), w.data_ptr(), _lib.ptr(row_scale), out.data_ptr(),
+            plan["tile_table"].data_ptr(), plan["tile_count"].data_ptr(), w.shape[0], n_out, x.shape[1],
+            out.stride(0), plan["max_tiles"], plan.get("tile_rows", TILE_ROWS), mode, _lib.current_stream()),
+        "b200_moe_grouped_gemm_gather",
+    )
+    return out
 
 
 def _grouped_gemm(x, w, row_scale, plan, n_out, mode):
@@ -207,7 +245,7 @@ def fused_moe_forward(
     T, H = x.shape
     k = selected_experts.shape[-1]
     selected_experts = selected_experts.reshape(T, k)
-    plan = _permute(selected_experts, routing_weights.reshape(T, k), x, num_experts)
+    plan = _permute(selected_experts, routing_weights.reshape(T, k), x, num_experts, gather=_gather_default())
     if fc1_1_2_weight is not None:
         assert fc1_1_2_weight.dtype == torch.bfloat16 and fc1_1_2_weight.is_contiguous()
         I = fc1_1_2_weight.shape[1] // 2
@@ -215,7 +253,7 @@ def fused_moe_forward(
             # many rows per expert (prefill): the fused SwiGLU epilogue, where two of the four epilogue
             # warps do a tile's activation math, would bound the kernel; one plain grouped GEMM over the
             # gate and up rows plus the elementwise kernel rounds at the same points (same bits)
-            gu = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, None, plan, 2 * I, mode=0)
+            gu = _grouped_gemm_fc1(fc1_1_2_weight, None, plan, 2 * I, mode=0)
             h = torch.empty((gu.shape[0], I), device=gu.device, dtype=torch.bfloat16)
             _lib.check(
                 _lib.load().b200_swiglu_scale_strided(gu.data_ptr(), gu.data_ptr() + I * gu.element_size(),
@@ -224,15 +262,15 @@ def fused_moe_forward(
                 "b200_swiglu_scale_strided",
             )
         else:
-            h = _grouped_gemm(plan["x_perm"], fc1_1_2_weight, plan["row_scale"], plan, I, mode=1)
+            h = _grouped_gemm_fc1(fc1_1_2_weight, plan["row_scale"], plan, I, mode=1)
     else:
         if fc1_1_weight is None or fc1_2_weight is None:
             raise ValueError("pass fc1_1_weight and fc1_2_weight, or fc1_1_2_weight")
         fc1_1_weight = fc1_1_weight.to(torch.bfloat16).contiguous()
         fc1_2_weight = fc1_2_weight.to(torch.bfloat16).contiguous()
         I = fc1_1_weight.shape[1]
-        g = _grouped_gemm(plan["x_perm"], fc1_1_weight, None, plan, I, mode=0)
-        u = _grouped_gemm(plan["x_perm"], fc1_2_weight, None, plan, I, mode=0)
+        g = _grouped_gemm_fc1(fc1_1_weight, None, plan, I, mode=0)
+        u = _grouped_gemm_fc1(fc1_2_weight, None, plan, I, mode=0)
         h = torch.empty_like(g)
         _lib.check(
             _lib.load().b200_swiglu_scale(g.data_ptr(), u.data_ptr(), plan["row_scale"].data_ptr(), h.data_ptr(),
