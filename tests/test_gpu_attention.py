@@ -185,6 +185,30 @@ def test_status_word_clean(vb):
     assert vb._lib.read_status()[0] == 0
 
 
+@pytest.mark.parametrize("case", ["more_queries_than_the_bucket", "fewer_keys_than_queries"])
+def test_inconsistent_lengths_are_skipped_and_reported(vb, case):
+    """A sequence whose q_len exceeds the max_seqlen_q the grid was sized for (a captured graph replayed with a
+    longer chunk), or whose key count is below its query count, is skipped and named in the status word
+    (code 2, detail = sequence); the other sequences of the batch are computed as if it were not there."""
+    hq, hkv, d, page = 8, 2, 128, 16
+    if case == "more_queries_than_the_bucket":
+        q_lens, kv_lens, max_q, bad = [1, 5, 1], [40, 70, 33], 1, 1
+    else:
+        q_lens, kv_lens, max_q, bad = [3, 4, 2], [50, 2, 20], 4, 1
+    q, kc, vc, cu, used, ptab = _build(q_lens, kv_lens, hq, hkv, d, d, page, seed=9)
+    assert vb._lib.read_status()[0] == 0
+    got = _run(vb, q, kc, vc, cu, used, ptab, d ** -0.5, max_q)
+    torch.cuda.synchronize()
+    code, detail, _, _ = vb._lib.read_status()          # reading clears the word
+    assert (code, detail) == (2, bad)
+    assert vb._lib.read_status()[0] == 0
+    for s in (0, 2):                                    # the well-formed sequences: same bits as when run alone
+        a, b = int(cu[s]), int(cu[s + 1])
+        alone = _run(vb, q[a:b], kc, vc, torch.tensor([0, b - a], dtype=torch.int32), used[s:s + 1],
+                     ptab[s:s + 1], d ** -0.5, max(q_lens[s], 1))
+        assert torch.equal(got[a:b], alone)
+
+
 def test_mma_sync_kernel_cross_check():
     """The mma.sync kernel (fallback for head dims the tcgen05 kernel does not cover) against the same
     oracle, golden and bitwise cases: the kernel choice is read once per process, so a child runs it."""

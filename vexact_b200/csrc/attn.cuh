@@ -61,6 +61,7 @@ struct AttnParams {
   int num_seqs;
   const int* seq_order;  // [num_seqs] sequence of each slot (longest first), or null
   int max_seqlen_q;      // the caller's bound on queries per sequence: it sized the tile grid
+  int scalar_out;        // development knob B200_ATTN_OUT_SCALAR=1: 2-byte output stores in the keys-on-lanes kernel
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -489,6 +490,10 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
   if (rc) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   p.max_seqlen_q = max_seqlen_q;
+  {
+    const char* v = getenv("B200_ATTN_OUT_SCALAR");
+    p.scalar_out = (v && v[0] == '1') ? 1 : 0;
+  }
   if (num_seqs > 65535 || num_kv_heads * p.head_chunks > 65535) return B200_ERR_SHAPE;
   const int hh = group < 8 ? group : 8;
   if (attn_use_tensor_memory() && dv == 128 && (dk == 128 || dk == 192) && q_tok_stride % 8 == 0 &&

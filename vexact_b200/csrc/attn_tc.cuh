@@ -682,7 +682,44 @@ paged_attn_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_cons
       }
       ptx::named_barrier_sync(3, NCT);
       if (*abort_flag) break;  // uniform over the compute threads: read after a common barrier
-      {
+      // Output.  A thread holds one value-dim element of NC / 2 columns; stored as they are that is one 2-byte
+      // store per column.  Each warp turns 8 columns x its 32 dims around in shared memory instead (its 512-byte
+      // slice of the P^T tile, which nothing reads between the tile's last PV product and the barrier that
+      // opens the next tile), so that a lane stores 16 bytes and one instruction writes all 8 columns.
+      const bool vec_out = !p.scalar_out && ((reinterpret_cast<uintptr_t>(p.out) | (uintptr_t)(p.o_tok_stride * 2) |
+                             (uintptr_t)(p.o_head_stride * 2)) & 15) == 0;
+      if (vec_out) {
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(p_ptr) + (warp - 2) * 256;
+#pragma unroll
+        for (int g8 = 0; g8 < NCL / 8; ++g8) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const int lc = g8 * 8 + k;
+            const int c = ((lc >> 2) << 3) + hsel * 4 + (lc & 3);
+            float v = 0.f;
+            if (c < ncv) {
+              const float4 l4 = *reinterpret_cast<const float4*>(s_lred[c]);
+              const float l = (l4.x + l4.y) + (l4.z + l4.w);
+              v = o_acc[lc] * (1.0f / l);
+            }
+            stg[k * 32 + lane] = f2bf(v);
+          }
+          __syncwarp();
+          {
+            const int k = lane >> 2, part = lane & 3;
+            const int lc = g8 * 8 + k;
+            const int c = ((lc >> 2) << 3) + hsel * 4 + (lc & 3);
+            if (c < ncv) {
+              const int pi = c / t.heads_here, h = c - pi * t.heads_here;
+              __nv_bfloat16* orow = p.out + (long long)(t.q_start + t.tile_pos0 + pi) * p.o_tok_stride +
+                                    (long long)(t.kvh * p.group + t.hchunk * 8 + h) * p.o_head_stride;
+              *reinterpret_cast<uint4*>(orow + q4 * 32 + part * 8) =
+                  *reinterpret_cast<const uint4*>(stg + k * 32 + part * 8);
+            }
+          }
+          __syncwarp();
+        }
+      } else {
         int pi = 0, h = 0;  // column c = position pi of the tile, head h of this KV head's chunk
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
