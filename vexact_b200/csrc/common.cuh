@@ -109,11 +109,12 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Programmatic dependent launch (B200_PDL): 0 = off, 1 = every kernel, 2 (default) = only kernels
-// without dynamic shared memory, i.e. the short row / routing / permutation kernels, which can be
-// resident beside a finishing GEMM or attention CTA and then start the moment it is done.  Every
-// kernel waits (griddepcontrol.wait) before it touches its inputs.  Measured inside the captured
-// decode step: mode 2 is worth 2.5 % on the small dense models and neutral on the 30B-A3B shape;
+// Programmatic dependent launch (B200_PDL): 0 = off, 1 = every kernel, 3 = only kernels without dynamic
+// shared memory, i.e. the short row / routing / permutation kernels, which can be resident beside a
+// finishing GEMM or attention CTA and then start the moment it is done; 2 (default) = those plus the dense
+// GEMMs, which request their first weight tiles before they wait.  Every kernel waits
+// (griddepcontrol.wait) before it touches what its predecessor wrote.  Measured inside the captured
+// decode step: mode 3 is worth 2.5 % on the small dense models and neutral on the 30B-A3B shape;
 // mode 1 costs the latter 0.4 %.
 inline int pdl_mode() {
   static const int mode = []() {
@@ -121,6 +122,22 @@ inline int pdl_mode() {
     return v ? atoi(v) : 2;
   }();
   return mode;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_k_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl,
+                         Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 template <typename... KArgs, typename... Args>
@@ -135,7 +152,7 @@ inline void launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sme
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   const int mode = pdl_mode();
-  cfg.numAttrs = (mode == 1 || (mode == 2 && smem == 0)) ? 1 : 0;
+  cfg.numAttrs = (mode == 1 || (mode >= 2 && smem == 0)) ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

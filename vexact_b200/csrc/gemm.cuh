@@ -177,11 +177,32 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_trigger();
-  pdl_wait();  // everything above is set-up; inputs written by the previous kernel are read below
   if (threadIdx.x == 0) GEMM_STAMP(1);   // set-up done
-
-  const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
   const int num_kb = (p.k + GEMM_BK * KA - 1) / (GEMM_BK * KA);  // K beyond the tensor reads as zero
+  // Everything above is set-up.  What the previous kernel wrote (activations, the tile table) is read only
+  // after pdl_wait().  The weights are not its output: with a static tiling (no tile table) the producer
+  // requests its first ring of weight tiles before it waits, so that under programmatic dependent launch
+  // their HBM latency runs alongside the predecessor's tail.
+  int prefetched = 0;
+  if (warp == 0 && !SWIGLU && !p.tile_table && !p.gather_idx) {
+    GemmTile t;
+    if (gemm_tile(p, p.dense_t_tiles, blockIdx.x, t)) {   // the same for every lane
+      prefetched = num_kb < S ? num_kb : S;
+      if (ptx::elect_one()) {
+        const int nbox = (t.n + p.xbox - 1) / p.xbox;
+        const uint32_t tx = GEMM_WBYTES + (uint32_t)nbox * p.xbox * (GEMM_BK * 2);
+        const int wrow = t.wt * GEMM_WTILE;
+        for (int kb = 0; kb < prefetched; ++kb) {
+          ptx::mbar_expect_tx(full_bar(kb), tx * KA);
+          for (int a = 0; a < KA; ++a)
+            ptx::tma_load_2d(stage_base + (uint32_t)kb * stage_bytes + (uint32_t)a * atom_bytes, &tm_w, full_bar(kb),
+                             (kb * KA + a) * GEMM_BK, wrow, p.w_policy);
+        }
+      }
+    }
+  }
+  pdl_wait();
+  const int t_tiles = p.tile_table ? *p.tile_count : p.dense_t_tiles;
 
   if (warp == 0 && p.gather_idx) {
     // ------------------------------------------------------------ TMA producer, gathered activation rows
@@ -248,16 +269,21 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const uint32_t tx = GEMM_WBYTES + (uint32_t)nbox * p.xbox * (GEMM_BK * 2);
         const int wrow = t.group * p.w_rows_per_group + t.wt * (SWIGLU ? 64 : GEMM_WTILE);
         for (int kb = 0; kb < num_kb; ++kb, ++it, s = (s + 1 == S ? 0 : s + 1), ph ^= (s == 0)) {
-          if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 100 + s)) {
-            ok = false;
-            break;
+          // the first tile's first `prefetched` stages were armed, and their weights requested, before pdl_wait
+          const bool early = it < (uint32_t)prefetched;
+          if (!early) {
+            if (!ptx::mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 100 + s)) {
+              ok = false;
+              break;
+            }
+            ptx::mbar_expect_tx(full_bar(s), tx * KA);
           }
-          ptx::mbar_expect_tx(full_bar(s), tx * KA);
           for (int a = 0; a < KA; ++a) {
             const uint32_t sw = stage_base + (uint32_t)s * stage_bytes + (uint32_t)a * atom_bytes;
             const uint32_t sx = sw + GEMM_WBYTES;
             const int kcol = (kb * KA + a) * GEMM_BK;
-            if (SWIGLU) {
+            if (early) {
+            } else if (SWIGLU) {
               ptx::tma_load_2d(sw, &tm_w, full_bar(s), kcol, wrow, p.w_policy);
               ptx::tma_load_2d(sw + 64 * GEMM_BK * 2, &tm_w, full_bar(s), kcol, wrow + p.up_offset, p.w_policy);
             } else {
@@ -583,7 +609,9 @@ inline int gemm_launch(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams&
   const size_t smem = 256 + 1024 + (size_t)stages * stage_bytes + exch_bytes;
   long long grid = max_tiles < sm_count() ? max_tiles : sm_count();
   if (grid <= 0) return B200_OK;
-  launch_k(gemm_ws_kernel<MODE>, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, st, tw, tx, p);
+  // A dense GEMM (static tiling) may start under its predecessor's tail: it prefetches weights before it waits.
+  launch_k_pdl(gemm_ws_kernel<MODE>, dim3((unsigned)grid), dim3(GEMM_THREADS), smem, st,
+               pdl_mode() == 1 || (pdl_mode() == 2 && !p.tile_table), tw, tx, p);
   return launch_status();
 }
 

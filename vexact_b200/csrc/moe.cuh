@@ -264,7 +264,11 @@ moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_
   // registers, with the expert ids requested before the first round: the second pass then reads nothing back.
   constexpr int KEEP = 8;
   const int rounds = (int)(seg / 32);
+#ifdef B200_INDEX_NO_KEEP
+  const bool keep = false;
+#else
   const bool keep = rounds <= KEEP;
+#endif
   int ke[KEEP], kr[KEEP];
   if (keep) {
 #pragma unroll
