@@ -560,6 +560,17 @@ def main():
     if pp > 1:
         dist.init_process_group("nccl", device_id=device)
     S, H = args.batch, shape.hidden
+    watchdog = float(os.environ.get("B200_BENCH_WATCHDOG", "0") or 0)
+    if watchdog > 0:      # debugging aid: every rank prints its Python stack if the run is still going by then
+        import faulthandler
+
+        faulthandler.dump_traceback_later(watchdog, exit=False, file=sys.stderr)
+
+    def phase(name):
+        if os.environ.get("B200_BENCH_TRACE"):
+            print(f"[trace rank {rank}] {name} at {time.perf_counter() - t_start:.1f} s", file=sys.stderr, flush=True)
+
+    t_start = time.perf_counter()
 
     weights = StageWeights.random_init(shape, rank, pp, device=device, seed=0)
     n_inflight = pp
@@ -647,6 +658,7 @@ def main():
             gr.replay()
         if pp > 1:
             hand_on(b, step_inputs[b], out, first=True)
+    phase("set-up round done")
     pending = [pp > 1 and rank == 0] * n_inflight   # rank 0: a token message of the batch's previous step is owed
     status = _lib.read_status()
     if status[0] != 0:
@@ -718,10 +730,12 @@ def main():
         sampler.start()
         sampler.wait_first_sample()
     sync_all()
+    phase("pipeline drained after set-up")
     for _ in range(max(args.warmup, 3) if not args.quick else args.warmup):
         global_step()
     if pp == 1:
         sync_all()
+    phase("warm-up done")
 
     # ---- device-timed run (inputs resident in HBM; weights + KV >> L2, so every step is cold).
     # With pipeline stages the warm-up steps run straight into the timed ones (no drain in between), so
@@ -733,6 +747,7 @@ def main():
         global_step()
     ev1.record()
     sync_all()
+    phase("device-timed steps done")
     dev_ms = ev0.elapsed_time(ev1)
     if trace is not None:
         tail = trace[-args.steps * n_inflight:]

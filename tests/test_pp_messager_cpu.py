@@ -51,7 +51,7 @@ def _same(a, b):
             assert getattr(x, f) == getattr(y, f), f
 
 
-def _worker(rank, world, port, fail_q, use_cuda=False):
+def _worker(rank, world, port, fail_q, use_cuda=False, shared_cpu=None):
     try:
         os.environ["MASTER_ADDR"] = "127.0.0.1"
         os.environ["MASTER_PORT"] = str(port)
@@ -64,7 +64,8 @@ def _worker(rank, world, port, fail_q, use_cuda=False):
             os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             torch.cuda.set_device(device)
         # the reference's constructor: (pp_info, parallel_config, device)
-        m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), device)
+        m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), device,
+                       shared_cpu_group=shared_cpu)
         for step, (T, S, W) in enumerate([(8, 4, 5), (64, 8, 3), (2, 1, 1)]):
             req = step != 2          # the last step carries neither sampling configs nor tokens_generated
             # ring: rank r sends to r + 1; rank 0 sends token ids, the others hidden states
@@ -124,11 +125,11 @@ def _worker(rank, world, port, fail_q, use_cuda=False):
         raise
 
 
-def _run_ring(world, use_cuda):
+def _run_ring(world, use_cuda, shared_cpu=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q, use_cuda)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, use_cuda, shared_cpu)) for r in range(world)]
     for p in procs:
         p.start()
     for p in procs:
@@ -149,6 +150,13 @@ def test_ring_handoff_gloo(world):
     _run_ring(world, use_cuda=False)
 
 
+def test_ring_handoff_with_one_header_group_for_all_ranks():
+    """Headers over a single gloo group of every rank instead of one per pair: what the messager falls back
+    to under a device-bound default group, where torch's subgroup creation would otherwise never finish with
+    three or more ranks (ranks outside a gloo pair take part in a communicator split its members skip)."""
+    _run_ring(3, use_cuda=False, shared_cpu=True)
+
+
 @pytest.mark.gpu
 def test_ring_handoff_nccl_two_gpus():
     """The same exchange with device tensors: headers on gloo, payloads on the pair's NCCL group
@@ -156,6 +164,15 @@ def test_ring_handoff_nccl_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run_ring(2, use_cuda=True)
+
+
+@pytest.mark.gpu
+def test_ring_handoff_nccl_four_gpus():
+    """Four ranks: every pair group has ranks outside it (the case in which per-pair header groups cannot be
+    made under the device-bound default group the messager initialises for NCCL)."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    _run_ring(4, use_cuda=True)
 
 
 def test_layer_split_matches_oracle():

@@ -54,9 +54,11 @@ def _esize(dtype) -> int:
 
 
 class PPMessager:
+    _world_cpu_group = None     # the all-ranks gloo group, made once per process when per-pair ones cannot be
+
     def __init__(self, pp_info, parallel_config=None, device=None, *, backend: Optional[str] = None,
                  recv_slots: int = 2, send_slots: int = 2, init_timeout: timedelta = timedelta(minutes=30),
-                 group_timeout: timedelta = timedelta(days=7)):
+                 group_timeout: timedelta = timedelta(days=7), shared_cpu_group: Optional[bool] = None):
         """`pp_info`: PPInfo(pp_size, pp_rank); `parallel_config`: address / port of the rendezvous when
         this call has to initialise torch.distributed; `device`: where payloads live.  `backend` defaults
         to NCCL for CUDA devices and gloo for CPU (tests)."""
@@ -65,6 +67,7 @@ class PPMessager:
         self.pp_rank, self.pp_size = pp_info.pp_rank, pp_info.pp_size
         self._dev_backend = backend or ("nccl" if self._device.type == "cuda" else "gloo")
         self._group_timeout = group_timeout
+        self._shared_cpu = shared_cpu_group     # None: decided from the default group (see _create_pp_pair_groups)
         if not dist.is_initialized():
             if parallel_config is not None:
                 os.environ.setdefault("MASTER_ADDR", str(parallel_config.torch_distributed_addr))
@@ -104,10 +107,23 @@ class PPMessager:
         every rank (new_group is collective).  pp_size 1 has no pair."""
         if self.pp_size == 1:
             return
+        # A default group that is bound to a device (init_process_group(..., device_id=...)) creates NCCL
+        # subgroups by splitting its communicator, and torch makes the ranks that are NOT in a new subgroup
+        # take part in that split whatever the subgroup's backend is, while the members of a gloo subgroup
+        # do not: with three or more ranks a per-pair gloo group then never finishes.  In that case the
+        # headers travel over one gloo group of all ranks (every rank a member, point-to-point by rank);
+        # the payload groups stay per pair.
+        bound = getattr(dist.distributed_c10d._get_default_group(), "bound_device_id", None) is not None
+        shared_cpu = None
+        if self._shared_cpu if self._shared_cpu is not None else (bound and self._dev_backend != "gloo"):
+            if PPMessager._world_cpu_group is None:
+                PPMessager._world_cpu_group = dist.new_group(backend="gloo", timeout=self._group_timeout)
+            shared_cpu = PPMessager._world_cpu_group
         for r in range(self.pp_size):
             nxt = (r + 1) % self.pp_size
             pair = [world_ranks[r], world_ranks[nxt]]
-            cpu = dist.new_group(backend="gloo", ranks=pair, timeout=self._group_timeout)
+            cpu = shared_cpu if shared_cpu is not None else dist.new_group(backend="gloo", ranks=pair,
+                                                                           timeout=self._group_timeout)
             dev = cpu if self._dev_backend == "gloo" else dist.new_group(backend=self._dev_backend, ranks=pair,
                                                                          timeout=self._group_timeout)
             if store and self.pp_rank == r:
