@@ -260,48 +260,6 @@ moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_
   __syncthreads();
   const long long seg = ((n + 31) / 32 + 31) / 32 * 32;  // entries per warp, a multiple of 32
   const long long w0 = warp * seg;
-  // Up to 8 rounds per warp (n <= 8192: every decode step) keep each entry's expert and local rank in
-  // registers, with the expert ids requested before the first round: the second pass then reads nothing back.
-  constexpr int KEEP = 8;
-  const int rounds = (int)(seg / 32);
-#ifdef B200_INDEX_NO_KEEP
-  const bool keep = false;
-#else
-  const bool keep = rounds <= KEEP;
-#endif
-  int ke[KEEP], kr[KEEP];
-  if (keep) {
-#pragma unroll
-    for (int it = 0; it < KEEP; ++it) {
-      const long long i = w0 + it * 32 + lane;
-      ke[it] = -1;
-      kr[it] = 0;
-      if (it < rounds && i < n) {
-        const long long ev = (long long)experts[i];
-        if (ev >= 0 && ev < E)
-          ke[it] = (int)ev;
-        else
-          report_status(B200_STATUS_BAD_INDEX, (int)ev);
-      }
-    }
-#pragma unroll
-    for (int it = 0; it < KEEP; ++it) {
-      if (it < rounds) {
-        const int e = ke[it];
-        const unsigned mask = __match_any_sync(0xffffffffu, e);
-        const int rank = __popc(mask & ((1u << lane) - 1u));
-        const int leader = __ffs(mask) - 1;
-        int old = 0;
-        if (rank == 0 && e >= 0) {
-          old = cnt[warp][e];
-          cnt[warp][e] = old + __popc(mask);
-        }
-        old = __shfl_sync(0xffffffffu, old, leader);
-        kr[it] = old + rank;
-        __syncwarp();
-      }
-    }
-  } else
   // pass 1: rank of every entry among the warp's earlier entries of the same expert
   for (long long o = 0; o < seg; o += 32) {
     const long long i = w0 + o + lane;
@@ -381,22 +339,6 @@ moe_index_kernel(const TIdx* __restrict__ experts, long long n, int E, int tile_
   }
   __syncthreads();
   // pass 2: local rank -> global position
-  if (keep) {
-#pragma unroll
-    for (int it = 0; it < KEEP; ++it) {
-      const long long i = w0 + it * 32 + lane;
-      if (it < rounds && i < n) {
-        const int e = ke[it];
-        const int pos = e >= 0 ? kr[it] + base[e] + cnt[warp][e] : -1;
-        scatter_index[i] = pos;
-        if (pos >= 0) {
-          if (gather_index) gather_index[pos] = (int)(i / topk);
-          if (row_scale) row_scale[pos] = weights[i];
-        }
-      }
-    }
-    return;
-  }
   for (long long o = 0; o < seg; o += 32) {
     const long long i = w0 + o + lane;
     if (i < n) {
