@@ -196,7 +196,9 @@ int b200_paged_attn_fwd(const void* q, const void* k_cache, const void* v_cache,
  * typically sequences by descending context length; may be NULL) names the sequence each group of
  * tiles belongs to.  The persistent tcgen05 kernel deals tiles to its CTAs round by round, so a
  * longest-first order keeps the CTAs' totals within about one tile of each other.  Results do not
- * depend on the order.  No counterpart in the reference (its grid is one program per head and tile). */
+ * depend on the order.  No counterpart in the reference (its grid is one program per head and tile).
+ * total_q: number of rows of q (0 = not known); with it, tiles of 128 queries fetch their queries by TMA
+ * (rows past total_q read as zeros) instead of through a loader warp.  Results do not depend on it either. */
 int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* v_cache, void* out,
                                 const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
                                 int num_seqs, int max_seqlen_q, int num_q_heads, int num_kv_heads, int dk, int dv,
@@ -204,7 +206,8 @@ int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* 
                                 long long q_tok_stride, long long q_head_stride, long long o_tok_stride,
                                 long long o_head_stride, long long kc_block_stride, long long kc_page_stride,
                                 long long kc_head_stride, long long vc_block_stride, long long vc_page_stride,
-                                long long vc_head_stride, float softmax_scale, const void* seq_order, void* stream);
+                                long long vc_head_stride, float softmax_scale, const void* seq_order,
+                                long long total_q, void* stream);
 
 /* ---- vexact/models/qwen3_moe/modeling_qwen3_moe.py:128-134 (softmax, top-k, renormalise, cast).
  * logits_dtype: 0 = fp32, 1 = bf16.  Any of the four outputs may be NULL except that one weight

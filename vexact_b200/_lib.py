@@ -41,7 +41,7 @@ SIGNATURES = {
     "b200_paged_attn_fwd": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL,
                             LL, LL, F, P],
     "b200_paged_attn_fwd_ordered": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, LL, LL, LL, LL, LL, LL, LL, LL,
-                            LL, LL, F, P, P],
+                            LL, LL, F, P, LL, P],
     "b200_moe_route_softmax_topk": [P, I, LL, P, P, P, P, LL, I, I, I, P],
     "b200_moe_route_sigmoid_group_topk": [P, LL, P, P, P, P, LL, I, I, I, I, I, F, P],
     "b200_moe_permute": [P, I, P, P, LL, P, P, P, P, P, P, LL, I, I, I, I, I, P],
@@ -67,7 +67,7 @@ class B200Error(RuntimeError):
     pass
 
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 def _check_fresh(lib) -> None:

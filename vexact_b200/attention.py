@@ -72,7 +72,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             page_table.shape[1], page_table.stride(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1),
             k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
             v_cache.stride(2), float(softmax_scale), seq_order.data_ptr() if seq_order is not None else None,
-            _lib.current_stream()),
+            q.shape[0], _lib.current_stream()),
         "b200_paged_attn_fwd_ordered",
     )
     return out

@@ -61,6 +61,8 @@ struct AttnParams {
   int num_seqs;
   const int* seq_order;  // [num_seqs] sequence of each slot (longest first), or null
   int max_seqlen_q;      // the caller's bound on queries per sequence: it sized the tile grid
+  int q_tma;             // rows-on-lanes kernel: the query tile comes by TMA (a 3-D box over [token, head, dim])
+  int o_tma;             // rows-on-lanes kernel: a warp's 32 output rows leave by one asynchronous TMA store
   int scalar_out;        // development knob B200_ATTN_OUT_SCALAR=1: 2-byte output stores in the keys-on-lanes kernel
 };
 
@@ -391,7 +393,28 @@ inline bool attn_use_tensor_memory() {
 }
 int attn_tc_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, dim3 grid, int dk, int nc,
                      cudaStream_t st);
-int attn_rows_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t st);
+int attn_rows_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tq, const CUtensorMap& to,
+                       const AttnParams& p, cudaStream_t st);
+
+// Queries as a 3-D tensor [tokens][heads][dim] with a box of {64 dims, box_heads, box_tokens}: the box's rows
+// land in shared memory in (token, head) order, 128 bytes each, 128-byte swizzle, which is the row order of a
+// rows-on-lanes tile.  Tokens past the end read as zeros.
+inline int make_tmap_q(CUtensorMap* m, const void* q, long long tokens, int heads, int dim, long long tok_stride,
+                       long long head_stride, int box_heads, int box_tokens, bool swizzle = true) {
+  EncodeTiledFn enc = tensor_map_encoder();
+  if (!enc) return B200_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (tok_stride * 2) % 16 || (head_stride * 2) % 16 || box_heads <= 0 ||
+      box_heads > 256 || box_tokens <= 0 || box_tokens > 256 || tokens <= 0)
+    return B200_ERR_ARG;
+  cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)head_stride * 2, (cuuint64_t)tok_stride * 2};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_heads, (cuuint32_t)box_tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
+}
 // Prefill tiles of head dim 128: rows-on-lanes kernel unless B200_ATTN_PREFILL=cols.
 // (Read at every call, so that a test can run both kernels in one process and compare their bits.)
 inline bool attn_prefill_rows() {
@@ -417,7 +440,7 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
                                            long long kc_block_stride, long long kc_page_stride,
                                            long long kc_head_stride, long long vc_block_stride,
                                            long long vc_page_stride, long long vc_head_stride, float softmax_scale,
-                                           const void* seq_order, void* stream);
+                                           const void* seq_order, long long total_q, void* stream);
 
 extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const void* v_cache, void* out,
                                    const void* cu_seqlens_q, const void* seqused_k, const void* page_table,
@@ -432,7 +455,7 @@ extern "C" int b200_paged_attn_fwd(const void* q, const void* k_cache, const voi
                                      max_seqlen_q, num_q_heads, num_kv_heads, dk, dv, num_blocks, page_size,
                                      max_pages, page_table_stride, q_tok_stride, q_head_stride, o_tok_stride,
                                      o_head_stride, kc_block_stride, kc_page_stride, kc_head_stride,
-                                     vc_block_stride, vc_page_stride, vc_head_stride, softmax_scale, nullptr, stream);
+                                     vc_block_stride, vc_page_stride, vc_head_stride, softmax_scale, nullptr, 0, stream);
 }
 
 // Same, with an optional processing order: seq_order[i] (int32, a permutation of 0..num_seqs-1, e.g.
@@ -447,7 +470,7 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
                                            long long kc_block_stride, long long kc_page_stride,
                                            long long kc_head_stride, long long vc_block_stride,
                                            long long vc_page_stride, long long vc_head_stride, float softmax_scale,
-                                           const void* seq_order, void* stream) {
+                                           const void* seq_order, long long total_q, void* stream) {
   using namespace b200;
   if (!q || !k_cache || !v_cache || !out || !cu_seqlens_q || !seqused_k || !page_table || num_seqs < 0 ||
       max_seqlen_q < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_blocks <= 0 || page_size <= 0 ||
@@ -517,7 +540,31 @@ extern "C" int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, c
     }
     p.num_seqs = num_seqs;
     p.seq_order = (const int*)seq_order;
-    if (rows) return attn_rows_dispatch(tk, tv, p, st);
+    if (rows) {
+      // The query tile by TMA when every tile of a KV head has the same (heads, positions) shape, i.e. the
+      // group is at most 8 heads or a multiple of 8, and the head stride is at least a head (a box row must
+      // not run into the next head); otherwise the loader warp copies the rows itself.
+      CUtensorMap tq = tk;
+      const int hh_const = group < 8 ? group : 8;
+      const char* qenv = getenv("B200_ATTN_Q_TMA");
+      p.q_tma = 0;
+      if (!(qenv && qenv[0] == '0') && (group <= 8 || group % 8 == 0) && q_head_stride >= dk &&
+          total_q > 0 &&
+          make_tmap_q(&tq, q, total_q, num_q_heads, dk, q_tok_stride, q_head_stride, hh_const, p.pos_per_tile) == B200_OK)
+        p.q_tma = 1;
+      // The output the same way round: each softmax warp owns 32 consecutive tile rows = 32 / heads whole
+      // positions (when the head count per tile divides 32), i.e. one box of {64 dims, heads, 32 / heads positions}
+      // of out [token, head, dim], stored from 128-byte-swizzled shared memory.
+      CUtensorMap to = tk;
+      const char* oenv = getenv("B200_ATTN_O_TMA");
+      p.o_tma = 0;
+      if (!(oenv && oenv[0] == '0') && (group <= 8 || group % 8 == 0) && 32 % hh_const == 0 && o_head_stride >= dv &&
+          total_q > 0 &&
+          make_tmap_q(&to, out, total_q, num_q_heads, dv, o_tok_stride, o_head_stride, hh_const, 32 / hh_const, true) ==
+              B200_OK)
+        p.o_tma = 1;
+      return attn_rows_dispatch(tk, tv, tq, to, p, st);
+    }
     return attn_tc_dispatch(tk, tv, p, grid, dk, nc, st);
   }
   const int q_tiles = (max_seqlen_q + p.pos_per_tile - 1) / p.pos_per_tile;

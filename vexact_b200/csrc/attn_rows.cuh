@@ -81,6 +81,7 @@ __device__ __forceinline__ float butterfly_order_sum32(const float (&p)[32]) {
 template <int DK>
 __global__ void __launch_bounds__(ATR_THREADS, 1)
 paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_out,
                        const AttnParams p) {
   constexpr int DV = 128, NC = ATR_ROWS, KST = 2, VST = 2;
   constexpr int KH = DK / 64, VH = DV / 64;
@@ -155,6 +156,8 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&tm_k);
     ptx::prefetch_tensormap(&tm_v);
+    if (p.q_tma) ptx::prefetch_tensormap(&tm_q);
+    if (p.o_tma) ptx::prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(tmem_slot_p), TMEM_COLS);
@@ -294,6 +297,22 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       if (lane == 0) w = ptx::mbar_wait(qfree_bar(qb), ((tile_it >> 1) & 1) ^ 1, abort_flag, 760 + qb);
       if (!__all_sync(0xffffffffu, w)) break;
       uint8_t* qd = q_ptr + qb * Q_BYTES;
+      if (p.q_tma) {
+        // One box per 64-dim half: {64 dims, heads of this KV head's chunk, positions of the tile}; its rows
+        // arrive in (position, head) order, 128 bytes each, swizzled, i.e. as the tile's rows.  Positions past
+        // the last query token read as zeros; positions past this sequence's queries are other sequences'
+        // rows, whose results are never stored.
+        if (lane == 0) {
+          const int rows = t.heads_here * t.pos_per_tile;
+          ptx::mbar_expect_tx(qfull_bar(qb), (uint32_t)(rows * 128 * (DK / 64)));
+#pragma unroll
+          for (int h = 0; h < DK / 64; ++h)
+            ptx::tma_load_3d(q_smem + qb * Q_BYTES + h * (NC * 128), &tm_q, qfull_bar(qb), h * 64,
+                             t.kvh * p.group + t.hchunk * 8, t.q_start + t.tile_pos0, ptx::kEvictLast);
+        }
+        __syncwarp();
+        continue;
+      }
 #pragma unroll 8
       for (int i = lane; i < NC * (DK / 8); i += 32) {
         const int c = i / (DK / 8), ch = i % (DK / 8);   // row, 16-byte chunk of its head vector
@@ -336,10 +355,16 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       ++pair_phase;
       return ok;
     };
-    AtcTile t;
+    AtcTile t, tn;
     bool alive = true;
-    for (int lin = atc_next_tile<NC>(p, blockIdx.x, t); lin >= 0 && alive;
-         lin = atc_next_tile<NC>(p, lin + (int)gridDim.x, t)) {
+    bool store_pending = false;   // an asynchronous output store of this warp still reads its slice of the P tile
+    int lin = atc_next_tile<NC>(p, blockIdx.x, t);
+    while (lin >= 0 && alive) {
+      // the next tile's description is requested now (loads only) so that it is at hand when this tile ends
+      const int cand = lin + (int)gridDim.x;
+      const bool have_cand = cand < p.tc_slots;
+      AtcRaw raw_next = {0, 0, 0, 0, -1};
+      if (have_cand) raw_next = atc_raw(p, cand);
       const int npos = min(t.pos_per_tile, t.q_len - t.tile_pos0);
       const int pi = row / t.heads_here, hd = row - pi * t.heads_here;
       const int cpos = t.q_abs0 + t.tile_pos0 + (pi < npos ? pi : 0);   // padding rows borrow position 0's mask
@@ -358,6 +383,11 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
         }
         ptx::tc_fence_after();
         if (warp == 4) ATR_STAMP(1, g, 0);   // S full seen
+        if (store_pending) {   // (uniform over the warp) the previous tile's output has left shared memory by now
+          if (lane == 0) ptx::bulk_wait_read0();
+          __syncwarp();
+          store_pending = false;
+        }
         float v[64];
         {
           uint32_t r0[32], r1[32];
@@ -467,39 +497,86 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
       // tile end: the last block's O, the row sum, the store
       if (!ptx::mbar_wait_warp(ofull_bar, (g0 + t.nblk - 1) & 1, abort_flag, 751)) break;
       ptx::tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[16];
-        ptx::tmem_ld16(o_addr + c * 16, r);
+      if (warp == 4) ATR_STAMP(2, g0 + t.nblk - 1, 0);   // last O complete
+      {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(o_addr, r0);
+        tmem_ld32(o_addr + 32, r1);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o[c * 16 + i] += __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) {
+          o[i] += __uint_as_float(r0[i]);
+          o[32 + i] += __uint_as_float(r1[i]);
+        }
       }
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ofree_bar);
+      if (warp == 4) ATR_STAMP(2, g0 + t.nblk - 1, 1);   // O read
       // The half-row sums meet in the maxima buffer of the tile's last block: both threads of every row read
       // it before that block's P was published, and the next tile's first block uses the other buffer.
       float (*s_lh)[NC] = s_hmax[(g0 + t.nblk - 1) & 1];
       s_lh[half][row] = l_a + l_b;             // (l_0 + l_1) from half 0, (l_2 + l_3) from half 1
       if (!pair_sync()) break;
-      if (pi < npos) {
+      if (warp == 4) ATR_STAMP(2, g0 + t.nblk - 1, 2);   // row sums joined
+      {
+        // Output.  A thread holds 64 value dims of one row (128 bytes); stored from there, one warp instruction
+        // would touch 32 rows' lines with 16 bytes each.  The warp first lays its 32 half rows down in its own
+        // 4 KB of the P tile (idle from the tile's last PV product until this warp's next P write; swizzled), then eight
+        // lanes store one row's 128 bytes, four rows per instruction.
         const float inv = 1.0f / (s_lh[0][row] + s_lh[1][row]);
-        __nv_bfloat16* orow = p.out + (long long)(t.q_start + t.tile_pos0 + pi) * p.o_tok_stride +
-                              (long long)(t.kvh * p.group + t.hchunk * 8 + hd) * p.o_head_stride + half * 64;
-        if ((reinterpret_cast<uintptr_t>(orow) & 15) == 0) {
+        const float inv_heads = 1.0f / (float)t.heads_here;
+        const bool vec = ((reinterpret_cast<uintptr_t>(p.out) | (uintptr_t)(p.o_tok_stride * 2) |
+                           (uintptr_t)(p.o_head_stride * 2)) & 15) == 0;
+        if (vec) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            reinterpret_cast<uint4*>(orow)[q] =
-                make_uint4(pack_bf2(o[q * 8] * inv, o[q * 8 + 1] * inv), pack_bf2(o[q * 8 + 2] * inv, o[q * 8 + 3] * inv),
-                           pack_bf2(o[q * 8 + 4] * inv, o[q * 8 + 5] * inv), pack_bf2(o[q * 8 + 6] * inv, o[q * 8 + 7] * inv));
-        } else {
+          for (int q = 0; q < 8; ++q)   // 128-byte rows, 16-byte chunks swizzled by row: no bank conflicts
+            *reinterpret_cast<uint4*>(p_half + sw128(row, q)) = make_uint4(pack_bf2(o[q * 8] * inv, o[q * 8 + 1] * inv), pack_bf2(o[q * 8 + 2] * inv, o[q * 8 + 3] * inv),
+                                 pack_bf2(o[q * 8 + 4] * inv, o[q * 8 + 5] * inv), pack_bf2(o[q * 8 + 6] * inv, o[q * 8 + 7] * inv));
+          const int ppw = 32 / t.heads_here;   // whole positions in this warp's 32 rows (if heads divide 32)
+          if (p.o_tma && ppw * t.heads_here == 32 && (q4 + 1) * ppw <= npos) {
+            // every row of the warp is a real query: one asynchronous store of the warp's box
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              ptx::tma_store_3d(&tm_out, ptx::smem_u32(p_half + q4 * 32 * 128), half * 64,
+                                t.kvh * p.group + t.hchunk * 8, t.q_start + t.tile_pos0 + q4 * ppw);
+              ptx::bulk_commit();
+            }
+            store_pending = true;
+          } else {
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = q4 * 32 + it * 4 + (lane >> 3);          // tile row whose chunk (lane & 7) I store
+            // r / heads_here without an integer division: exact for r < 128 and at most 8 heads
+            const int rpi = (int)(((float)r + 0.5f) * inv_heads), rhd = r - rpi * t.heads_here;
+            if (rpi < npos) {
+              const uint4 v = *reinterpret_cast<const uint4*>(p_half + sw128(r, lane & 7));
+              __nv_bfloat16* orow = p.out + (long long)(t.q_start + t.tile_pos0 + rpi) * p.o_tok_stride +
+                                    (long long)(t.kvh * p.group + t.hchunk * 8 + rhd) * p.o_head_stride + half * 64;
+              reinterpret_cast<uint4*>(orow)[lane & 7] = v;
+            }
+          }
+          __syncwarp();
+          }
+        } else if (pi < npos) {
+          __nv_bfloat16* orow = p.out + (long long)(t.q_start + t.tile_pos0 + pi) * p.o_tok_stride +
+                                (long long)(t.kvh * p.group + t.hchunk * 8 + hd) * p.o_head_stride + half * 64;
 #pragma unroll
           for (int i = 0; i < 64; ++i) orow[i] = f2bf(o[i] * inv);
         }
       }
+      if (warp == 4) ATR_STAMP(2, g0 + t.nblk - 1, 3);   // tile stored
       g0 += t.nblk;
+      lin = -1;
+      if (have_cand) {
+        atc_make<NC>(p, cand, raw_next, tn);
+        lin = tn.valid ? cand : atc_next_tile<NC>(p, cand + (int)gridDim.x, tn);
+      }
+      t = tn;
     }
+    if (lane == 0) ptx::bulk_wait0();   // this warp's output stores are complete before the CTA may leave
   }
 
   __syncthreads();
@@ -516,7 +593,8 @@ paged_attn_rows_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
 }
 
 template <int DK>
-inline int attn_rows_launch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t st) {
+inline int attn_rows_launch(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tq, const CUtensorMap& to,
+                            const AttnParams& p, cudaStream_t st) {
   // tiles (K ring, V ring, two Q buffers, P) + small arrays (barriers, alpha, l, TMEM slot, abort flag) + alignment
   constexpr int tiles = ATC_BN * (2 * DK + 2 * 128) * 2 + 2 * (DK / 64) * ATR_ROWS * 128 + 2 * ATR_ROWS * 128;
   constexpr int small = 256 + 4 * ATR_ROWS * 4 + 16;
@@ -525,12 +603,13 @@ inline int attn_rows_launch(const CUtensorMap& tk, const CUtensorMap& tv, const 
   static PerDeviceFlags attr_set;
   if (int rc = set_max_dyn_smem_once(attr_set, paged_attn_rows_kernel<DK>, smem)) return rc;
   const int nctas = p.tc_tiles < sm_count() ? p.tc_tiles : sm_count();
-  launch_k(paged_attn_rows_kernel<DK>, dim3((unsigned)nctas), dim3(ATR_THREADS), (size_t)smem, st, tk, tv, p);
+  launch_k(paged_attn_rows_kernel<DK>, dim3((unsigned)nctas), dim3(ATR_THREADS), (size_t)smem, st, tk, tv, tq, to, p);
   return launch_status();
 }
 
-inline int attn_rows_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const AttnParams& p, cudaStream_t st) {
-  return attn_rows_launch<128>(tk, tv, p, st);
+inline int attn_rows_dispatch(const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tq, const CUtensorMap& to,
+                              const AttnParams& p, cudaStream_t st) {
+  return attn_rows_launch<128>(tk, tv, tq, to, p, st);
 }
 
 }  // namespace b200
