@@ -69,6 +69,9 @@ def parse_args():
     ap.add_argument("--skew", action="store_true",
                     help="side measurement: one MoE layer of the model with near-uniform routing and with a "
                          "Zipf(1.1) router bias: rows per expert, token tiles, fc1 / fc2 time")
+    ap.add_argument("--row-kernels", action="store_true",
+                    help="side measurement: the row kernels (RMSNorm, log_softmax, gather_logprob, kv_store) at the "
+                         "operator-suite shapes, rotating over inputs larger than L2, GB/s per kernel")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
                     help="side measurement: time one causal prefill attention call of QLEN queries on the "
                          "model's head shape (context --ctx if larger) and print its own JSON line")
@@ -480,6 +483,57 @@ def run_skew(args, shape):
     print(json.dumps(res))
 
 
+def run_row_kernels(args, shape):
+    """Side measurement (not the contract line): the HBM-bound row kernels at BASELINE config 1's shapes
+    (hidden 2048, vocabulary 151936), each call on a fresh input (a ring of inputs larger than the L2), CUDA events."""
+    from vexact_b200.batch_invariant_ops import batch_invariant_rms_norm, hf_rms_norm, log_softmax
+    from vexact_b200.kv_cache_context import store_kvcache
+    from vexact_b200.standalone_logprobs import logprobs_from_logits_flash_attn
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    BF = torch.bfloat16
+    out = {}
+
+    def timed(name, calls, nbytes):
+        for c in calls[:2]:
+            c()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for c in calls:
+            c()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / len(calls)
+        out[name] = {"us": round(us, 2), "bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1)}
+
+    rows, n, V = 16384, shape.hidden, shape.vocab
+    w = torch.randn(n, device=dev, generator=g).to(BF)
+    xs = [torch.randn(rows, n, device=dev, generator=g).to(BF) for _ in range(4)]        # 4 x 64 MB
+    timed(f"rms_norm_{rows}x{n}", [lambda x=x: batch_invariant_rms_norm(x, w, 1e-6) for x in xs], rows * n * 4)
+    timed(f"hf_rms_norm_{rows}x{n}", [lambda x=x: hf_rms_norm(x, w, 1e-6) for x in xs], rows * n * 4)
+    M = 256
+    ls = [torch.randn(M, V, device=dev, generator=g) * 2 for _ in range(3)]                # 3 x 156 MB fp32
+    labels = torch.randint(0, V, (M,), device=dev, generator=g)
+    timed(f"log_softmax_f32_{M}x{V}", [lambda x=x: log_softmax(x, -1) for x in ls], M * V * 8)
+    timed(f"gather_logprob_f32_{M}x{V}", [lambda x=x: logprobs_from_logits_flash_attn(x, labels) for x in ls], M * V * 4)
+    lb = [x.to(BF) for x in ls] + [x.to(BF) * 0.5 for x in ls]
+    timed(f"gather_logprob_bf16_{M}x{V}", [lambda x=x: logprobs_from_logits_flash_attn(x, labels) for x in lb], M * V * 2)
+    T, hkv, d, page = 16384, shape.num_kv_heads, shape.head_dim, args.page
+    blocks = 4 * T // page
+    kc = torch.zeros(blocks, page, hkv, d, device=dev, dtype=BF)
+    vc = torch.zeros_like(kc)
+    ks = [torch.randn(T, hkv, d, device=dev, generator=g).to(BF) for _ in range(4)]
+    slots = [torch.randperm(T, device=dev, generator=g).int() + i * T for i in range(4)]
+    timed(f"kv_store_{T}_tokens", [lambda k=k, sl=sl: store_kvcache(k, k, kc, vc, sl) for k, sl in zip(ks, slots)],
+          T * hkv * d * 2 * 4)
+    peak = float(measured_peaks().get("hbm_gbs", 6650.0))
+    for v in out.values():
+        v["frac_of_measured_hbm"] = round(v["GBps"] / peak, 3)
+    print(json.dumps({"measurement": "row_kernels", "hbm_peak_GBps": peak, "kernels": out}))
+
+
 def run_prefill_attention(args, shape):
     """Side measurement (not the contract line): one sequence's causal prefill through paged attention."""
     import vexact_b200 as vb
@@ -500,18 +554,37 @@ def run_prefill_attention(args, shape):
     for _ in range(max(args.warmup, 1)):
         call()
     torch.cuda.synchronize()
-    best = float("inf")
+    # eager call: CUDA events around one call, i.e. with the host's launch path (three tensor-map encodes) inside
+    eager = float("inf")
     for _ in range(max(args.steps, 1)):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         call()
         b.record()
         torch.cuda.synchronize()
-        best = min(best, a.elapsed_time(b))
+        eager = min(eager, a.elapsed_time(b))
+    # the kernel by itself: `reps` calls captured in one CUDA graph, replayed
+    reps = 8
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            call()
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(max(args.steps, 1)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b) / reps)
     keys = sum(range(kvlen - qlen + 1, kvlen + 1))          # causal (query, key) pairs
     flops = 2.0 * keys * hq * 2 * d                          # QK^T and PV
     print(json.dumps({"measurement": "prefill_attention", "queries": qlen, "context": kvlen, "heads": hq,
-                      "kv_heads": hkv, "head_dim": d, "ms": best, "tflops": flops / best / 1e9}))
+                      "kv_heads": hkv, "head_dim": d, "ms": best, "tflops": flops / best / 1e9,
+                      "timing": "8 calls in a CUDA graph, per call", "eager_call_ms": eager,
+                      "eager_call_tflops": flops / eager / 1e9}))
 
 
 def main():
@@ -530,6 +603,9 @@ def main():
         return
     if args.skew:
         run_skew(args, shape)
+        return
+    if args.row_kernels:
+        run_row_kernels(args, shape)
         return
     if args.prefill_attention:
         run_prefill_attention(args, shape)
