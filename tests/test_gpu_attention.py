@@ -279,6 +279,46 @@ def test_rows_kernel_and_columns_kernel_give_the_same_bits(vb):
         assert torch.equal(rows, cols), f"{(hq, hkv, page, q_lens)}: max diff {(rows.float() - cols.float()).abs().max()}"
 
 
+def test_query_and_output_tiles_by_tma_change_no_bit(vb):
+    """The rows-on-lanes kernel fetches its query tile by TMA and stores a warp's output rows by one TMA store
+    when the tile shape allows it, and through a loader warp / per-lane stores otherwise (B200_ATTN_Q_TMA=0,
+    B200_ATTN_O_TMA=0 force those): same bits; rows outside the tiles' valid positions (a sequence's last,
+    partial tile; the canary rows behind q) are never written."""
+    g = torch.Generator().manual_seed(78)
+    for (hq, hkv, page, q_lens, ctx) in [(32, 4, 16, [130, 40, 1, 7], [130, 200, 257, 7]),     # groups of 8
+                                         (16, 8, 16, [300, 33], [300, 513]),                # groups of 2
+                                         (12, 2, 16, [257, 64], [1000, 64]),               # groups of 6: no output box
+                                         (16, 1, 16, [70], [70])]:                          # two chunks of 8 heads
+        S, d = len(ctx), 128
+        pages = max((c + page - 1) // page for c in ctx)
+        kc = torch.randn(S * pages + 1, page, hkv, d, generator=g).to(BF).cuda()
+        vc = torch.randn(S * pages + 1, page, hkv, d, generator=g).to(BF).cuda()
+        table = torch.randperm(S * pages, generator=g).view(S, pages).to(torch.int32).cuda()
+        q = torch.randn(sum(q_lens), hq, d, generator=g).to(BF).cuda()
+        cu = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32).cuda()
+        used = torch.tensor(ctx, dtype=torch.int32).cuda()
+        kw = dict(cu_seqlens_q=cu, max_seqlen_q=max(q_lens), seqused_k=used, page_table=table,
+                  softmax_scale=d ** -0.5, causal=True)
+        with_tma, _ = vb.flash_attn_varlen_func(q, kc, vc, **kw)
+        os.environ["B200_ATTN_Q_TMA"] = "0"
+        os.environ["B200_ATTN_O_TMA"] = "0"
+        try:
+            without, _ = vb.flash_attn_varlen_func(q, kc, vc, **kw)
+        finally:
+            del os.environ["B200_ATTN_Q_TMA"], os.environ["B200_ATTN_O_TMA"]
+        torch.cuda.synchronize()
+        assert torch.equal(with_tma, without), f"{(hq, hkv, page, q_lens)}"
+        # only the first sequence's rows are asked for: the rows of the others must stay untouched
+        from vexact_b200.attention import paged_attention
+
+        canary = torch.full_like(with_tma, 7.0)
+        paged_attention(q, kc, vc, cu[:2].contiguous(), used[:1].contiguous(), table[:1].contiguous(), d ** -0.5,
+                        q_lens[0], out=canary)
+        torch.cuda.synchronize()
+        assert torch.equal(canary[:q_lens[0]], with_tma[:q_lens[0]])
+        assert bool((canary[q_lens[0]:] == 7.0).all())
+
+
 def test_packed_varlen_forward_equals_paged_prefill_bitwise(vb):
     """The training-side packed call (no page table) must give the rollout's bits: same tokens through the
     packed path and through a paged prefill with another page size and a shuffled page table."""

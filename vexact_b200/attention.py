@@ -29,8 +29,10 @@ def _require_cuda_int32(name: str, t: torch.Tensor) -> None:
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_seqlens_q: torch.Tensor,
                     seqused_k: torch.Tensor, page_table: torch.Tensor, softmax_scale: float,
-                    max_seqlen_q: int, seq_order: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q (total_q, heads, dk) against caches (blocks, page, kv_heads, d); returns (total_q, heads, dv).
+                    max_seqlen_q: int, seq_order: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q (total_q, heads, dk) against caches (blocks, page, kv_heads, d); returns (total_q, heads, dv)
+    (written into `out` when given; rows of q that belong to no sequence are left as they are).
 
     seq_order (int32 [num_seqs], optional): a permutation of the sequences, longest context first,
     that balances the persistent kernel's CTAs on ragged batches; it never changes a result."""
@@ -58,7 +60,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         cu_seqlens_q = cu_seqlens_q.contiguous()
     if not seqused_k.is_contiguous():
         seqused_k = seqused_k.contiguous()
-    out = torch.empty((q.shape[0], q.shape[1], v_cache.shape[-1]), device=q.device, dtype=q.dtype)
+    shape_out = (q.shape[0], q.shape[1], v_cache.shape[-1])
+    if out is None:
+        out = torch.empty(shape_out, device=q.device, dtype=q.dtype)
+    elif tuple(out.shape) != shape_out or out.dtype != q.dtype or out.device != q.device or out.stride(-1) != 1:
+        raise ValueError(f"out must be a {q.dtype} tensor of shape {shape_out} on {q.device}")
     num_seqs = seqused_k.numel()
     if seq_order is not None:
         _require_cuda_int32("seq_order", seq_order)
