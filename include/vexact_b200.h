@@ -122,6 +122,14 @@ int b200_sample_token(const void* logits, const void* noise_q_f32, void* tokens_
                       long long rows, int n, long long row_stride, long long q_row_stride, int dtype,
                       float temperature, int top_k, float top_p, void* stream);
 
+/* ---- HF nn.Embedding on input_ids, and vexact/inferencer/inferencer.py:403-404 (each sequence's last-token row:
+ *      hidden[query_start_loc[1:] - 1]) as one row-gather kernel instead of torch indexing kernels:
+ *      out[t, :] = src[ids[t], :] (ids int64), or with ids_i64 == NULL src[max(query_start_loc[t + 1] - 1, 0), :].
+ *      src rows src_row_stride elements apart, out [T, H] contiguous bf16, H % 8 == 0.  An index outside
+ *      [0, src_rows) is reported in the status word (code 2) and reads row 0. */
+int b200_gather_rows(const void* src, long long src_rows, long long src_row_stride, const void* ids_i64,
+                     const void* query_start_loc_i32, void* out, long long T, int H, void* stream);
+
 /* ---- vexact/inferencer/sampler.py:57-63, 90-118 seeded sampling (per-request seed, keyed by token position):
  *      fills noise_q_f32 [rows, n] with Exp(1) draws from Philox4x32-10 (key = seeds[r], counter = (column / 4,
  *      positions[r], 0)), to be passed to b200_sample_token.  A request's draws depend on its seed, the position

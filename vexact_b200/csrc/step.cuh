@@ -143,3 +143,47 @@ extern "C" int b200_prepare_step(const int* num_computed_tokens, const int* toke
            (cudaStream_t)stream, p);
   return launch_status();
 }
+
+// ------------------------------------------------------------------ row gathers of the stage runner
+// Two gathers of [rows, H] bf16 rows that the reference leaves to torch indexing kernels: the embedding
+// lookup (HF nn.Embedding on input_ids) and the pick of each sequence's last token before the final norm and
+// lm_head (vexact/inferencer/inferencer.py:403-404: hidden[query_start_loc[1:] - 1]).
+namespace b200 {
+
+// mode 0: src row = ids[t] (int64).  mode 1: src row = max(query_start_loc[t + 1] - 1, 0) (int32 offsets).
+// A row index outside [0, src_rows) is reported and reads row 0.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long long src_stride, long long src_rows,
+                   const long long* __restrict__ ids, const int* __restrict__ query_start_loc,
+                   __nv_bfloat16* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  long long r = ids ? ids[t] : (long long)query_start_loc[t + 1] - 1;
+  if (!ids && r < 0) r = 0;   // a zero-length (padding) sequence: any row will do, its result is not used
+  if (r < 0 || r >= src_rows) {
+    if (threadIdx.x == 0) report_status(B200_STATUS_BAD_INDEX, (int)r);
+    r = 0;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(src + r * src_stride);
+  uint4* d = reinterpret_cast<uint4*>(out + t * (long long)H);
+  for (int i = threadIdx.x; i < (H >> 3); i += 256) d[i] = s[i];
+}
+
+}  // namespace b200
+
+// out[t, :] = src[ids[t], :] (ids int64) or, with ids == NULL, src[max(query_start_loc[t + 1] - 1, 0), :].
+// src rows are src_row_stride elements apart; out is [T, H] contiguous; H a multiple of 8; 16-byte aligned rows.
+extern "C" int b200_gather_rows(const void* src, long long src_rows, long long src_row_stride, const void* ids_i64,
+                                const void* query_start_loc_i32, void* out, long long T, int H, void* stream) {
+  using namespace b200;
+  if (!src || !out || (!ids_i64 && !query_start_loc_i32) || src_rows <= 0 || T < 0 || H <= 0) return B200_ERR_ARG;
+  if (H % 8 != 0 || src_row_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  if (T > 0x7fffffffLL) return B200_ERR_SHAPE;
+  launch_k(gather_rows_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)src,
+           src_row_stride, src_rows, (const long long*)ids_i64, (const int*)query_start_loc_i32, (__nv_bfloat16*)out, H);
+  return launch_status();
+}

@@ -192,6 +192,20 @@ class PendingMoE:
         )
         return out.reshape(self.shape)
 
+    def finish_add(self, residual: torch.Tensor) -> torch.Tensor:
+        """residual + moe output (each a bf16 tensor, as `residual + finish()` computes it) in the top-k sum's
+        own launch; with a shared-expert addend pending the two steps stay separate."""
+        if self.addend is not None:
+            return residual + self.finish()
+        out = torch.empty((self.T, self.H), device=self.y.device, dtype=torch.bfloat16)
+        r = residual.reshape(self.T, self.H).contiguous()
+        _lib.check(
+            _lib.load().b200_moe_unpermute_reduce(self.y.data_ptr(), self.scatter_index.data_ptr(), r.data_ptr(),
+                                                  out.data_ptr(), self.T, self.k, self.H, _lib.current_stream()),
+            "b200_moe_unpermute_reduce",
+        )
+        return out.reshape(residual.shape)
+
     def add_norm(self, residual: torch.Tensor, weight: torch.Tensor, eps: float, hf: bool = True):
         """(residual + moe output, rmsnorm of that sum): `finish()` + `add_rms_norm` in one launch."""
         # the fused kernel reproduces the one-CTA-per-row norm kernel, which serves rows of 1025..8192 elements

@@ -247,6 +247,28 @@ class StepInputs:
     seq_order: Optional[torch.Tensor] = None  # [S] int32, sequences by descending context (attention balance)
 
 
+def _gather_rows(src: torch.Tensor, ids: Optional[torch.Tensor] = None,
+                 query_start_loc: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """src[ids] (the embedding lookup) or each sequence's last-token row src[query_start_loc[1:] - 1]
+    (inferencer.py:403-404; a zero-length padding sequence reads row 0), one kernel either way."""
+    if src.dim() != 2 or src.dtype != BF or src.stride(1) != 1:
+        raise ValueError("row gather expects a 2-D bf16 matrix with contiguous rows")
+    if ids is not None:
+        ids = ids.reshape(-1)
+        if ids.dtype != torch.int64 or not ids.is_contiguous():
+            ids = ids.to(torch.int64).contiguous()
+        T = ids.numel()
+    else:
+        if query_start_loc.dtype != torch.int32 or not query_start_loc.is_contiguous():
+            query_start_loc = query_start_loc.to(torch.int32).contiguous()
+        T = query_start_loc.numel() - 1
+    out = torch.empty((T, src.shape[1]), device=src.device, dtype=BF)
+    _lib.check(_lib.load().b200_gather_rows(src.data_ptr(), src.shape[0], src.stride(0), _lib.ptr(ids),
+                                            _lib.ptr(query_start_loc) if ids is None else None, out.data_ptr(), T,
+                                            src.shape[1], _lib.current_stream()), "b200_gather_rows")
+    return out
+
+
 class StageRunner:
     """Runs the local layers of one pipeline stage; optionally through a captured CUDA graph."""
 
@@ -376,7 +398,7 @@ class StageRunner:
     def forward(self, inp: StepInputs) -> torch.Tensor:
         """Hidden states after the local layers ([T, H]); the residual stream is complete."""
         if self.is_first:
-            h = self.w.embed.index_select(0, inp.input_ids)
+            h = _gather_rows(self.w.embed, ids=inp.input_ids)
         else:
             h = inp.hidden_in
         delta = None
@@ -389,7 +411,7 @@ class StageRunner:
             h, xn2 = self._add_norm(attn_out, h, lw.post_norm)
             delta = self._mlp_block(lw, xn2)
         if delta is not None:
-            h = h + (delta.finish() if isinstance(delta, PendingMoE) else delta)
+            h = delta.finish_add(h) if isinstance(delta, PendingMoE) else h + delta
         return h
 
     def last_token_logits(self, h: torch.Tensor, inp: StepInputs) -> torch.Tensor:
@@ -400,8 +422,7 @@ class StageRunner:
         return linear(self.last_token_hidden(h, inp), self.w.lm_head)
 
     def last_token_hidden(self, h: torch.Tensor, inp: StepInputs) -> torch.Tensor:
-        last = (inp.query_start_loc[1:] - 1).to(torch.long)
-        return self._norm(h.index_select(0, last.clamp(min=0)), self.w.final_norm)
+        return self._norm(_gather_rows(h, query_start_loc=inp.query_start_loc), self.w.final_norm)
 
     def select_tokens(self, h: torch.Tensor, inp: StepInputs):
         """Last stage: last-token logits -> greedy (or sampled) token + its logprob."""
