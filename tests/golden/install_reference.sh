@@ -1,9 +1,9 @@
 #!/bin/sh
 # Puts the UNMODIFIED reference package where the GPU-side fixture generator
 # (make_reference_gpu_golden.py, same directory) can import it: the git-ignored baseline/_ref/,
-# which travels to the GPU box with the working tree but never enters the history.
+# which travels with the working tree but never enters the history.
 #
-#   sh tests/golden/install_reference.sh [/path/to/vexact-checkout]
+#   sh tests/golden/install_reference.sh /path/to/vexact-checkout      (or VEXACT_REFERENCE=... in the environment)
 #
 # First choice is a regular offline pip install.  The project's build backend (hatchling) is not
 # in the offline wheelhouse, so that fails here; a wheel of this pure-Python project is nothing
@@ -11,7 +11,7 @@
 # packages = ["vexact"]), and unpacking that directory into the target is what pip would have done.
 # Test infrastructure only: nothing under vexact_b200/ and no timed region of bench.py imports it.
 set -e
-REF="${1:-/root/reference}"
+REF="${1:-${VEXACT_REFERENCE:?give the path of the reference checkout}}"
 ROOT="$(cd "$(dirname "$0")/../.." && pwd)"
 DEST="$ROOT/baseline/_ref"
 mkdir -p "$DEST"

@@ -15,8 +15,7 @@ Model-level sections run a stock HuggingFace module tree twice, once under the r
 the stage runner on weights loaded from the same module, and report per-token logprob deltas.
 
 A section that cannot run records the exception text instead of numbers.  One GPU only: quack's sm100
-GEMM uses thread-block clusters, so this script is listed in .gpurunignore.multi and is never part of
-a multi-GPU call.  Test infrastructure: nothing here is imported by vexact_b200/ or timed by bench.py.
+GEMM uses thread-block clusters, so this script is a one-GPU tool and is kept out of multi-GPU runs.  Test infrastructure: nothing here is imported by vexact_b200/ or timed by bench.py.
 """
 from __future__ import annotations
 
@@ -687,7 +686,7 @@ SECTIONS = [sec_matmul, sec_rowops, sec_kv_store, sec_attention, sec_moe, sec_mo
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=os.path.join(ROOT, "gpurun_out", "ref_gpu"))
+    ap.add_argument("--out", default=os.path.join(ROOT, "ref_gpu_out"))
     ap.add_argument("--sections", default="")
     args = ap.parse_args()
     os.makedirs(args.out, exist_ok=True)
