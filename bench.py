@@ -634,7 +634,8 @@ def main():
     _lib.load()
     pp = world
     if pp > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # a rank that dies must end the others' waits with an error, not leave the run hanging
+        dist.init_process_group("nccl", device_id=device, timeout=__import__("datetime").timedelta(minutes=5))
     S, H = args.batch, shape.hidden
     watchdog = float(os.environ.get("B200_BENCH_WATCHDOG", "0") or 0)
     if watchdog > 0:      # debugging aid: every rank prints its Python stack if the run is still going by then
@@ -657,7 +658,8 @@ def main():
 
         # one receive slot per batch in flight: batch b of every round lands at the same addresses, so
         # each later stage captures its graph directly on the received views (no copy on arrival)
-        msg = PPMessager(PPInfo(pp, rank), None, device, recv_slots=n_inflight, send_slots=2)
+        msg = PPMessager(PPInfo(pp, rank), None, device, recv_slots=n_inflight, send_slots=2,
+                         group_timeout=__import__("datetime").timedelta(minutes=5))
     runners, graphs, outs, step_inputs, step_bufs, kv_blocks = [], [], [], [], [], []
     computed_host, tts_host = [args.ctx] * S, [1] * S    # per-request counters of a decode step
     first_ctx = [None] * n_inflight                       # stages > 0: the context a batch's graph was captured on
