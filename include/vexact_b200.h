@@ -122,6 +122,22 @@ int b200_sample_token(const void* logits, const void* noise_q_f32, void* tokens_
                       long long rows, int n, long long row_stride, long long q_row_stride, int dtype,
                       float temperature, int top_k, float top_p, void* stream);
 
+/* ---- modeling_qwen3_moe.py:128-134 routing + fused_moe.py:268-292 index math in two launches instead of three:
+ *      b200_moe_route_plan_softmax_topk routes like b200_moe_route_softmax_topk and also gives every selected
+ *      (token, expert) its rank inside the expert's group (an atomic counter per expert) and, from the last CTA to
+ *      finish, cu_seqlens and the token-tile table; b200_moe_scatter_ranked then writes the expert-sorted copy,
+ *      row_scale and scatter_index.  Rows keep no particular order inside an expert's group (it varies from run
+ *      to run), which changes no output of the MoE; the reference's index arrays are reproduced by
+ *      b200_moe_permute.  counters_i32: 257 int32, zero before the first call, left zero by every call; calls
+ *      sharing it must not overlap on the GPU. */
+int b200_moe_route_plan_softmax_topk(const void* logits, int logits_dtype, long long row_stride, void* weights_bf16,
+                                     void* experts_i64, void* rank_i32, void* counters_i32, void* cu_seqlens,
+                                     void* tile_table, void* tile_count, long long T, int E, int topk, int renorm,
+                                     int tile_rows, int max_tiles, void* stream);
+int b200_moe_scatter_ranked(const void* x, long long x_row_stride, const void* experts_i64, const void* weights_bf16,
+                            const void* rank_i32, const void* cu_seqlens, void* scatter_index, void* x_perm,
+                            void* row_scale, long long T, int topk, int E, int H, void* stream);
+
 /* ---- HF nn.Embedding on input_ids, and vexact/inferencer/inferencer.py:403-404 (each sequence's last-token row:
  *      hidden[query_start_loc[1:] - 1]) as one row-gather kernel instead of torch indexing kernels:
  *      out[t, :] = src[ids[t], :] (ids int64), or with ids_i64 == NULL src[max(query_start_loc[t + 1] - 1, 0), :].

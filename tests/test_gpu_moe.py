@@ -212,6 +212,39 @@ def test_fc1_gathering_its_rows_equals_the_permuted_copy_bitwise(vb, monkeypatch
     assert torch.equal(outs["1"][0], outs["1"][2])
 
 
+@pytest.mark.parametrize("T,E,k,H,I,skew", [(1, 8, 2, 64, 32, False), (40, 128, 8, 2048, 768, False),
+                                            (512, 128, 8, 2048, 768, False), (300, 8, 2, 512, 192, True)])
+def test_routing_with_its_plan_equals_route_index_scatter_bitwise(vb, T, E, k, H, I, skew):
+    """Routing that hands out the permutation itself (two launches) against route -> index -> scatter (three):
+    same routing weights and experts, cu_seqlens and tile table; the rows of an expert's group may sit in another
+    order, and every output of the MoE is the same bits.  Twice in a row: the counters come back clean."""
+    from vexact_b200.fused_moe import _PLAN_COUNTERS, _permute, route_plan_softmax_topk
+
+    hidden, gate_up, down, _, _ = _moe_case(T, E, k, H, I, seed=21, skew=skew)
+    g = torch.Generator().manual_seed(4)
+    logits = (torch.randn(T, E, generator=g) * (3.0 if skew else 1.0)).to(BF).cuda()
+    x, gu, dn = hidden.cuda(), gate_up.cuda(), down.cuda()
+    rw0, sel0 = vb.route_softmax_topk(logits, k, True)
+    want = vb.fused_moe_forward(E, rw0, sel0, x, fc2_weight=dn, fc1_1_2_weight=gu)
+    classic = _permute(sel0, rw0, None, E)
+    for _ in range(2):
+        rw, sel, plan = route_plan_softmax_topk(logits, k, True, E)
+        assert torch.equal(rw, rw0) and torch.equal(sel, sel0)
+        assert torch.equal(plan["cu_seqlens"], classic["cu_seqlens"])
+        assert torch.equal(plan["tile_count"], classic["tile_count"])
+        nt = int(plan["tile_count"])
+        assert torch.equal(plan["tile_table"][:nt], classic["tile_table"][:nt])
+        # ranks: within every expert exactly 0 .. count-1
+        cnt = torch.bincount(sel.flatten(), minlength=E)
+        for e in range(E):
+            r = plan["rank"][(sel.flatten() == e)].sort().values
+            assert torch.equal(r, torch.arange(int(cnt[e]), device="cuda", dtype=torch.int32))
+        got = vb.fused_moe_forward(E, rw, sel, x, fc2_weight=dn, fc1_1_2_weight=gu, plan=plan)
+        assert torch.equal(got, want)
+        torch.cuda.synchronize()
+        assert int(_PLAN_COUNTERS[torch.cuda.current_device()].abs().sum()) == 0
+
+
 def test_gather_index_is_the_inverse_of_scatter_index(vb):
     from vexact_b200.fused_moe import _permute
 

@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200_sample_token": [P, P, P, P, LL, I, LL, LL, I, F, I, F, P],
     "b200_seeded_exponential": [P, P, P, LL, I, LL, P],
     "b200_gather_rows": [P, LL, LL, P, P, P, LL, I, P],
+    "b200_moe_route_plan_softmax_topk": [P, I, LL, P, P, P, P, P, P, P, LL, I, I, I, I, I, P],
+    "b200_moe_scatter_ranked": [P, LL, P, P, P, P, P, P, P, LL, I, I, I, P],
     "b200_selftest_wait_expiry": [I, P, P],
     "b200_prepare_step": [P, P, P, P, P, P, I, I, I, I, I, P, P, P, P, P, P, P, P],
     "b200_kv_store": [P, P, P, P, P, LL, I, I, I, LL, LL, LL, P],

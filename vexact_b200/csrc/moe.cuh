@@ -574,6 +574,173 @@ extern "C" int b200_moe_route_softmax_topk(const void* logits, int logits_dtype 
   return launch_status();
 }
 
+// ------------------------------------------------------------------ routing + plan in two launches
+// The decode chain route -> index -> scatter is three dependent launches of which the middle one (a stable
+// counting sort on one CTA) exists only to give every sorted row a position.  Which position a row gets
+// inside its expert's group changes no result: a GEMM row's value does not depend on where the row sits, and
+// the top-k sum finds its rows through scatter_index.  So the routing kernel hands out ranks itself (one
+// atomicAdd per selected expert: counts[e]++), the last of its CTAs to finish (a ticket counter, nobody waits
+// for anybody) turns the counts into cu_seqlens and the token-tile table and clears the counters for the next
+// call, and the scatter kernel places row f at cu_seqlens[e] + rank[f].  The order of rows within an expert
+// therefore varies from run to run; every output bit is the same.  b200_moe_permute keeps the stable order
+// (it is what reproduces the reference's index arrays).
+namespace b200 {
+
+template <typename TIn>
+__global__ void __launch_bounds__(256)
+moe_route_plan_kernel(const TIn* __restrict__ logits, long long row_stride, __nv_bfloat16* __restrict__ w_bf16,
+                      long long* __restrict__ idx_i64, int* __restrict__ rank_out, int* __restrict__ counters,
+                      int* __restrict__ cu_seqlens, int4* __restrict__ tile_table, int* __restrict__ tile_count,
+                      long long T, int E, int topk, int renorm, int tile_rows, int max_tiles) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ int s_last;
+  __shared__ int s_scan[2][8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long tok = (long long)blockIdx.x * 8 + warp;
+  if (tok < T) {
+    route_softmax_topk_token<TIn>(logits + tok * row_stride, tok, w_bf16, nullptr, nullptr, idx_i64, E, topk, renorm,
+                                  lane);
+    __syncwarp();
+    // the expert ids were just written by lane 0: lane k takes entry k's rank in its expert's group
+    if (lane < topk) {
+      const int e = (int)idx_i64[tok * topk + lane];
+      rank_out[tok * topk + lane] = atomicAdd(&counters[e], 1);
+    }
+  }
+  // counters[MOE_MAX_EXPERTS] is the ticket: the CTA that draws the last one sees every count
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&counters[MOE_MAX_EXPERTS], 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // 256 threads, one expert each (E <= MOE_MAX_EXPERTS = 256): exclusive scans of rows and tiles
+  const int e = threadIdx.x;
+  const int rows = e < E ? __ldcg(&counters[e]) : 0;
+  const int tiles = (rows + tile_rows - 1) / tile_rows;
+  int r = rows, t = tiles;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int r2 = __shfl_up_sync(0xffffffffu, r, o);
+    const int t2 = __shfl_up_sync(0xffffffffu, t, o);
+    if (lane >= o) {
+      r += r2;
+      t += t2;
+    }
+  }
+  if (lane == 31) {
+    s_scan[0][warp] = r;
+    s_scan[1][warp] = t;
+  }
+  __syncthreads();
+  int roff = 0, toff = 0;
+  for (int w = 0; w < warp; ++w) {
+    roff += s_scan[0][w];
+    toff += s_scan[1][w];
+  }
+  const int rexcl = roff + r - rows, texcl = toff + t - tiles;
+  if (e < E) {
+    cu_seqlens[e] = rexcl;
+    for (int j = 0; j < tiles; ++j)
+      if (texcl + j < max_tiles)
+        tile_table[texcl + j] = make_int4(e, rexcl + j * tile_rows, min(tile_rows, rows - j * tile_rows), 0);
+    if (e == E - 1) {
+      cu_seqlens[E] = rexcl + rows;
+      *tile_count = min(texcl + tiles, max_tiles);
+    }
+    counters[e] = 0;   // ready for the next call
+  }
+  if (threadIdx.x == 0) counters[MOE_MAX_EXPERTS] = 0;
+}
+
+// Row f = (token f / topk, choice f % topk) goes to sorted row cu_seqlens[expert] + rank[f].
+__global__ void __launch_bounds__(128)
+moe_scatter_ranked_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
+                          const long long* __restrict__ experts, const __nv_bfloat16* __restrict__ weights,
+                          const int* __restrict__ rank, const int* __restrict__ cu_seqlens,
+                          int* __restrict__ scatter_index, __nv_bfloat16* __restrict__ x_perm,
+                          __nv_bfloat16* __restrict__ row_scale, int H, int topk, int E, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  const long long f = blockIdx.x;
+  const long long e = experts[f];
+  if (e < 0 || e >= E) {
+    if (threadIdx.x == 0) {
+      report_status(B200_STATUS_BAD_INDEX, (int)e);
+      scatter_index[f] = -1;
+    }
+    return;
+  }
+  const long long pos = (long long)cu_seqlens[e] + rank[f];
+  if (pos < 0 || pos >= n) {   // counters that were not clean when the routing kernel ran
+    if (threadIdx.x == 0) {
+      report_status(B200_STATUS_BAD_INDEX, (int)pos);
+      scatter_index[f] = -1;
+    }
+    return;
+  }
+  const __nv_bfloat16* src = x + (f / topk) * x_stride;
+  __nv_bfloat16* dst = x_perm + pos * H;
+  for (int i = threadIdx.x; i < (H >> 3); i += 128)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  if (threadIdx.x == 0) {
+    scatter_index[f] = (int)pos;
+    if (row_scale && weights) row_scale[pos] = weights[f];
+  }
+}
+
+}  // namespace b200
+
+// Qwen3-MoE routing (modeling_qwen3_moe.py:128-134) that also plans the permutation: weights_bf16 [T, topk],
+// experts_i64 [T, topk] as b200_moe_route_softmax_topk writes them, plus rank [T*topk] i32 (the row's place
+// inside its expert's group), cu_seqlens [E+1], tile_table / tile_count as b200_moe_permute writes them.
+// counters: E_max + 1 = 257 int32, zero before the first call; every call leaves them zero again.  Calls that
+// share a counters array must not overlap on the GPU.
+extern "C" int b200_moe_route_plan_softmax_topk(const void* logits, int logits_dtype /*0 = f32, 1 = bf16*/,
+                                                long long row_stride, void* weights_bf16, void* experts_i64,
+                                                void* rank_i32, void* counters_i32, void* cu_seqlens,
+                                                void* tile_table, void* tile_count, long long T, int E, int topk,
+                                                int renorm, int tile_rows, int max_tiles, void* stream) {
+  using namespace b200;
+  if (!logits || !weights_bf16 || !experts_i64 || !rank_i32 || !counters_i32 || !cu_seqlens || !tile_table ||
+      !tile_count || T <= 0 || E <= 0 || topk <= 0 || tile_rows <= 0 || max_tiles <= 0)
+    return B200_ERR_ARG;
+  if (E > MOE_MAX_EXPERTS || topk > MOE_MAX_TOPK || topk > E || topk > 32) return B200_ERR_SHAPE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned grid = (unsigned)((T + 7) / 8);
+  if (logits_dtype == 0)
+    launch_k(moe_route_plan_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)logits, row_stride,
+             (__nv_bfloat16*)weights_bf16, (long long*)experts_i64, (int*)rank_i32, (int*)counters_i32,
+             (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, T, E, topk, renorm, tile_rows, max_tiles);
+  else if (logits_dtype == 1)
+    launch_k(moe_route_plan_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)logits,
+             row_stride, (__nv_bfloat16*)weights_bf16, (long long*)experts_i64, (int*)rank_i32, (int*)counters_i32,
+             (int*)cu_seqlens, (int4*)tile_table, (int*)tile_count, T, E, topk, renorm, tile_rows, max_tiles);
+  else
+    return B200_ERR_ARG;
+  return launch_status();
+}
+
+// The permuted copy for a plan made by b200_moe_route_plan_softmax_topk: x_perm, row_scale and scatter_index.
+extern "C" int b200_moe_scatter_ranked(const void* x, long long x_row_stride, const void* experts_i64,
+                                       const void* weights_bf16, const void* rank_i32, const void* cu_seqlens,
+                                       void* scatter_index, void* x_perm, void* row_scale, long long T, int topk,
+                                       int E, int H, void* stream) {
+  using namespace b200;
+  if (!x || !experts_i64 || !rank_i32 || !cu_seqlens || !scatter_index || !x_perm || T < 0 || topk <= 0 || E <= 0 ||
+      H <= 0 || (row_scale && !weights_bf16))
+    return B200_ERR_ARG;
+  if (H % 8 != 0 || x_row_stride % 8 != 0) return B200_ERR_SHAPE;
+  const long long n = T * topk;
+  if (n == 0) return B200_OK;
+  if (n > 0x7fffffffLL) return B200_ERR_SHAPE;
+  launch_k(moe_scatter_ranked_kernel, dim3((unsigned)n), dim3(128), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x,
+           x_row_stride, (const long long*)experts_i64, (const __nv_bfloat16*)weights_bf16, (const int*)rank_i32,
+           (const int*)cu_seqlens, (int*)scatter_index, (__nv_bfloat16*)x_perm, (__nv_bfloat16*)row_scale, H, topk, E, n);
+  return launch_status();
+}
+
 extern "C" int b200_moe_route_sigmoid_group_topk(const void* logits_f32, long long row_stride,
                                                  const void* bias_f32, void* weights_f32, void* experts_i32,
                                                  void* experts_i64, long long T, int E, int n_group,

@@ -58,6 +58,69 @@ def route_softmax_topk(router_logits: torch.Tensor, top_k: int, norm_topk_prob: 
     return w, idx
 
 
+_PLAN_COUNTERS: dict = {}      # device index -> the 257 zeroed int32 counters of the routing-plan kernel
+
+
+def route_plan_softmax_topk(router_logits: torch.Tensor, top_k: int, norm_topk_prob: bool, num_experts: int):
+    """`route_softmax_topk` that also plans the expert permutation in the same launch.
+
+    Returns (routing_weights [T, k] bf16, selected_experts [T, k] int64, plan); pass `plan` to
+    `fused_moe_forward(..., plan=plan)`.  The plan orders rows inside an expert's group by arrival (an atomic
+    counter), not by token; no MoE output depends on that order.  The counters live in one array per device,
+    so calls on one device must not overlap (they do not on one stream)."""
+    if not router_logits.is_cuda:
+        raise ValueError("router_logits must be a CUDA tensor")
+    T, E = router_logits.shape
+    if E != num_experts:
+        raise ValueError("router logits do not have one column per expert")
+    x = router_logits if router_logits.stride(-1) == 1 else router_logits.contiguous()
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError(f"router logits dtype {x.dtype}")
+    dev = x.device
+    counters = _PLAN_COUNTERS.get(dev.index)
+    if counters is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("make the first routing-plan call on a device outside graph capture")
+        counters = torch.zeros(257, device=dev, dtype=torch.int32)
+        _PLAN_COUNTERS[dev.index] = counters
+    n = T * top_k
+    max_tiles = max(1, max_token_tiles(n, num_experts))
+    w = torch.empty((T, top_k), device=dev, dtype=torch.bfloat16)
+    idx = torch.empty((T, top_k), device=dev, dtype=torch.int64)
+    rank = torch.empty(n, device=dev, dtype=torch.int32)
+    cu_seqlens = torch.empty(num_experts + 1, device=dev, dtype=torch.int32)
+    tile_table = torch.empty((max_tiles, 4), device=dev, dtype=torch.int32)
+    tile_count = torch.empty(1, device=dev, dtype=torch.int32)
+    _lib.check(
+        _lib.load().b200_moe_route_plan_softmax_topk(
+            x.data_ptr(), 0 if x.dtype == torch.float32 else 1, x.stride(0), w.data_ptr(), idx.data_ptr(),
+            rank.data_ptr(), counters.data_ptr(), cu_seqlens.data_ptr(), tile_table.data_ptr(), tile_count.data_ptr(),
+            T, E, top_k, 1 if norm_topk_prob else 0, TILE_ROWS, max_tiles, _lib.current_stream()),
+        "b200_moe_route_plan_softmax_topk",
+    )
+    plan = dict(rank=rank, cu_seqlens=cu_seqlens, tile_table=tile_table, tile_count=tile_count, max_tiles=max_tiles)
+    return w, idx, plan
+
+
+def _scatter_ranked(plan: dict, expert_index: torch.Tensor, routing_weights: torch.Tensor, x: torch.Tensor,
+                    num_experts: int) -> dict:
+    """Expert-sorted copy of x, row scales and scatter_index for a plan of `route_plan_softmax_topk`."""
+    T, k = expert_index.shape
+    n, H = T * k, x.shape[-1]
+    x_perm = torch.empty((n, H), device=x.device, dtype=torch.bfloat16)
+    row_scale = torch.empty(n, device=x.device, dtype=torch.bfloat16)
+    scatter_index = torch.empty(n, device=x.device, dtype=torch.int32)
+    _lib.check(
+        _lib.load().b200_moe_scatter_ranked(
+            x.data_ptr(), x.stride(0), expert_index.data_ptr(), routing_weights.data_ptr(), plan["rank"].data_ptr(),
+            plan["cu_seqlens"].data_ptr(), scatter_index.data_ptr(), x_perm.data_ptr(), row_scale.data_ptr(), T, k,
+            num_experts, H, _lib.current_stream()),
+        "b200_moe_scatter_ranked",
+    )
+    return dict(scatter_index=scatter_index, cu_seqlens=plan["cu_seqlens"], tile_table=plan["tile_table"],
+                tile_count=plan["tile_count"], x_perm=x_perm, row_scale=row_scale, max_tiles=plan["max_tiles"])
+
+
 def route_sigmoid_group_topk(router_logits: torch.Tensor, e_score_correction_bias: Optional[torch.Tensor],
                              n_group: int, topk_group: int, top_k: int, norm_topk_prob: bool,
                              routed_scaling_factor: float):
@@ -237,6 +300,7 @@ def fused_moe_forward(
     fc1_1_2_weight: Optional[torch.Tensor] = None,
     addend: Optional[torch.Tensor] = None,
     defer_reduce: bool = False,
+    plan: Optional[dict] = None,
 ):
     """sum_k w_k * fc2_e(silu(fc1_1_e x) * fc1_2_e x) for the selected experts e of each token.
 
@@ -259,7 +323,12 @@ def fused_moe_forward(
     T, H = x.shape
     k = selected_experts.shape[-1]
     selected_experts = selected_experts.reshape(T, k)
-    plan = _permute(selected_experts, routing_weights.reshape(T, k), x, num_experts, gather=_gather_default())
+    if plan is not None:      # made by route_plan_softmax_topk together with the routing
+        if selected_experts.dtype != torch.int64 or not selected_experts.is_contiguous():
+            raise ValueError("a routing plan goes with the int64 expert indices its routing call returned")
+        plan = _scatter_ranked(plan, selected_experts, routing_weights.reshape(T, k), x, num_experts)
+    else:
+        plan = _permute(selected_experts, routing_weights.reshape(T, k), x, num_experts, gather=_gather_default())
     if fc1_1_2_weight is not None:
         assert fc1_1_2_weight.dtype == torch.bfloat16 and fc1_1_2_weight.is_contiguous()
         I = fc1_1_2_weight.shape[1] // 2

@@ -15,6 +15,7 @@ libvexact_b200.so.  The whole stage forward is captured in a CUDA graph per toke
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -23,12 +24,18 @@ import torch
 from . import _lib
 from .attention import paged_attention
 from .batch_invariant_ops import add_rms_norm, batch_invariant_rms_norm, hf_rms_norm, linear, linear_f32_from_bf16
-from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_sigmoid_group_topk,
+from .fused_moe import (TILE_ROWS, PendingMoE, _grouped_gemm, fused_moe_forward, route_plan_softmax_topk,
+                        route_sigmoid_group_topk,
                         route_softmax_topk)
 from .standalone_logprobs import greedy_token_and_logprob, lm_head_greedy
 from .sampler import sample_token_and_logprob
 
 BF = torch.bfloat16
+# B200_MOE_ROUTE_PLAN=1: routing hands out the permutation itself (route -> scatter, two launches instead of
+# route -> index -> scatter; same outputs bit for bit, rows of an expert's group in arrival order).  Off by
+# default: inside the captured decode step it measured 0.0-0.5 % (32.04 -> 31.87-32.04 ms), within run-to-run
+# noise, and the stable order is the simpler thing to reason about.
+_ROUTE_PLAN = os.environ.get("B200_MOE_ROUTE_PLAN", "0") == "1"
 
 
 @dataclass(frozen=True)
@@ -391,6 +398,10 @@ class StageRunner:
             return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
                                      fc1_1_2_weight=lw.experts_gate_up, addend=shared, defer_reduce=True)
         logits = linear(xn, lw.router, lw.router_logit_bias)   # (aten::addmm when the router Linear has a bias)
+        if _ROUTE_PLAN:   # routing and the permutation plan in one launch
+            rw, sel, plan = route_plan_softmax_topk(logits, m.top_k, m.norm_topk_prob, m.num_experts)
+            return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
+                                     fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True, plan=plan)
         rw, sel = route_softmax_topk(logits, m.top_k, m.norm_topk_prob)
         return fused_moe_forward(m.num_experts, rw, sel, xn, fc2_weight=lw.experts_down,
                                  fc1_1_2_weight=lw.experts_gate_up, defer_reduce=True)
