@@ -49,8 +49,10 @@ kv_store_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __rest
   }
 }
 
-// One warp per (token, head).  head_dim is 128: each lane owns 4 consecutive
-// elements; rotate_half pairs element j with j +- 64, i.e. lane l with lane l ^ 16.
+// One CTA per token, eight warps taking its heads in turn (head h of the fused qkv row: q heads, then k heads,
+// then v heads).  head_dim is 128: each lane owns 4 consecutive elements; rotate_half pairs element j with
+// j +- 64, i.e. lane l with lane l ^ 16.  The token's 64 (cos, sin) pairs are computed once, by the CTA, while
+// every warp's head slices are already on their way from memory.
 __global__ void __launch_bounds__(256)
 qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_stride,
                          const long long* __restrict__ positions, const int* __restrict__ slot_mapping,
@@ -61,98 +63,88 @@ qknorm_rope_store_kernel(const __nv_bfloat16* __restrict__ qkv, long long qkv_st
                          float eps) {
   pdl_trigger();
   pdl_wait();
-  constexpr int D = 128;
+  constexpr int D = 128, MAXH = 8;   // heads per warp held in registers at a time
   const int heads_total = num_q_heads + 2 * num_kv_heads;
-  // When the head count is a multiple of the 8 warps of a CTA, all of them serve one token: its 64
-  // (cos, sin) pairs are computed once into shared memory instead of once per head.
   __shared__ float s_cos[64], s_sin[64];
-  const bool one_token = heads_total % 8 == 0;
-  // This warp's head: its 8-byte slice per lane and (for K / V) the cache slot are requested first, so that
-  // the loads are in flight while the CTA computes the token's cos / sin table.
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const bool valid = wid < num_tokens * heads_total;
-  const int lane = threadIdx.x & 31;
-  const long long tok = valid ? wid / heads_total : 0;
-  const int head = valid ? (int)(wid % heads_total) : 0;
-  const bool is_q = head < num_q_heads;
-  const bool is_k = !is_q && head < num_q_heads + num_kv_heads;
-  uint2 raw = make_uint2(0u, 0u);
-  long long slot = -1;
-  if (valid) {
-    raw = *reinterpret_cast<const uint2*>(qkv + tok * qkv_stride + (long long)head * D + lane * 4);
-    if (!is_q) slot = slot_mapping[tok];
-  }
-  if (one_token) {
-    const long long tok0 = (long long)blockIdx.x * 8 / heads_total;
-    if (threadIdx.x < 64 && tok0 < num_tokens) {
-      const float ang = (float)positions[tok0] * inv_freq[threadIdx.x];
-      s_cos[threadIdx.x] = round_bf(cosf(ang));
-      s_sin[threadIdx.x] = round_bf(sinf(ang));
+  const long long tok = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const __nv_bfloat16* row = qkv + tok * qkv_stride;
+  const long long slot = slot_mapping[tok];
+  for (int h0 = 0; h0 < heads_total; h0 += 8 * MAXH) {
+    // this warp's heads of the chunk: h0 + warp, h0 + warp + 8, ...; all their slices are requested first
+    uint2 raw[MAXH];
+#pragma unroll
+    for (int i = 0; i < MAXH; ++i) {
+      const int head = h0 + warp + 8 * i;
+      raw[i] = head < heads_total ? *reinterpret_cast<const uint2*>(row + (long long)head * D + lane * 4)
+                                  : make_uint2(0u, 0u);
     }
-    __syncthreads();
-  }
-  if (!valid) return;
-  if (!is_q) {
-    if (slot < 0) return;  // padded token: nothing to cache
-    if (slot >= num_slots) {
-      if (lane == 0) report_status(B200_STATUS_BAD_INDEX, (int)slot);
-      return;
+    if (h0 == 0) {
+      if (threadIdx.x < 64) {
+        const float ang = (float)positions[tok] * inv_freq[threadIdx.x];
+        s_cos[threadIdx.x] = round_bf(cosf(ang));
+        s_sin[threadIdx.x] = round_bf(sinf(ang));
+      }
+      __syncthreads();
     }
-  }
-  if (!is_q && !is_k) {  // V: plain copy into the cache
-    const int kvh = head - num_q_heads - num_kv_heads;
-    *reinterpret_cast<uint2*>(v_cache + (slot * num_kv_heads + kvh) * D + lane * 4) = raw;
-    return;
-  }
-
-  float x[4];
-  unpack_bf2(raw.x, x[0], x[1]);
-  unpack_bf2(raw.y, x[2], x[3]);
-  const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
-  if (nw != nullptr) {
-    float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
-    ss = warp_sum(ss);
-    const float inv = rsqrtf(ss / (float)D + eps);
-    const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
-    float w[4];
-    unpack_bf2(wr.x, w[0], w[1]);
-    unpack_bf2(wr.y, w[2], w[3]);
+    for (int i = 0; i < MAXH; ++i) {
+      const int head = h0 + warp + 8 * i;
+      if (head >= heads_total) break;
+      const bool is_q = head < num_q_heads;
+      const bool is_k = !is_q && head < num_q_heads + num_kv_heads;
+      if (!is_q) {
+        if (slot < 0) continue;  // padded token: nothing to cache
+        if (slot >= num_slots) {
+          if (lane == 0) report_status(B200_STATUS_BAD_INDEX, (int)slot);
+          continue;
+        }
+      }
+      if (!is_q && !is_k) {  // V: plain copy into the cache
+        const int kvh = head - num_q_heads - num_kv_heads;
+        *reinterpret_cast<uint2*>(v_cache + (slot * num_kv_heads + kvh) * D + lane * 4) = raw[i];
+        continue;
+      }
+      float x[4];
+      unpack_bf2(raw[i].x, x[0], x[1]);
+      unpack_bf2(raw[i].y, x[2], x[3]);
+      const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
+      if (nw != nullptr) {
+        float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) x[j] = round_bf(w[j] * round_bf(x[j] * inv));
-  }
-  // RoPE.  cos/sin are bf16 tensors in the HF model: emb = cat(freqs, freqs),
-  // freqs[j] = position * inv_freq[j] in fp32, cos = bf16(cos(emb)).
-  const float pos = (float)positions[tok];
-  float partner[4];
+        for (int j = 0; j < 4; ++j) ss += x[j] * x[j];
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        const uint2 wr = *reinterpret_cast<const uint2*>(nw + lane * 4);
+        float w[4];
+        unpack_bf2(wr.x, w[0], w[1]);
+        unpack_bf2(wr.y, w[2], w[3]);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) partner[j] = __shfl_xor_sync(0xffffffffu, x[j], 16);
-  const bool upper = lane >= 16;  // elements 64..127
-  float y[4];
+        for (int j = 0; j < 4; ++j) x[j] = round_bf(w[j] * round_bf(x[j] * inv));
+      }
+      // RoPE.  cos/sin are bf16 tensors in the HF model: emb = cat(freqs, freqs),
+      // freqs[j] = position * inv_freq[j] in fp32, cos = bf16(cos(emb)).
+      float partner[4];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const int fi = (lane & 15) * 4 + j;  // frequency index in [0, 64)
-    float c, s;
-    if (one_token) {
-      c = s_cos[fi];
-      s = s_sin[fi];
-    } else {
-      const float ang = pos * inv_freq[fi];
-      c = round_bf(cosf(ang));
-      s = round_bf(sinf(ang));
+      for (int j = 0; j < 4; ++j) partner[j] = __shfl_xor_sync(0xffffffffu, x[j], 16);
+      const bool upper = lane >= 16;  // elements 64..127
+      float y[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int fi = (lane & 15) * 4 + j;  // frequency index in [0, 64)
+        const float rot = upper ? partner[j] : -partner[j];  // rotate_half: cat(-x2, x1)
+        y[j] = round_bf(round_bf(x[j] * s_cos[fi]) + round_bf(rot * s_sin[fi]));
+      }
+      uint2 o;
+      o.x = pack_bf2(y[0], y[1]);
+      o.y = pack_bf2(y[2], y[3]);
+      if (is_q) {
+        *reinterpret_cast<uint2*>(q_out + (tok * num_q_heads + head) * D + lane * 4) = o;
+      } else {
+        const int kvh = head - num_q_heads;
+        *reinterpret_cast<uint2*>(k_cache + (slot * num_kv_heads + kvh) * D + lane * 4) = o;
+      }
     }
-    const float rot = upper ? partner[j] : -partner[j];  // rotate_half: cat(-x2, x1)
-    y[j] = round_bf(round_bf(x[j] * c) + round_bf(rot * s));
-  }
-  uint2 o;
-  o.x = pack_bf2(y[0], y[1]);
-  o.y = pack_bf2(y[2], y[3]);
-  if (is_q) {
-    *reinterpret_cast<uint2*>(q_out + (tok * num_q_heads + head) * D + lane * 4) = o;
-  } else {
-    const int kvh = head - num_q_heads;
-    *reinterpret_cast<uint2*>(k_cache + (slot * num_kv_heads + kvh) * D + lane * 4) = o;
   }
 }
 
@@ -258,8 +250,8 @@ extern "C" int b200_qknorm_rope_store(const void* qkv, long long qkv_token_strid
   if ((q_norm_weight == nullptr) != (k_norm_weight == nullptr)) return B200_ERR_ARG;
   if (qkv_token_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(qkv) & 7) != 0) return B200_ERR_ARG;
   if (num_tokens == 0) return B200_OK;
-  const long long warps = num_tokens * (num_q_heads + 2 * num_kv_heads);
-  launch_k(qknorm_rope_store_kernel, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
+  if (num_tokens > 0x7fffffffLL) return B200_ERR_SHAPE;
+  launch_k(qknorm_rope_store_kernel, dim3((unsigned)num_tokens), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)qkv, qkv_token_stride, (const long long*)positions, (const int*)slot_mapping,
       (const __nv_bfloat16*)q_norm_weight, (const __nv_bfloat16*)k_norm_weight, (const float*)inv_freq,
       (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, num_q_heads, num_kv_heads,
