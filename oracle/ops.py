@@ -5,13 +5,15 @@ all index work is integer-exact), what the cited reference code computes.  Paths
 are relative to the verl-project/vexact tree.
 
 Pinning: every function here is checked against fixtures under tests/golden/
-(tests/test_oracle_golden.py).  The fixtures were produced by
-tests/golden/make_golden.py, which runs the reference's own Triton kernels under
-the Triton CPU interpreter and the reference's torch-level model code on CPU.
-The expert arithmetic the reference's model files delegate to
-`veomni.ops.fused_moe_forward` (veomni @ a4ed599, not vendored) has no fixture:
-that boundary is "parity unpinned"; the oracle follows the repository's own
-vexact/batch_invariant_ops/fused_moe.py instead.
+(tests/test_oracle_golden.py), of two kinds.  (1) tests/golden/make_golden.py ran the
+reference's own Triton kernels under the Triton CPU interpreter and the reference's
+torch-level model code on CPU.  (2) tests/golden/make_reference_gpu_golden.py ran the
+reference's compiled kernels on a B200 with bf16 operands (ref_gpu_*.pt): its Triton GEMM,
+norms, log-softmax, KV store and paged attention (P really rounded to bf16), flash-attn's
+cross entropy, and the fused-MoE expert arithmetic through both of the reference's expert
+functions (Triton and quack), which is what the model files' call to
+`veomni.ops.fused_moe_forward` (veomni @ a4ed599, not vendored) is bound to
+(vexact/models/register.py:40-57).
 """
 from __future__ import annotations
 

@@ -193,3 +193,95 @@ def test_mla_projection_and_rope_match_hf_deepseek_modules():
     q2, k2, v2 = cpu_model.mla_qkv(shape, lw, x[0], pos[0])
     assert torch.equal(q2, Q[0].transpose(0, 1)) and torch.equal(k2, K[0].transpose(0, 1))
     assert torch.equal(v2, v[0].transpose(0, 1))
+
+
+# --------------------------------------------------------------------------------------------------------------
+# The oracle against outputs of the reference's COMPILED kernels (tests/golden/ref_gpu_*.pt, written on a B200 by
+# tests/golden/make_reference_gpu_golden.py; inputs rebuilt here from the same seeds, guarded by checksums).
+# These pin what the interpreter fixtures above cannot: bf16 operands end to end (P really rounded to bf16 in the
+# attention kernel) and the fused-MoE expert arithmetic (Triton and quack expert functions).  The oracle's GEMMs
+# run through torch's CPU bf16 matmul, whose accumulation order is not the kernels', hence tolerances here; the
+# CUDA kernels meet the same fixtures bit for bit where tests/test_gpu_reference_parity.py says so.
+import os as _os
+
+import pytest
+import sys as _sys
+
+from conftest import GOLDEN as _GOLDEN
+
+_sys.path.insert(0, _GOLDEN)
+import golden_inputs as _gi  # noqa: E402
+
+
+def _have(name):
+    return _os.path.exists(_os.path.join(_GOLDEN, name + ".pt"))
+
+
+@pytest.mark.skipif(not _have("ref_gpu_matmul"), reason="fixture not generated")
+def test_oracle_matmul_vs_compiled_reference():
+    for fx in load_golden("ref_gpu_matmul"):
+        a, w, bias = _gi.matmul_inputs(fx["case"])
+        assert _gi.checksum(a, w, bias) == fx["checksum"], "seeded inputs changed"
+        for got, want in ((ops.matmul(a, w.t()), fx["out"]), (ops.matmul(a, w.t(), bias), fx["out_bias"])):
+            tol = 2.0 ** -7 * want.float().abs().clamp(min=0.25)       # one bf16 ulp, with a floor for cancellation
+            assert bool(((got.float() - want.float()).abs() <= tol).all()), fx["case"]
+            assert (got == want).float().mean() > 0.97, fx["case"]
+
+
+@pytest.mark.skipif(not _have("ref_gpu_rms_norm"), reason="fixture not generated")
+def test_oracle_row_ops_vs_compiled_reference():
+    for fx in load_golden("ref_gpu_rms_norm"):
+        x, w = _gi.rmsnorm_inputs(fx["case"])
+        assert _gi.checksum(x, w) == fx["checksum"]
+        got = ops.rms_norm_single_round(x, w, 1e-6)
+        assert _ulp_diff_bf16(got, fx["out"]) <= 1 and (got == fx["out"]).float().mean() > 0.999, fx["case"]
+    for fx in load_golden("ref_gpu_mean_dim"):
+        x, _ = _gi.rmsnorm_inputs(fx["case"], seed=23)
+        torch.testing.assert_close(ops.mean_lastdim(x.float()).reshape(-1), fx["out"].reshape(-1), rtol=1e-6, atol=1e-7)
+    for fx in load_golden("ref_gpu_logits"):
+        x, labels, cols = _gi.logits_inputs(fx["case"])
+        assert _gi.checksum(x, labels) == fx["checksum"]
+        torch.testing.assert_close(ops.log_softmax(x)[:, cols], fx["log_softmax_cols"], rtol=0, atol=4e-6)
+        torch.testing.assert_close(ops.gather_logprob(x, labels), fx["logprob"], rtol=0, atol=4e-6)
+    fx = load_golden("ref_gpu_kv_store")
+    c = fx["case"]
+    key, value, slots = _gi.kv_store_inputs()
+    kc = torch.zeros((c["blocks"], c["page"], c["heads"], c["dk"]), dtype=torch.bfloat16)
+    vc = torch.zeros((c["blocks"], c["page"], c["heads"], c["dv"]), dtype=torch.bfloat16)
+    ops.kv_store(key, value, kc, vc, slots)
+    assert torch.equal(kc, fx["k_cache"]) and torch.equal(vc, fx["v_cache"])
+
+
+@pytest.mark.skipif(not _have("ref_gpu_paged_attention"), reason="fixture not generated")
+def test_oracle_attention_vs_compiled_reference_bf16_p():
+    """bf16 operands: the reference kernel really rounds P to bf16 (triton_invariant_attention.py:542); the
+    blocked oracle with the reference's 64-key blocks restates exactly that."""
+    for fx in load_golden("ref_gpu_paged_attention"):
+        case = fx["case"]
+        q, kc, vc, cu, used, table = _gi.attention_inputs(case)
+        assert _gi.checksum(q, kc, vc, cu, used, table) == fx["checksum"]
+        block_n = 64 if case["dk"] <= 128 else 32        # the reference's BLOCK_N choice (:648-649)
+        got = ops.paged_attention(q, kc, vc, cu, used, table, case["dk"] ** -0.5, block_n=block_n)
+        d = (got.float() - fx["out"].float()).abs()
+        assert d.max() <= 0.04 and d.mean() <= 1e-3, (case["name"], float(d.max()), float(d.mean()))
+
+
+@pytest.mark.skipif(not _have("ref_gpu_fused_moe"), reason="fixture not generated")
+def test_oracle_fused_moe_vs_compiled_reference_triton_and_quack():
+    """The expert arithmetic (fused_moe.py:299-344) as the reference's own Triton and quack expert functions
+    computed it on bf16 operands: the oracle's restatement of the rounding points, checked against both."""
+    for fx in load_golden("ref_gpu_fused_moe"):
+        case = fx["case"]
+        hidden, gate_up, down, router = _gi.moe_inputs(case)
+        assert _gi.checksum(hidden, gate_up, down, router) == fx["checksum"]
+        E, I = case["E"], case["I"]
+        sel, rw = fx["selected"], fx["weights"]
+        # index math, bit exact against the reference's histogram kernel + sorts
+        cu, _, scat = ops.build_moe_indices(sel, E)
+        assert torch.equal(torch.as_tensor(scat).reshape(-1).int(), fx["scatter_index"].reshape(-1).int()), case["name"]
+        got = ops.fused_moe_batched(E, rw, sel, hidden, gate_up[:, :I], gate_up[:, I:], down)
+        for tag in ("out_triton", "out_quack"):
+            want = fx[tag]
+            tol = 2.0 ** -6 * max(float(want.float().abs().max()), 1e-3)
+            torch.testing.assert_close(got.float(), want.float(), rtol=0, atol=tol)
+            assert (got == want).float().mean() > 0.90, (case["name"], tag)
