@@ -51,6 +51,11 @@ int b200_status_read(int* host_out4, void* stream);
 int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
                    long long x_row_stride, long long w_row_stride, long long out_row_stride, int out_dtype,
                    void* stream);
+/* The same GEMM on fp16 tensors (matmul_persistent serves bf16, fp16 and fp32, batch_invariant_ops.py:181-189):
+ * fp32 accumulation in the same K order, bias (fp16) added in fp32, one rounding.  out_dtype 0 = f16, 1 = f32. */
+int b200_gemm_f16(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
+                  long long x_row_stride, long long w_row_stride, long long out_row_stride, int out_dtype,
+                  void* stream);
 
 /* fp32 variant for the DeepSeek-V3 router (vexact/models/deepseek_v3/modeling_deepseek_v3.py:97-100,
  * F.linear in fp32, reaching matmul_persistent with fp32 operands).  Exact fp32 FMA arithmetic. */

@@ -139,3 +139,25 @@ def test_fused_lm_head_greedy_matches_two_kernel_path_and_is_batch_invariant():
     assert t1.item() == tr.item()
     from vexact_b200 import _lib
     assert _lib.read_status()[0] == 0
+
+
+def test_fp16_matmul_and_batch_invariance(vb):
+    """matmul_persistent on fp16 tensors (the reference serves bf16, fp16 and fp32): fp32 accumulation, bias in
+    fp32, one rounding to fp16; a row's bits do not depend on the batch it is computed in."""
+    g = torch.Generator().manual_seed(12)
+    for (M, K, N) in [(1, 2048, 768), (7, 512, 200), (64, 2048, 6144), (300, 1536, 256)]:
+        a = (torch.randn(M, K, generator=g)).half()
+        w = (torch.randn(N, K, generator=g) * 0.05).half()
+        bias = torch.randn(N, generator=g).half()
+        ad, wd, bd = a.cuda(), w.cuda(), bias.cuda()
+        out = vb.matmul_persistent(ad, wd.t())
+        outb = vb.matmul_persistent(ad, wd.t(), bd)
+        assert out.dtype == torch.float16
+        ref = a.double() @ w.double().t()
+        for got, want in ((out, ref), (outb, ref + bias.double())):
+            err = (got.cpu().double() - want).abs()
+            tol = 2.0 ** -10 * want.abs().clamp(min=0.5)           # one fp16 ulp, with a floor for cancellation
+            assert bool((err <= tol).all()), (M, K, N, float(err.max()))
+        assert torch.equal(vb.matmul_persistent(ad[:1], wd.t(), bd), outb[:1])
+        if M > 8:
+            assert torch.equal(vb.matmul_persistent(ad[5:8], wd.t(), bd), outb[5:8])

@@ -21,6 +21,7 @@ SIGNATURES = {
     "b200_abi_version": [],
     "b200_status_read": [C.POINTER(C.c_int), P],
     "b200_gemm_bf16": [P, P, P, P, LL, I, I, LL, LL, LL, I, P],
+    "b200_gemm_f16": [P, P, P, P, LL, I, I, LL, LL, LL, I, P],
     "b200_gemm_f32": [P, P, P, P, LL, I, I, LL, LL, LL, P],
     "b200_gemm_f32_from_bf16": [P, P, P, LL, I, I, LL, LL, LL, P],
     "b200_rmsnorm": [P, P, P, LL, I, LL, LL, F, I, P],

@@ -58,21 +58,22 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         weight = weight.contiguous()
     T = x2.shape[0]
     lib = _lib.load()
-    if x.dtype == torch.bfloat16:
-        out_dtype = out_dtype or torch.bfloat16
-        if out_dtype not in (torch.bfloat16, torch.float32):
+    if x.dtype in (torch.bfloat16, torch.float16):
+        out_dtype = out_dtype or x.dtype
+        if out_dtype not in (x.dtype, torch.float32):
             raise ValueError(f"unsupported output dtype {out_dtype}")
         if K % 8 or x2.stride(0) % 8 or weight.stride(0) % 8 or x2.data_ptr() % 16 or weight.data_ptr() % 16:
-            raise ValueError("bf16 matmul needs K and row strides that are multiples of 8 and 16-byte aligned data")
+            raise ValueError("16-bit matmul needs K and row strides that are multiples of 8 and 16-byte aligned data")
         if bias is not None:
             assert bias.dim() == 1, "bias must be 1-D"
-            bias = bias.to(torch.bfloat16).contiguous()
+            bias = bias.to(x.dtype).contiguous()
         out = torch.empty((T, N), device=x.device, dtype=out_dtype)
+        fn, name = (lib.b200_gemm_bf16, "b200_gemm_bf16") if x.dtype == torch.bfloat16 else \
+            (lib.b200_gemm_f16, "b200_gemm_f16")
         _lib.check(
-            lib.b200_gemm_bf16(x2.data_ptr(), weight.data_ptr(), _lib.ptr(bias), out.data_ptr(), T, N, K,
-                               x2.stride(0), weight.stride(0), out.stride(0),
-                               0 if out_dtype == torch.bfloat16 else 1, _lib.current_stream()),
-            "b200_gemm_bf16",
+            fn(x2.data_ptr(), weight.data_ptr(), _lib.ptr(bias), out.data_ptr(), T, N, K, x2.stride(0),
+               weight.stride(0), out.stride(0), 0 if out_dtype == x.dtype else 1, _lib.current_stream()),
+            name,
         )
     elif x.dtype == torch.float32:
         if bias is not None:

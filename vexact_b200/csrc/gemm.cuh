@@ -60,6 +60,7 @@ struct GemmParams {
   // already in tile order).  The activation tensor map then has a one-row box and the producer warp fetches
   // four rows per TMA gather.
   const int* gather_idx;
+  int fp16;             // plain dense mode: operands, bias and 16-bit output are fp16 instead of bf16
   int scalar_epilogue;  // development knob B200_GEMM_EPI_SCALAR=1: 2-byte stores in the plain epilogue
   const int* tile_count;
   int xbox;       // rows per activation TMA box (multiple of 16)
@@ -307,7 +308,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if (!gemm_tile(p, t_tiles, lin, t)) break;
         const int buf = tile_it & 1;
         const int nbox = (t.n + p.xbox - 1) / p.xbox;
-        const uint32_t idesc = ptx::umma_idesc_bf16_m128((uint32_t)(nbox * p.xbox));
+        const uint32_t idesc = p.fp16 ? ptx::umma_idesc_f16_m128((uint32_t)(nbox * p.xbox))
+                                      : ptx::umma_idesc_bf16_m128((uint32_t)(nbox * p.xbox));
         if (!ptx::mbar_wait(tempty_bar(buf), ((tile_it >> 1) & 1) ^ 1, abort_flag, 200 + buf)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * p.xrows_max);
@@ -438,7 +440,14 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       } else if (!SWIGLU) {
         const int f = t.wt * GEMM_WTILE + q * 32 + lane;
         const bool fvalid = f < p.n_w;
-        const float bias = (p.bias && fvalid) ? bf2f(p.bias[f]) : 0.f;
+        const float bias = !(p.bias && fvalid) ? 0.f
+                           : p.fp16     ? __half2float(reinterpret_cast<const __half*>(p.bias)[f])
+                                        : bf2f(p.bias[f]);
+        // rounds to the 16-bit output type (bf16, or fp16 for fp16 operands) and returns the bits
+        auto cvt16 = [&](float v) -> unsigned short {
+          if (p.fp16) return __half_as_ushort(__float2half_rn(v));
+          return __bfloat16_as_ushort(f2bf(v));
+        };
         // bf16 output whose rows allow 16-byte stores: each warp turns its 32 features x 16 tokens around in
         // shared memory, so that a lane stores eight consecutive features of one token (16 bytes) and one
         // instruction covers eight token rows, instead of one 2-byte store per (feature, token).
@@ -453,7 +462,8 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             ptx::tmem_ld16(taddr + c0, r);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) stg[j * 32 + lane] = f2bf(__uint_as_float(r[j]) + bias);
+            for (int j = 0; j < 16; ++j)
+              reinterpret_cast<unsigned short*>(stg)[j * 32 + lane] = cvt16(__uint_as_float(r[j]) + bias);
             __syncwarp();
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -479,7 +489,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
                 if (p.out_f32)
                   reinterpret_cast<float*>(p.out)[o] = v;
                 else
-                  reinterpret_cast<__nv_bfloat16*>(p.out)[o] = f2bf(v);
+                  reinterpret_cast<unsigned short*>(p.out)[o] = cvt16(v);
               }
             }
           }
@@ -549,7 +559,7 @@ gemm_ws_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 // 2-D bf16 tensor [rows, cols] with `row_stride` elements between rows; box = 64 cols x box_rows,
 // 128-byte swizzle.  Out-of-range elements read as zero.
 inline int make_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
-                        uint32_t box_rows) {
+                        uint32_t box_rows, bool fp16 = false) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (!enc) return B200_ERR_DRIVER;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride * 2) % 16 || box_rows == 0 || box_rows > 256)
@@ -558,9 +568,9 @@ inline int make_tmap_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
   cuuint64_t strides[1] = {row_stride * 2};
   cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r = enc(m, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_DRIVER;
 }
 
@@ -675,10 +685,10 @@ extern "C" int b200_gemm_f32_from_bf16(const void* x, const void* w, void* out, 
 
 // out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N], added in fp32 before the cast).
 // x rows are `x_row_stride` elements apart, w rows `w_row_stride`, out rows `out_row_stride`.
-extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, long long T, int N,
-                              int K, long long x_row_stride, long long w_row_stride, long long out_row_stride,
-                              int out_dtype /*0 = bf16, 1 = f32*/, void* stream) {
-  using namespace b200;
+namespace b200 {
+inline int gemm_dense_16bit(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
+                            long long x_row_stride, long long w_row_stride, long long out_row_stride, int out_dtype,
+                            bool fp16, void* stream) {
   if (!x || !w || !out || T < 0 || N <= 0 || K <= 0 || (out_dtype != 0 && out_dtype != 1)) return B200_ERR_ARG;
   if (K % 8 != 0 || x_row_stride % 8 != 0 || w_row_stride % 8 != 0) return B200_ERR_SHAPE;
   if (T == 0) return B200_OK;
@@ -721,12 +731,30 @@ extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, vo
   p.bias = (const __nv_bfloat16*)bias;
   p.row_scale = nullptr;
   p.w_policy = p.dense_t_tiles == 1 ? ptx::kEvictFirst : ptx::kEvictNormal;
+  p.fp16 = fp16 ? 1 : 0;
   CUtensorMap tw, tx;
-  int rc = make_tmap_2d(&tw, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_row_stride, GEMM_WTILE);
+  int rc = make_tmap_2d(&tw, w, (uint64_t)N, (uint64_t)K, (uint64_t)w_row_stride, GEMM_WTILE, fp16);
   if (rc) return rc;
-  rc = make_tmap_2d(&tx, x, (uint64_t)T, (uint64_t)K, (uint64_t)x_row_stride, (uint32_t)p.xbox);
+  rc = make_tmap_2d(&tx, x, (uint64_t)T, (uint64_t)K, (uint64_t)x_row_stride, (uint32_t)p.xbox, fp16);
   if (rc) return rc;
   return gemm_launch<GEMM_PLAIN>(tw, tx, p, (long long)p.w_tiles * p.dense_t_tiles, (cudaStream_t)stream);
+}
+}  // namespace b200
+
+extern "C" int b200_gemm_bf16(const void* x, const void* w, const void* bias, void* out, long long T, int N,
+                              int K, long long x_row_stride, long long w_row_stride, long long out_row_stride,
+                              int out_dtype /*0 = bf16, 1 = f32*/, void* stream) {
+  return b200::gemm_dense_16bit(x, w, bias, out, T, N, K, x_row_stride, w_row_stride, out_row_stride, out_dtype, false,
+                                stream);
+}
+
+// The same GEMM on fp16 tensors (the reference's matmul_persistent serves bf16, fp16 and fp32,
+// batch_invariant_ops.py:181-189): fp32 accumulation in the same K order, bias added in fp32, one rounding to fp16.
+extern "C" int b200_gemm_f16(const void* x, const void* w, const void* bias, void* out, long long T, int N, int K,
+                             long long x_row_stride, long long w_row_stride, long long out_row_stride,
+                             int out_dtype /*0 = f16, 1 = f32*/, void* stream) {
+  return b200::gemm_dense_16bit(x, w, bias, out, T, N, K, x_row_stride, w_row_stride, out_row_stride, out_dtype, true,
+                                stream);
 }
 
 namespace b200 {
