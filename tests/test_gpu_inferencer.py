@@ -177,3 +177,49 @@ def test_hf_module_through_the_inferencer_matches_stage_model():
     print(f"HF module vs native stage through the Inferencer: max |dlogit| = {d:.4f}")
     assert d < 0.08
     assert (hf[0][1] - st[0][1]).abs().max().item() < 0.05 or not torch.equal(hf[0][0], st[0][0])
+
+
+def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
+    """`HFModel(hf_model, pp_info)` slices a stock HF module tree the way the reference's `_apply_pp` does
+    (missing layers pass their input on, embedding on the first rank, norm + lm_head on the last); two such ranks
+    chained in one process give the single-rank bits (reference: tests/test_inferencer.py:180-297)."""
+    transformers = pytest.importorskip("transformers")
+    import copy
+
+    import vexact_b200 as vb
+    from vexact_b200.attention import register_attention_functions
+    from vexact_b200.config import PPInfo
+    from vexact_b200.inferencer import HFModel, Inferencer
+    from vexact_b200.models import shape_from_hf_config
+
+    register_attention_functions()
+    cfg = transformers.Qwen3Config(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                   num_hidden_layers=4, vocab_size=1024, intermediate_size=768,
+                                   tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
+                                   max_position_embeddings=4096)
+    cfg._attn_implementation = "fa-invariant"
+    with torch.device(DEV):
+        model = transformers.Qwen3ForCausalLM(cfg).to(BF).eval()
+    g = torch.Generator(device=DEV).manual_seed(9)
+    with torch.no_grad():
+        for name, p in sorted(model.named_parameters()):
+            p.normal_(0.0, 0.05, generator=g)
+            if "norm" in name:
+                p.add_(1.0)
+    shape = shape_from_hf_config(cfg)
+    econf = _config(shape, eager=True)
+    econf.model.hf_config = cfg
+    try:
+        one = _run([Inferencer(HFModel(copy.deepcopy(model)), econf, PPInfo(1, 0), None, torch.device(DEV),
+                               enable_batch_invariant=True)], steps=3)
+        lo = _Loopback()
+        ranks = [Inferencer(HFModel(copy.deepcopy(model), PPInfo(2, r)), econf, PPInfo(2, r), lo, torch.device(DEV),
+                            enable_batch_invariant=True) for r in range(2)]
+        assert ranks[0].model.layer_ids == [0, 1] and ranks[1].model.layer_ids == [2, 3]
+        two = _run(ranks, steps=3)
+    finally:
+        vb.disable_batch_invariant_mode()
+        torch.use_deterministic_algorithms(False)
+    for step, (a, b) in enumerate(zip(one, two)):
+        for x, y, what in zip(a, b, ("tokens", "logprobs", "logits")):
+            assert torch.equal(x, y), f"step {step}: two HF pipeline ranks differ from one in {what}"

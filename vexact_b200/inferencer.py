@@ -546,26 +546,65 @@ class StageModel:
     __call__ = forward
 
 
-class HFModel:
-    """An HF `*ForCausalLM` module behind the same forward keywords (single pipeline stage): the module
-    runs on this library's operators through `enable_batch_invariant_mode()`, the registered attention
-    function and `register_models()`.  The reference's wrapper for this is `TransformersForCausalLM`
-    (model_loader.py:218); its pipeline slicing is what `StageModel` does natively."""
+class PPMissingLayer(torch.nn.Module):
+    """Stands in for a module that lives on another pipeline rank: hands its first argument on
+    (model_loader.py:205-215)."""
 
-    def __init__(self, hf_model):
+    attention_type = "full_attention"
+
+    def forward(self, *args, **kwargs):
+        return args[0] if args else next(iter(kwargs.values()))
+
+
+class HFModel:
+    """An HF `*ForCausalLM` module behind the same forward keywords: the module runs on this library's
+    operators through `enable_batch_invariant_mode()`, the registered attention function and
+    `register_models()`.  The reference's wrapper for this is `TransformersForCausalLM` (model_loader.py:218-282)
+    and its pipeline plan `ModelCreator._apply_pp` (:346-400): with `pp_info` of more than one rank the decoder
+    layers outside `get_pp_indices(...)` become `PPMissingLayer`s, the embedding stays on the first rank (and on
+    the last one when the word embeddings are tied), the final norm and lm_head on the last; later ranks take the
+    previous rank's hidden states as `inputs_embeds`."""
+
+    def __init__(self, hf_model, pp_info=None):
         self.hf_model = hf_model
         self.config = hf_model.config
+        self.pp_rank = 0 if pp_info is None else pp_info.pp_rank
+        self.pp_size = 1 if pp_info is None else pp_info.pp_size
+        s0, s1 = get_pp_indices(self.config.num_hidden_layers, self.pp_rank, self.pp_size)
+        self.layer_ids = list(range(s0, s1))       # the layers whose KV cache this rank keeps
+        if self.pp_size > 1:
+            self._apply_pp()
+
+    def _apply_pp(self):
+        base = self.hf_model.model
+        first, last = self.pp_rank == 0, self.pp_rank == self.pp_size - 1
+        if not (first or (getattr(self.config, "tie_word_embeddings", False) and last)):
+            base.embed_tokens = PPMissingLayer()
+        s0, s1 = get_pp_indices(self.config.num_hidden_layers, self.pp_rank, self.pp_size)
+        for i in range(len(base.layers)):
+            if not (s0 <= i < s1):
+                base.layers[i] = PPMissingLayer()
+        if not last:
+            base.norm = PPMissingLayer()
+            self.hf_model.lm_head = PPMissingLayer()
 
     def eval(self):
         self.hf_model.eval()
         return self
 
     def forward(self, input_ids=None, intermediate_tensors=None, position_ids=None, **_unused) -> StageOutput:
-        if intermediate_tensors is not None and input_ids is None:
-            raise NotImplementedError("an HF module runs as a single stage; use StageModel for pipeline ranks")
-        out = self.hf_model(input_ids=input_ids, position_ids=position_ids, use_cache=False,
-                            output_hidden_states=True, return_dict=True)
-        return StageOutput(hidden_states=out.hidden_states[-1], logits=out.logits)
+        if self.pp_rank > 0:
+            assert intermediate_tensors is not None, "a later pipeline rank runs on the previous rank's hidden states"
+            out = self.hf_model.model(input_ids=None, inputs_embeds=intermediate_tensors, position_ids=position_ids,
+                                      use_cache=False, return_dict=True)
+        else:
+            assert input_ids is not None
+            out = self.hf_model.model(input_ids=input_ids, position_ids=position_ids, use_cache=False,
+                                      return_dict=True)
+        hidden = out.last_hidden_state
+        if self.pp_rank != self.pp_size - 1:
+            return StageOutput(hidden_states=hidden, logits=None)
+        return StageOutput(hidden_states=hidden, logits=self.hf_model.lm_head(hidden))
 
     __call__ = forward
 
