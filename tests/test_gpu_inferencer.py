@@ -217,9 +217,15 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
                             enable_batch_invariant=True) for r in range(2)]
         assert ranks[0].model.layer_ids == [0, 1] and ranks[1].model.layer_ids == [2, 3]
         two = _run(ranks, steps=3)
+        # the same module replayed from captured bucket graphs (reference: tests/test_inferencer.py:301-595)
+        gconf = _config(shape, eager=False)
+        gconf.model.hf_config = cfg
+        graph = _run([Inferencer(HFModel(copy.deepcopy(model)), gconf, PPInfo(1, 0), None, torch.device(DEV),
+                                 enable_batch_invariant=True)], steps=3)
     finally:
         vb.disable_batch_invariant_mode()
         torch.use_deterministic_algorithms(False)
-    for step, (a, b) in enumerate(zip(one, two)):
-        for x, y, what in zip(a, b, ("tokens", "logprobs", "logits")):
+    for step, (a, b, c) in enumerate(zip(one, two, graph)):
+        for x, y, z, what in zip(a, b, c, ("tokens", "logprobs", "logits")):
             assert torch.equal(x, y), f"step {step}: two HF pipeline ranks differ from one in {what}"
+            assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
