@@ -229,3 +229,53 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
         for x, y, z, what in zip(a, b, c, ("tokens", "logprobs", "logits")):
             assert torch.equal(x, y), f"step {step}: two HF pipeline ranks differ from one in {what}"
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
+
+
+def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise():
+    """What the engine promises the trainer (reference: tests/scripts/verify_logits_vs_native_hf.py with
+    --rtol 0 --atol 0): the logits a request got at decode step k, batched with other requests and running on
+    cached keys, are the bits a fresh forward over its whole sequence (prompt + the k tokens generated so far)
+    gives at the last position.  Stock HF module under the mode switch, three requests, three decode steps."""
+    transformers = pytest.importorskip("transformers")
+    import vexact_b200 as vb
+    from vexact_b200.attention import register_attention_functions
+    from vexact_b200.config import PPInfo
+    from vexact_b200.inferencer import HFModel, Inferencer
+    from vexact_b200.models import shape_from_hf_config
+
+    register_attention_functions()
+    cfg = transformers.Qwen3Config(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                   num_hidden_layers=3, vocab_size=1024, intermediate_size=768,
+                                   tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
+                                   max_position_embeddings=4096)
+    cfg._attn_implementation = "fa-invariant"
+    with torch.device(DEV):
+        model = transformers.Qwen3ForCausalLM(cfg).to(BF).eval()
+    g = torch.Generator(device=DEV).manual_seed(13)
+    with torch.no_grad():
+        for name, p in sorted(model.named_parameters()):
+            p.normal_(0.0, 0.05, generator=g)
+            if "norm" in name:
+                p.add_(1.0)
+    shape = shape_from_hf_config(cfg)
+    econf = _config(shape, eager=True)
+    econf.model.hf_config = cfg
+    steps = 4
+    try:
+        rollout = _run([Inferencer(HFModel(model), econf, PPInfo(1, 0), None, torch.device(DEV),
+                                   enable_batch_invariant=True)], steps=steps)
+        prompts = [r.input_ids_list for r in _requests(shape)]
+        for k in range(1, steps):
+            # every request's sequence so far, as one fresh prefill (a new inferencer: empty cache)
+            reqs = _requests(shape)
+            for i, r in enumerate(reqs):
+                ids = prompts[i] + [int(rollout[j][0][i]) for j in range(k)]
+                r.input_ids_list, r.tokens_this_step, r.num_computed_tokens = ids, len(ids), len(ids)
+            fresh = Inferencer(HFModel(model), econf, PPInfo(1, 0), None, torch.device(DEV),
+                               enable_batch_invariant=True)
+            out = fresh.infer(reqs, recv_infer_out=False)
+            assert torch.equal(out.logits, rollout[k][2]), f"decode step {k}: logits differ from the one-shot forward"
+            assert torch.equal(out.logprobs, rollout[k][1]) and torch.equal(out.token_ids, rollout[k][0])
+    finally:
+        vb.disable_batch_invariant_mode()
+        torch.use_deterministic_algorithms(False)
