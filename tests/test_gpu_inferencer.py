@@ -276,6 +276,21 @@ def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise():
             out = fresh.infer(reqs, recv_infer_out=False)
             assert torch.equal(out.logits, rollout[k][2]), f"decode step {k}: logits differ from the one-shot forward"
             assert torch.equal(out.logprobs, rollout[k][1]) and torch.equal(out.token_ids, rollout[k][0])
+        # chunked prefill (reference: scripts/run_batch_invariant_tests.sh, "random prompts + chunked prefill"):
+        # request 1's nine prompt tokens arrive as 4 + 5 while the other two requests prefill and then decode
+        reqs = _requests(shape)
+        reqs[1].tokens_this_step, reqs[1].num_computed_tokens = 4, 4
+        chunked = Inferencer(HFModel(model), econf, PPInfo(1, 0), None, torch.device(DEV), enable_batch_invariant=True)
+        first = chunked.infer(reqs, recv_infer_out=False)
+        assert torch.equal(first.logits[0], rollout[0][2][0]) and torch.equal(first.logits[2], rollout[0][2][2])
+        for i in (0, 2):                                   # requests 0 and 2 go on to their first decode step
+            r = reqs[i]
+            r.generated_tokens.append(int(first.token_ids[i]))
+            r.tokens_this_step, r.num_computed_tokens = 1, r.num_computed_tokens + 1
+        reqs[1].tokens_this_step, reqs[1].num_computed_tokens = 5, 9
+        second = chunked.infer(reqs, recv_infer_out=False)
+        assert torch.equal(second.logits[1], rollout[0][2][1]), "a prompt prefilled in two chunks differs from one shot"
+        assert torch.equal(second.logits[0], rollout[1][2][0]) and torch.equal(second.logits[2], rollout[1][2][2])
     finally:
         vb.disable_batch_invariant_mode()
         torch.use_deterministic_algorithms(False)
