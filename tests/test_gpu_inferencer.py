@@ -231,7 +231,8 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
 
 
-def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise():
+@pytest.mark.parametrize("moe", [False, True])
+def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe):
     """What the engine promises the trainer (reference: tests/scripts/verify_logits_vs_native_hf.py with
     --rtol 0 --atol 0): the logits a request got at decode step k, batched with other requests and running on
     cached keys, are the bits a fresh forward over its whole sequence (prompt + the k tokens generated so far)
@@ -244,13 +245,25 @@ def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise():
     from vexact_b200.models import shape_from_hf_config
 
     register_attention_functions()
-    cfg = transformers.Qwen3Config(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
-                                   num_hidden_layers=3, vocab_size=1024, intermediate_size=768,
-                                   tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
-                                   max_position_embeddings=4096)
+    if moe:      # the MoE block runs through apply_qwen3_moe_patches(): routing kernel + fused MoE
+        from vexact_b200.models import apply_qwen3_moe_patches
+
+        apply_qwen3_moe_patches()
+        cfg = transformers.Qwen3MoeConfig(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                          num_hidden_layers=2, vocab_size=1024, num_experts=16, num_experts_per_tok=4,
+                                          moe_intermediate_size=128, norm_topk_prob=True, tie_word_embeddings=False,
+                                          intermediate_size=256, decoder_sparse_step=1, mlp_only_layers=[],
+                                          rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=4096)
+        cls = transformers.Qwen3MoeForCausalLM
+    else:
+        cfg = transformers.Qwen3Config(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                       num_hidden_layers=3, vocab_size=1024, intermediate_size=768,
+                                       tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
+                                       max_position_embeddings=4096)
+        cls = transformers.Qwen3ForCausalLM
     cfg._attn_implementation = "fa-invariant"
     with torch.device(DEV):
-        model = transformers.Qwen3ForCausalLM(cfg).to(BF).eval()
+        model = cls(cfg).to(BF).eval()
     g = torch.Generator(device=DEV).manual_seed(13)
     with torch.no_grad():
         for name, p in sorted(model.named_parameters()):
