@@ -231,7 +231,7 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
 
 
-@pytest.mark.parametrize("moe", [False, True])
+@pytest.mark.parametrize("moe", [False, True, "deepseek_v3"])
 def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe):
     """What the engine promises the trainer (reference: tests/scripts/verify_logits_vs_native_hf.py with
     --rtol 0 --atol 0): the logits a request got at decode step k, batched with other requests and running on
@@ -245,7 +245,20 @@ def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe)
     from vexact_b200.models import shape_from_hf_config
 
     register_attention_functions()
-    if moe:      # the MoE block runs through apply_qwen3_moe_patches(): routing kernel + fused MoE
+    if moe == "deepseek_v3":   # MLA (keys 192 wide, values 128) + sigmoid-group routing + shared experts, patched
+        from vexact_b200.models import apply_deepseek_v3_patches
+
+        apply_deepseek_v3_patches()
+        cfg = transformers.DeepseekV3Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=4,
+                                            num_hidden_layers=2, vocab_size=1024, intermediate_size=256,
+                                            moe_intermediate_size=128, n_routed_experts=16, num_experts_per_tok=4,
+                                            n_shared_experts=1, kv_lora_rank=64, q_lora_rank=None,
+                                            qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                                            first_k_dense_replace=1, n_group=2, topk_group=1,
+                                            routed_scaling_factor=2.5, norm_topk_prob=True, tie_word_embeddings=False,
+                                            rms_norm_eps=1e-6, max_position_embeddings=4096)
+        cls = transformers.DeepseekV3ForCausalLM
+    elif moe:    # the MoE block runs through apply_qwen3_moe_patches(): routing kernel + fused MoE
         from vexact_b200.models import apply_qwen3_moe_patches
 
         apply_qwen3_moe_patches()
