@@ -231,7 +231,7 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
 
 
-@pytest.mark.parametrize("moe", [False, True, "deepseek_v3"])
+@pytest.mark.parametrize("moe", [False, True, "deepseek_v3", "qwen2"])
 def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe):
     """What the engine promises the trainer (reference: tests/scripts/verify_logits_vs_native_hf.py with
     --rtol 0 --atol 0): the logits a request got at decode step k, batched with other requests and running on
@@ -258,6 +258,12 @@ def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe)
                                             routed_scaling_factor=2.5, norm_topk_prob=True, tie_word_embeddings=False,
                                             rms_norm_eps=1e-6, max_position_embeddings=4096)
         cls = transformers.DeepseekV3ForCausalLM
+    elif moe == "qwen2":       # q/k/v projections with a bias (aten::addmm), no q/k norm
+        cfg = transformers.Qwen2Config(hidden_size=512, num_attention_heads=4, num_key_value_heads=2,
+                                       num_hidden_layers=3, vocab_size=1024, intermediate_size=768,
+                                       tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
+                                       max_position_embeddings=4096)
+        cls = transformers.Qwen2ForCausalLM
     elif moe:    # the MoE block runs through apply_qwen3_moe_patches(): routing kernel + fused MoE
         from vexact_b200.models import apply_qwen3_moe_patches
 
