@@ -280,3 +280,59 @@ def test_pipeline_ring_where_every_stage_sends_before_it_receives(world):
             errs.append("a rank did not finish in time (a send blocked on its receiver?)")
     assert not errs, "\n".join(errs)
     assert all(p.exitcode == 0 for p in procs)
+
+
+def _replica_worker(rank, world, pp, port, fail_q):
+    """torch.distributed belongs to somebody else (a trainer's world of `world` ranks); the messager finds its
+    replica's ring inside it (pp_messager.py:62-87 of the reference)."""
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import torch.distributed as dist
+
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from vexact_b200.config import PPInfo
+        from vexact_b200.pp_messager import InferencerOutput, PPMessager
+
+        replica, pp_rank = rank // pp, rank % pp
+        m = PPMessager(PPInfo(pp, pp_rank), None, torch.device("cpu"))
+        H, T, S, W = 32, 6, 3, 2
+        mine = _ctx(T + replica, S, W, H, first=True)            # every replica sends its own content
+        if pp_rank == 0:
+            m.send_gen_ctx(mine)
+            got = m.recv_infer_out()
+            assert torch.equal(got.token_ids, torch.arange(S) + 100 * replica)
+        else:
+            got = m.recv_gen_ctx()
+            _same(got, mine)                                     # not another replica's message
+            m.send_infer_out(InferencerOutput(token_ids=torch.arange(S) + 100 * replica, logits=torch.empty(0),
+                                              logprobs=torch.zeros(S)))
+        m.flush()
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception as e:
+        import traceback
+
+        fail_q.put(f"rank {rank}: {e}\n{traceback.format_exc()}")
+        raise
+
+
+def test_two_replicas_inside_one_world():
+    world, pp = 4, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_replica_worker, args=(r, world, pp, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    errs = []
+    while not q.empty():
+        errs.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append("a rank did not finish in time")
+    assert not errs, "\n".join(errs)
+    assert all(p.exitcode == 0 for p in procs)
