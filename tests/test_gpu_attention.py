@@ -349,3 +349,58 @@ def test_packed_varlen_forward_equals_paged_prefill_bitwise(vb):
         out, _ = vb.flash_attn_varlen_func(qq, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
                                            max_seqlen_k=max(lens), causal=True)
         out.float().sum().backward()
+
+
+def test_flex_key_paged_gives_the_other_keys_bits_and_packed_one_sequence(vb):
+    """`attn_impl="flex"` (reference flex_attention.py:280): with a paged context it is the same store + paged
+    call as the other keys (same bits); with a packed context it serves one sequence whose q_len queries sit
+    at the end of context_len keys, and gives the paged path's bits for the same tokens."""
+    hq, hkv, d, page = 16, 8, 128, 16
+    past, new = 45, 19
+    L = past + new
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(1, hq, new, d, generator=g).to(BF).cuda()
+    k_all = torch.randn(1, hkv, L, d, generator=g).to(BF).cuda()
+    v_all = torch.randn(1, hkv, L, d, generator=g).to(BF).cuda()
+    mod = torch.nn.Module()
+    mod.layer_idx = 0
+    blocks = [3, 0, 2, 4]
+    ptab = torch.tensor([blocks], dtype=torch.int32).cuda()
+    outs = {}
+    for name, fn in (("flash", vb.flash_attention_forward), ("flex", vb.flex_attention_forward)):
+        kc = {0: torch.zeros(5, page, hkv, d, dtype=BF).cuda()}
+        vc = {0: torch.zeros(5, page, hkv, d, dtype=BF).cuda()}
+        past_slots = torch.tensor(ops.slot_mapping([blocks], [0], [past], page)).cuda()
+        vb.store_kvcache(k_all[0, :, :past].transpose(0, 1).contiguous(), v_all[0, :, :past].transpose(0, 1).contiguous(),
+                         kc[0], vc[0], past_slots)
+        slots = torch.tensor(ops.slot_mapping([blocks], [past], [new], page)).cuda()
+        vb.set_kv_cache_context(is_paged_attn=True, key_cache=kc, value_cache=vc, block_tables=ptab,
+                                context_lens=torch.tensor([L], dtype=torch.int32).cuda(), slot_mapping=slots,
+                                query_start_loc=torch.tensor([0, new], dtype=torch.int32).cuda(), max_seqlen_q=new)
+        out, w = fn(mod, q, k_all[:, :, past:], v_all[:, :, past:], None, scaling=d ** -0.5)
+        assert w is None and out.shape == (new, hq, d)
+        outs[name] = out
+    assert torch.equal(outs["flash"], outs["flex"])
+
+    # Packed context: the whole key sequence is handed over, with keys past context_len that must stay unseen.
+    pad = 7
+    k_pad = torch.cat([k_all, torch.full((1, hkv, pad, d), 50.0, dtype=BF).cuda()], dim=2)
+    v_pad = torch.cat([v_all, torch.full((1, hkv, pad, d), 50.0, dtype=BF).cuda()], dim=2)
+    vb.set_kv_cache_context(is_paged_attn=False, context_lens=torch.tensor([L], dtype=torch.int32).cuda(),
+                            query_start_loc=torch.tensor([0, new], dtype=torch.int32).cuda())
+    packed, w = vb.flex_attention_forward(mod, q, k_pad, v_pad, None, scaling=d ** -0.5)
+    assert w is None and torch.equal(packed, outs["flash"])
+    # fp32 statement of the reference's mask (flex_attention.py:104-120): kv_idx <= offset + q_idx, kv_idx < context_len
+    qf, kf, vf = q[0].float(), k_pad[0].float().repeat_interleave(hq // hkv, 0), v_pad[0].float().repeat_interleave(hq // hkv, 0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * d ** -0.5
+    qi = torch.arange(new).cuda()[:, None] + past
+    ki = torch.arange(L + pad).cuda()[None, :]
+    s = s.masked_fill(~((ki <= qi) & (ki < L)), float("-inf"))
+    ref = torch.einsum("hqk,hkd->qhd", torch.softmax(s, -1), vf)
+    torch.testing.assert_close(packed.float(), ref, rtol=2 ** -7, atol=3e-3)
+
+    # Several sequences packed into one row: the reference's mask is not meaningful there; this library refuses.
+    vb.set_kv_cache_context(is_paged_attn=False, context_lens=torch.tensor([10, 9], dtype=torch.int32).cuda(),
+                            query_start_loc=torch.tensor([0, 10, 19], dtype=torch.int32).cuda())
+    with pytest.raises(NotImplementedError):
+        vb.flex_attention_forward(mod, q, k_all[:, :, :new], v_all[:, :, :new], None, scaling=d ** -0.5)

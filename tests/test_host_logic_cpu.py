@@ -71,3 +71,21 @@ def test_seeded_noise_restatement_properties():
     assert torch.equal(q[0], osamp.seeded_exponential([7], [3], 4099)[0])    # and nothing else does
     assert torch.equal(q[0, :4096], osamp.seeded_exponential([7], [3], 4096)[0])
     assert abs(float(q.mean()) - 1.0) < 0.05
+
+
+def test_attention_keys_and_attn_impl_validation():
+    """The four `attn_impl` names of the reference (config.py:138) are accepted and registered with HF
+    (inferencer.py:51-55); anything else is a ValueError; `flex` refuses CUDA-graph capture elsewhere."""
+    from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+
+    from vexact_b200 import attention
+    from vexact_b200.config import ModelConfig
+
+    for name in ("fa-invariant", "fa-invariant-cute", "triton-invariant", "flex"):
+        assert ModelConfig(attn_impl=name).attn_impl == name
+    with pytest.raises(ValueError, match="attn_impl must be one of"):
+        ModelConfig(attn_impl="sdpa")
+    attention.register_attention_functions()
+    for name in ("fa-invariant", "fa-invariant-cute", "triton-invariant"):
+        assert ALL_ATTENTION_FUNCTIONS[name] is attention.flash_attention_forward
+    assert ALL_ATTENTION_FUNCTIONS["flex"] is attention.flex_attention_forward

@@ -28,6 +28,7 @@ from .batch_invariant_ops import (  # noqa: F401
 from .attention import flash_attention_forward, flash_attn_varlen_func, paged_attention  # noqa: F401
 from .attention import flash_attention_forward as flash_attention_forward_cute  # noqa: F401
 from .attention import flash_attention_forward as triton_flash_attention_forward  # noqa: F401
+from .attention import flex_attention_forward  # noqa: F401
 from .attention import flash_attn_varlen_func as triton_flash_attn_varlen_func  # noqa: F401
 from .fused_moe import fused_moe_forward, route_sigmoid_group_topk, route_softmax_topk  # noqa: F401
 from .kv_cache_context import (  # noqa: F401

@@ -6,6 +6,9 @@
 * `flash_attention_forward`: the HF `ALL_ATTENTION_FUNCTIONS` adapter of
   triton_invariant_attention.py:982 and flash_attention.py:26, which reads the
   thread-local KV-cache context, stores K/V and calls the paged kernel.
+* `flex_attention_forward`: the adapter behind the reference's fourth key, `flex`
+  (flex_attention.py:280): the same paged call, plus the packed (non-paged) form
+  for one sequence.
 """
 from __future__ import annotations
 
@@ -18,6 +21,8 @@ from . import _lib
 from .kv_cache_context import get_kv_cache_context, store_kvcache
 
 ATTENTION_KEYS = ("fa-invariant", "fa-invariant-cute", "triton-invariant")
+FLEX_KEY = "flex"
+VALID_ATTN_IMPLS = ATTENTION_KEYS + (FLEX_KEY,)   # vexact/config.py:138
 
 
 def _require_cuda_int32(name: str, t: torch.Tensor) -> None:
@@ -236,9 +241,64 @@ def flash_attention_forward(
     )
 
 
+def flex_attention_forward(
+    module: nn.Module,
+    query: torch.Tensor,
+    key: Optional[torch.Tensor],
+    value: Optional[torch.Tensor],
+    attention_mask: Optional[torch.Tensor],
+    scaling: float,
+    dropout: float = 0.0,
+    **kwargs,
+):
+    """The reference's `flex` attention key (flex_attention.py:280-407): (B, heads, q_len, d) in,
+    (B * q_len, heads, dv) out, None for weights.
+
+    Paged context: store the new K / V, then causal attention over the page table; the reference builds a
+    block mask over the physical slots for this (flex_attention.py:187-268), here it is the paged kernel,
+    so `flex` gives the bits of the other three keys.
+
+    Packed context (`is_paged_attn=False`): K / V are the whole key sequence of ONE sequence
+    (flex_attention.py:348-381 with the mask of :74-122: query i sits at absolute position
+    context_len - q_len + i and sees keys 0..that position, capped at context_len).  The reference's mask
+    for several sequences packed into one row compares a key's packed index with a query's position
+    inside its own sequence, which is only meaningful for the first of them; that form raises here."""
+    del attention_mask
+    ctx = get_kv_cache_context()
+    if ctx is None:
+        raise RuntimeError("KV cache context not set. Call set_kv_cache_context() before forward pass.")
+    if ctx.is_paged_attn:
+        return flash_attention_forward(module, query, key, value, None, scaling, dropout, **kwargs)
+    if key is None or value is None:
+        raise ValueError("packed flex attention needs the key and value tensors")
+    if dropout != 0.0:
+        raise NotImplementedError("dropout is not supported")
+    bsz, heads, q_len, head_dim = query.shape
+    if bsz != 1 or ctx.query_start_loc.numel() != 2 or ctx.context_lens.numel() != 1:
+        raise NotImplementedError("packed flex attention serves one sequence per call "
+                                  "(batch 1, query_start_loc of two entries)")
+    kv_len = key.shape[2]
+    if q_len > kv_len:
+        raise ValueError(f"packed flex attention: {q_len} queries but only {kv_len} keys")
+    q = query[0].transpose(0, 1)                     # (q_len, heads, d)
+    k = key[0].transpose(0, 1).contiguous()          # (kv_len, kv_heads, d)
+    v = value[0].transpose(0, 1).contiguous()
+    dev = query.device
+    zero = torch.zeros(1, device=dev, dtype=torch.int32)
+    # Keys past context_len are never visible (the mask's `kv_idx < context_lens` term); the length stays on
+    # the device, so nothing here waits for the GPU.
+    ctx_len = ctx.context_lens.to(torch.int32).reshape(1).clamp(max=kv_len)
+    cu_k = torch.cat([zero, ctx_len])
+    cu_q = torch.tensor([0, q_len], device=dev, dtype=torch.int32)
+    out, _ = flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_seqlen_q=q_len, max_seqlen_k=kv_len,
+                                    softmax_scale=scaling, causal=True)
+    return out, None
+
+
 def register_attention_functions() -> None:
-    """Install the adapter under the reference's attention keys (inferencer.py:51-55)."""
+    """Install the adapters under the reference's attention keys (inferencer.py:51-55)."""
     from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
 
     for key in ATTENTION_KEYS:
         ALL_ATTENTION_FUNCTIONS[key] = flash_attention_forward
+    ALL_ATTENTION_FUNCTIONS[FLEX_KEY] = flex_attention_forward

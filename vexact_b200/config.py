@@ -76,6 +76,11 @@ class ModelConfig:
     enforce_eager: bool = False
     use_fp32_logits: bool = False
 
+    def __post_init__(self):
+        valid_attn_impls = ["fa-invariant", "fa-invariant-cute", "triton-invariant", "flex"]   # config.py:138
+        if self.attn_impl not in valid_attn_impls:
+            raise ValueError(f"attn_impl must be one of {valid_attn_impls}, got '{self.attn_impl}'")
+
 
 @dataclass
 class EngineConfig:
