@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-/* Changes whenever an exported signature changes (currently 2). */
+/* Changes whenever an exported signature changes or an entry point is added (currently 4). */
 int b200_abi_version(void);
 
 /* Hash of the sources and compiler flags the binary was built from: the Python loader compares it with
@@ -313,6 +313,18 @@ int b200_swiglu_scale_strided(const void* gate, const void* up, const void* row_
  *      output of modeling_deepseek_v3.py:217). */
 int b200_moe_unpermute_reduce(const void* y, const void* scatter_index, const void* addend, void* out,
                               long long T, int topk, int H, void* stream);
+
+/* ---- vexact/batch_invariant_ops/group_gemm/kernel/moe.py:304 moe_scatter and :131 moe_gather as operators
+ *      over an index array the CALLER supplies (index [T, topk] int32, element strides given):
+ *      scatter: out[index[t, k]] = x[t] (any 2-byte element type; out [out_rows, H] contiguous);
+ *      gather:  out[t] = bf16(sum over k, ascending, of fp32(x[index[t, k]])) (x [x_rows, H] bf16 contiguous).
+ *      H a multiple of 8, 16-byte aligned rows.  An index outside the row count is skipped and reported through
+ *      the status word (code 2), where the reference has a device assert. */
+int b200_moe_scatter(const void* x, long long x_row_stride, const void* index_i32, long long index_stride_t,
+                     long long index_stride_k, void* out, long long out_rows, long long T, int topk, int H,
+                     void* stream);
+int b200_moe_gather(const void* x, long long x_rows, const void* index_i32, long long index_stride_t,
+                    long long index_stride_k, void* out, long long T, int topk, int H, void* stream);
 
 /* b200_moe_unpermute_reduce followed by b200_add_rmsnorm (the residual add and input RMSNorm the next
  * decoder layer starts with) in one launch, with that pair's arithmetic element for element:

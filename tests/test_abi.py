@@ -27,7 +27,7 @@ def test_ctypes_signatures_cover_header(lib):
     from vexact_b200 import _lib
 
     assert sorted(_lib.SIGNATURES) == _declared_symbols()
-    assert lib.b200_abi_version() == _lib.ABI_VERSION == 3
+    assert lib.b200_abi_version() == _lib.ABI_VERSION == 4
 
 
 def test_argument_validation_without_gpu(lib):

@@ -288,3 +288,89 @@ def test_routing_of_nan_rows_stays_in_range():
     assert torch.equal(sel_c, sel[[0, 2, 4]])
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+def test_group_gemm_operators_under_the_reference_names(vb):
+    """`expert_histogram`, `moe_scatter`, `group_gemm_same_nk`, `moe_gather` (reference group_gemm/kernel/moe.py:52,
+    :304, :131; group_gemm.py:156) one at a time, chained as FusedMoeExpertFunction.forward chains them
+    (fused_moe.py:24-111): index and copy steps bit-exact, the GEMM equal to the dense GEMM's bits per expert,
+    the chain equal to `fused_moe_forward` up to the activation's rounding."""
+    from vexact_b200 import group_gemm as gg
+
+    T, E, k, H, I = 70, 16, 4, 256, 128
+    hidden, gate_up, down, sel, rw = _moe_case(T, E, k, H, I, seed=11)
+    x, sel_d, rw_d = hidden.cuda(), sel.cuda(), rw.cuda()
+    w1, w2, w3 = gate_up[:, :I].contiguous().cuda(), gate_up[:, I:].contiguous().cuda(), down.cuda()
+
+    splits = gg.expert_histogram(sel_d, E)
+    assert splits.dtype == torch.int32
+    assert torch.equal(splits.cpu().long(), torch.bincount(sel.flatten(), minlength=E))
+    assert torch.equal(gg.expert_histogram(sel_d.int(), E), splits)
+
+    scatter_index = sel_d.flatten().argsort(stable=True).argsort().int().view(sel_d.shape)   # fused_moe.py:43
+    cu, a_idx, scatter_ours = vb.fused_moe.build_moe_indices(sel_d, E)
+    assert torch.equal(scatter_ours, scatter_index)
+
+    scattered = gg.moe_scatter(x, scatter_index)
+    assert torch.equal(scattered, x[a_idx.long()])
+    assert torch.equal(gg.moe_scatter(x.half(), scatter_index.long()), x.half()[a_idx.long()])   # fp16 rows, int64 index
+
+    cumsum_t = torch.cumsum(splits, dim=0)
+    fc1_1 = gg.group_gemm_same_nk(a=scattered, b=w1, cumsum_M=cumsum_t, max_M=scattered.shape[0], transpose_b=True)
+    fc1_2 = gg.group_gemm_same_nk(a=scattered, b=w2, cumsum_M=cumsum_t, max_M=scattered.shape[0], transpose_b=True)
+    bounds = [0] + cumsum_t.tolist()
+    for e in range(E):          # a token's dot products do not depend on the tile it sits in: the dense GEMM's bits
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi > lo:
+            assert torch.equal(fc1_1[lo:hi], vb.matmul_persistent(scattered[lo:hi], w1[e].t()))
+    ref32 = torch.cat([scattered[bounds[e]:bounds[e + 1]].float() @ w2[e].float().t() for e in range(E)])
+    torch.testing.assert_close(fc1_2.float(), ref32, rtol=2 ** -7, atol=2 ** -7 * ref32.abs().max().item())
+
+    gate_w = torch.empty(T * k, 1, dtype=BF, device="cuda")
+    gate_w[scatter_index.flatten().long()] = rw_d.reshape(-1, 1)                               # fused_moe.py:84-86
+    weighted = torch.ops.aten.silu(fc1_1) * fc1_2 * gate_w
+    fc2 = gg.group_gemm_same_nk(a=weighted, b=w3, cumsum_M=cumsum_t, max_M=weighted.shape[0], transpose_b=True)
+
+    out = gg.moe_gather(fc2, scatter_index)
+    acc = torch.zeros(T, H, device="cuda")
+    for j in range(k):                                   # fp32 sum in k order, one rounding (moe.py:113-127)
+        acc += fc2[scatter_index[:, j].long()].float()
+    assert torch.equal(out, acc.to(BF))
+
+    fused = vb.fused_moe_forward(E, rw_d, sel_d, x, w1, w2, w3)
+    tol = 2 ** -6 * max(fused.float().abs().max().item(), 1e-3)
+    torch.testing.assert_close(out.float(), fused.float(), rtol=0, atol=tol)
+    assert (out == fused).float().mean() > 0.95
+
+    for call in (lambda: gg.group_gemm_same_nk(scattered, w1, cumsum_t, T * k, transpose_b=False),
+                 lambda: gg.group_gemm_same_mn(scattered, scattered, w1, cumsum_t, T * k),
+                 lambda: gg.moe_add_gather(fc2, fc2, scatter_index)):
+        with pytest.raises(NotImplementedError):
+            call()
+
+
+def test_scatter_and_gather_skip_and_report_an_index_out_of_range(vb):
+    from vexact_b200 import group_gemm as gg
+
+    T, k, H = 6, 2, 64
+    x = _seeded(T, H, seed=2).cuda()
+    index = torch.randperm(T * k, generator=torch.Generator().manual_seed(3)).int().view(T, k).cuda()
+    good = gg.moe_scatter(x, index)
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0
+    bad = index.clone()
+    bad[4, 1] = T * k + 5
+    gg.moe_scatter(x, bad)
+    torch.cuda.synchronize()
+    code, detail, _, _ = vb._lib.read_status()
+    assert (code, detail) == (2, 4 * k + 1)
+    rows = _seeded(T * k, H, seed=4).cuda()
+    bad[4, 1] = -3
+    out = gg.moe_gather(rows, bad)
+    torch.cuda.synchronize()
+    code, detail, _, _ = vb._lib.read_status()
+    assert (code, detail) == (2, 4 * k + 1)
+    assert torch.equal(out[4], rows[bad[4, 0].long()])          # the bad term contributes nothing
+    assert torch.equal(out[:4], gg.moe_gather(rows, index)[:4])
+    assert vb._lib.read_status()[0] == 0
+    assert good.shape == (T * k, H)

@@ -56,6 +56,8 @@ SIGNATURES = {
     "b200_swiglu_scale": [P, P, P, P, LL, I, P],
     "b200_swiglu_scale_strided": [P, P, P, P, LL, I, LL, P],
     "b200_moe_unpermute_reduce": [P, P, P, P, LL, I, I, P],
+    "b200_moe_scatter": [P, LL, P, LL, LL, P, LL, LL, I, I, P],
+    "b200_moe_gather": [P, LL, P, LL, LL, P, LL, I, I, P],
     "b200_moe_unpermute_add_rmsnorm": [P, P, P, P, P, P, P, LL, I, I, F, I, P],
 }
 
@@ -71,7 +73,7 @@ class B200Error(RuntimeError):
     pass
 
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 def _check_fresh(lib) -> None:

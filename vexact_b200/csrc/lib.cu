@@ -57,7 +57,7 @@ extern "C" int b200_status_read(int* host_out4, void* stream) {
 }
 
 // Bumped whenever an exported signature changes.
-extern "C" int b200_abi_version(void) { return 3; }
+extern "C" int b200_abi_version(void) { return 4; }
 
 // Hash of the sources and compiler flags this binary was built from (set by the build script);
 // the loader compares it with the sources beside it and refuses a stale library.

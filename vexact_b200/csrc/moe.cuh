@@ -529,6 +529,65 @@ moe_unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ y, const int* __re
   }
 }
 
+// The two row permutations as operators of their own, over an index array the caller supplies
+// (group_gemm/kernel/moe.py:304 moe_scatter, :131 moe_gather).  Unlike the kernels above, which only ever see
+// indices this library built, these check every index against the row count: a bad one is skipped and
+// reported through the status word (B200_STATUS_BAD_INDEX), where the reference has a device assert.
+// Rows are moved as 16-byte vectors, so the scatter serves any 2-byte element type.
+__global__ void __launch_bounds__(128)
+moe_scatter_checked_kernel(const uint4* __restrict__ x, long long x_stride_v, const int* __restrict__ index,
+                           long long index_stride_t, long long index_stride_k, uint4* __restrict__ out,
+                           long long out_rows, int hv, int topk) {
+  pdl_trigger();
+  pdl_wait();
+  const long long f = blockIdx.x;
+  const long long t = f / topk;
+  const int pos = index[t * index_stride_t + (f - t * topk) * index_stride_k];
+  if (pos < 0 || pos >= out_rows) {
+    if (threadIdx.x == 0) report_status(B200_STATUS_BAD_INDEX, (int)f);
+    return;
+  }
+  const uint4* src = x + t * x_stride_v;
+  uint4* dst = out + (long long)pos * hv;
+  for (int i = threadIdx.x; i < hv; i += 128) dst[i] = src[i];
+}
+
+// out[t] = bf16( sum_k fp32(x[index[t, k]]) ), k ascending.
+__global__ void __launch_bounds__(256)
+moe_gather_checked_kernel(const __nv_bfloat16* __restrict__ x, long long x_rows, const int* __restrict__ index,
+                          long long index_stride_t, long long index_stride_k, __nv_bfloat16* __restrict__ out,
+                          int H, int topk) {
+  pdl_trigger();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  for (int v = threadIdx.x; v < (H >> 3); v += 256) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      const int pos = index[t * index_stride_t + k * index_stride_k];
+      if (pos < 0 || pos >= x_rows) {
+        if (v == 0) report_status(B200_STATUS_BAD_INDEX, (int)(t * topk + k));
+        continue;
+      }
+      const uint4 r = reinterpret_cast<const uint4*>(x + (long long)pos * H)[v];
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a, b;
+        unpack_bf2(rp[j], a, b);
+        acc[2 * j] += a;
+        acc[2 * j + 1] += b;
+      }
+    }
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) op[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(out + t * H)[v] = o;
+  }
+}
+
 // h = bf16(bf16(bf16(silu(g)) * u) * s): the unfused tail of fc1 for split gate / up weights.
 __global__ void __launch_bounds__(256)
 swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
@@ -831,6 +890,36 @@ extern "C" int b200_moe_unpermute_reduce(const void* y, const void* scatter_inde
   launch_k(moe_unpermute_reduce_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)y, (const int*)scatter_index, (const __nv_bfloat16*)addend, (__nv_bfloat16*)out, H,
       topk);
+  return launch_status();
+}
+
+// out[index[t, k]] = x[t] for every (t, k): rows of a 2-byte element type, H a multiple of 8, x rows
+// x_row_stride elements apart (a multiple of 8), out [out_rows, H] contiguous, index [T, topk] i32 with the
+// given element strides.  An index outside [0, out_rows) is skipped and reported through the status word.
+extern "C" int b200_moe_scatter(const void* x, long long x_row_stride, const void* index_i32,
+                                long long index_stride_t, long long index_stride_k, void* out, long long out_rows,
+                                long long T, int topk, int H, void* stream) {
+  using namespace b200;
+  if (!x || !index_i32 || !out || T < 0 || topk <= 0 || H <= 0 || out_rows < 0) return B200_ERR_ARG;
+  if (H % 8 != 0 || x_row_stride % 8 != 0 || T * topk > 0x7fffffffLL) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  launch_k(moe_scatter_checked_kernel, dim3((unsigned)(T * topk)), dim3(128), 0, (cudaStream_t)stream,
+           (const uint4*)x, x_row_stride / 8, (const int*)index_i32, index_stride_t, index_stride_k, (uint4*)out,
+           out_rows, H / 8, topk);
+  return launch_status();
+}
+
+// out[t] = bf16(sum over k, ascending, of fp32(x[index[t, k]])): x [x_rows, H] bf16 contiguous, out [T, H].
+// An index outside [0, x_rows) contributes nothing and is reported through the status word.
+extern "C" int b200_moe_gather(const void* x, long long x_rows, const void* index_i32, long long index_stride_t,
+                               long long index_stride_k, void* out, long long T, int topk, int H, void* stream) {
+  using namespace b200;
+  if (!x || !index_i32 || !out || T < 0 || topk <= 0 || H <= 0 || x_rows < 0) return B200_ERR_ARG;
+  if (H % 8 != 0 || T > 0x7fffffffLL) return B200_ERR_SHAPE;
+  if (T == 0) return B200_OK;
+  launch_k(moe_gather_checked_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream,
+           (const __nv_bfloat16*)x, x_rows, (const int*)index_i32, index_stride_t, index_stride_k,
+           (__nv_bfloat16*)out, H, topk);
   return launch_status();
 }
 
