@@ -231,6 +231,56 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
 
 
+def test_attn_impl_flex_gives_the_other_keys_bits_and_refuses_graphs():
+    """`attn_impl="flex"` (reference inferencer.py:52, :108-109): a stock HF module whose attention key is `flex`
+    runs the paged kernel like the other three keys (same bits through the Inferencer, eager), and asking for
+    CUDA graphs with it raises the reference's RuntimeError."""
+    transformers = pytest.importorskip("transformers")
+    import copy
+
+    import vexact_b200 as vb
+    from vexact_b200.attention import register_attention_functions
+    from vexact_b200.config import PPInfo
+    from vexact_b200.inferencer import HFModel, Inferencer
+    from vexact_b200.models import shape_from_hf_config
+
+    register_attention_functions()
+    cfg = transformers.Qwen3Config(hidden_size=512, num_attention_heads=8, num_key_value_heads=2, head_dim=128,
+                                   num_hidden_layers=2, vocab_size=1024, intermediate_size=768,
+                                   tie_word_embeddings=False, rope_theta=1e6, rms_norm_eps=1e-6,
+                                   max_position_embeddings=4096)
+    outs = {}
+    try:
+        for key in ("triton-invariant", "flex"):
+            c = copy.deepcopy(cfg)
+            c._attn_implementation = key
+            with torch.device(DEV):
+                model = transformers.Qwen3ForCausalLM(c).to(BF).eval()
+            g = torch.Generator(device=DEV).manual_seed(13)
+            with torch.no_grad():
+                for name, p in sorted(model.named_parameters()):
+                    p.normal_(0.0, 0.05, generator=g)
+                    if "norm" in name:
+                        p.add_(1.0)
+            shape = shape_from_hf_config(c)
+            econf = _config(shape, eager=True)
+            econf.model.hf_config = c
+            econf.model.attn_impl = key
+            outs[key] = _run([Inferencer(HFModel(model), econf, PPInfo(1, 0), None, torch.device(DEV),
+                                         enable_batch_invariant=True)], steps=2)
+        gconf = _config(shape, eager=False)
+        gconf.model.hf_config = c
+        gconf.model.attn_impl = "flex"
+        with pytest.raises(RuntimeError, match="flex attention is not supported for CUDA graph"):
+            Inferencer(HFModel(model), gconf, PPInfo(1, 0), None, torch.device(DEV), enable_batch_invariant=True)
+    finally:
+        vb.disable_batch_invariant_mode()
+        torch.use_deterministic_algorithms(False)
+    for a, b in zip(outs["triton-invariant"], outs["flex"]):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+
+
 @pytest.mark.parametrize("moe", [False, True, "deepseek_v3", "qwen2"])
 def test_rollout_steps_equal_one_shot_prefill_of_the_same_sequences_bitwise(moe):
     """What the engine promises the trainer (reference: tests/scripts/verify_logits_vs_native_hf.py with

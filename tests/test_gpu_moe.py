@@ -374,3 +374,21 @@ def test_scatter_and_gather_skip_and_report_an_index_out_of_range(vb):
     assert torch.equal(out[:4], gg.moe_gather(rows, index)[:4])
     assert vb._lib.read_status()[0] == 0
     assert good.shape == (T * k, H)
+
+
+def test_expert_function_classes_take_the_reference_arguments(vb):
+    """`FusedMoeExpertFunction.apply` / `QuackFusedMoeExpertFunction.apply` (fused_moe.py:22, :295) with the
+    reference's seven positional arguments: the fused forward's bits; differentiating through them raises."""
+    from vexact_b200.fused_moe import FusedMoeExpertFunction, QuackFusedMoeExpertFunction
+
+    T, E, k, H, I = 33, 8, 2, 128, 64
+    hidden, gate_up, down, sel, rw = _moe_case(T, E, k, H, I, seed=21)
+    args = (E, rw.cuda(), sel.cuda(), hidden.cuda(), gate_up[:, :I].contiguous().cuda(),
+            gate_up[:, I:].contiguous().cuda(), down.cuda())
+    fused = vb.fused_moe_forward(*args)
+    assert torch.equal(FusedMoeExpertFunction.apply(*args), fused)
+    assert torch.equal(QuackFusedMoeExpertFunction.apply(*args), fused)
+    x = args[3].clone().requires_grad_(True)
+    out = FusedMoeExpertFunction.apply(E, args[1], args[2], x, *args[4:])
+    with pytest.raises(NotImplementedError):
+        out.float().sum().backward()

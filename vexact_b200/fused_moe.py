@@ -367,3 +367,22 @@ def fused_moe_forward(
         addend = addend.to(torch.bfloat16).reshape(T, H).contiguous()
     pending = PendingMoE(y, plan["scatter_index"], addend, T, k, H, orig_shape)
     return pending if defer_reduce else pending.finish()
+
+
+class FusedMoeExpertFunction(torch.autograd.Function):
+    """The reference's entry class (fused_moe.py:22; `QuackFusedMoeExpertFunction` :295 on sm_90 and newer) with
+    its positional arguments.  Forward only: the backward (dgrad / ragged-K wgrad grouped GEMMs) is the training
+    side's and raises."""
+
+    @staticmethod
+    def forward(ctx, num_experts, gate_weights, expert_index, hidden_states, fc1_1_weight, fc1_2_weight, fc2_weight):
+        return fused_moe_forward(num_experts, gate_weights, expert_index, hidden_states, fc1_1_weight, fc1_2_weight,
+                                 fc2_weight)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        raise NotImplementedError("the fused-MoE backward is not part of this library")
+
+
+QuackFusedMoeExpertFunction = FusedMoeExpertFunction
+_build_moe_indices = build_moe_indices

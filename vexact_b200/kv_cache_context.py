@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import threading
 from dataclasses import dataclass
-from typing import Optional
+from typing import Iterable, Optional
 
 import torch
 
@@ -75,6 +75,19 @@ def has_kv_cache_context() -> bool:
 def clear_kv_cache_context() -> None:
     if hasattr(_context_storage, "kv_cache_context"):
         del _context_storage.kv_cache_context
+
+
+@dataclass(frozen=True)
+class KVCacheInfo:
+    """What a KV cache is built from (kv_cache_context.py:36-46)."""
+
+    layer_idxs: Iterable[int]
+    num_kv_heads: int
+    head_dim: int
+    page_size: int
+    max_blocks: int
+    device: torch.device
+    dtype: torch.dtype = torch.bfloat16
 
 
 class KVCacheManager:
