@@ -222,13 +222,19 @@ def test_hf_module_split_over_two_pipeline_ranks_equals_one_rank_bitwise():
         gconf.model.hf_config = cfg
         graph = _run([Inferencer(HFModel(copy.deepcopy(model)), gconf, PPInfo(1, 0), None, torch.device(DEV),
                                  enable_batch_invariant=True)], steps=3)
+        # the reference's own wrapper class and constructor (model_loader.py:218): base model + lm_head + position
+        from vexact_b200.inferencer import TransformersForCausalLM
+        m = copy.deepcopy(model)
+        wrapped = _run([Inferencer(TransformersForCausalLM(m.model, m.lm_head, PPInfo(1, 0)), gconf, PPInfo(1, 0), None,
+                                   torch.device(DEV), enable_batch_invariant=True)], steps=3)
     finally:
         vb.disable_batch_invariant_mode()
         torch.use_deterministic_algorithms(False)
-    for step, (a, b, c) in enumerate(zip(one, two, graph)):
-        for x, y, z, what in zip(a, b, c, ("tokens", "logprobs", "logits")):
+    for step, (a, b, c, d) in enumerate(zip(one, two, graph, wrapped)):
+        for x, y, z, w, what in zip(a, b, c, d, ("tokens", "logprobs", "logits")):
             assert torch.equal(x, y), f"step {step}: two HF pipeline ranks differ from one in {what}"
             assert torch.equal(x, z), f"step {step}: the HF module replayed from a bucket graph differs from eager in {what}"
+            assert torch.equal(x, w), f"step {step}: TransformersForCausalLM differs from HFModel in {what}"
 
 
 def test_attn_impl_flex_gives_the_other_keys_bits_and_refuses_graphs():

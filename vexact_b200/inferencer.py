@@ -609,6 +609,42 @@ class HFModel:
     __call__ = forward
 
 
+class TransformersForCausalLM(torch.nn.Module):
+    """The reference's wrapper class under its own name and constructor (model_loader.py:218-276): the HF base
+    model and the lm_head as two modules plus the pipeline position.  Ranks after the first run on the previous
+    rank's hidden states (`intermediate_tensors` become `inputs_embeds`), ranks before the last return the hidden
+    states and no logits, the last rank applies the lm_head to the positions `logits_to_keep` selects (0 = all).
+    The pipeline slicing of the module tree is the caller's (the reference's `ModelCreator._apply_pp`, or
+    `HFModel(hf_model, pp_info)` here, which does both)."""
+
+    def __init__(self, model: torch.nn.Module, lm_head: torch.nn.Module, pp_info):
+        super().__init__()
+        self.model = model
+        self.lm_head = lm_head
+        self._pp_info = pp_info
+
+    def forward(self, input_ids=None, intermediate_tensors=None, inputs_embeds=None, attention_mask=None,
+                position_ids=None, use_cache=None, output_hidden_states=None, logits_to_keep=0, **kwargs):
+        from transformers.modeling_outputs import CausalLMOutputWithPast
+
+        if self._pp_info.pp_rank > 0:
+            assert intermediate_tensors is not None
+            input_ids, inputs_embeds = None, intermediate_tensors
+        else:
+            assert input_ids is not None
+            inputs_embeds = None
+        out = self.model(input_ids=input_ids, attention_mask=attention_mask, inputs_embeds=inputs_embeds,
+                         use_cache=use_cache, position_ids=position_ids, output_hidden_states=output_hidden_states,
+                         **kwargs)
+        if self._pp_info.pp_rank != self._pp_info.pp_size - 1:
+            return CausalLMOutputWithPast(loss=None, logits=None, past_key_values=None,
+                                          hidden_states=out.last_hidden_state, attentions=None)
+        keep = slice(-logits_to_keep, None) if isinstance(logits_to_keep, int) else logits_to_keep
+        logits = self.lm_head(out.last_hidden_state[:, keep, :])
+        return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=None, hidden_states=out.hidden_states,
+                                      attentions=None)
+
+
 class Inferencer:
     """One forward + token selection per scheduler step, with the pipeline send / receive choreography.
 
@@ -823,9 +859,13 @@ class Inferencer:
                 raise RuntimeError(f"Cuda graph is enabled but no captured descriptor can cover {num_seqs} sequences "
                                    f"and {total} tokens. Available descriptors: {list(self._cudagraph_mgr.graphs)}")
             self._prepare_input_buffers_from_gen_ctx(gen_ctx, desc)
-            with torch.cuda.nvtx.range("model_forward_cudagraph"):
-                return self._cudagraph_mgr.replay(desc)
+            return self._forward_cudagraph(desc)
         return self._forward_eager(gen_ctx)
+
+    @torch.inference_mode()
+    def _forward_cudagraph(self, graph_key):
+        with torch.cuda.nvtx.range("model_forward_cudagraph"):
+            return self._cudagraph_mgr.replay(graph_key)
 
     @torch.inference_mode()
     def _forward_eager(self, gen_ctx):
