@@ -127,6 +127,14 @@ int b200_sample_token(const void* logits, const void* noise_q_f32, void* tokens_
                       long long rows, int n, long long row_stride, long long q_row_stride, int dtype,
                       float temperature, int top_k, float top_p, void* stream);
 
+/* ---- vexact/inferencer/sampler.py:146-186 apply_top_k_top_p as an operator of its own: out[r, i] =
+ *      logits[r, i] / temperature where token i survives top-k (ties with the k-th value kept) and top-p
+ *      (ascending cumulative mass <= 1 - p masked, at least one kept), -inf elsewhere; fp32 [rows, n].
+ *      Same thresholds as b200_sample_token.  top_k <= 0 / top_p >= 1 switch the respective cut off. */
+int b200_apply_top_k_top_p(const void* logits, void* out_f32, long long rows, int n, long long row_stride,
+                           long long out_row_stride, int dtype, float temperature, int top_k, float top_p,
+                           void* stream);
+
 /* ---- modeling_qwen3_moe.py:128-134 routing + fused_moe.py:268-292 index math in two launches instead of three:
  *      b200_moe_route_plan_softmax_topk routes like b200_moe_route_softmax_topk and also gives every selected
  *      (token, expert) its rank inside the expert's group (an atomic counter per expert) and, from the last CTA to

@@ -165,3 +165,100 @@ def test_seeded_sampler_is_reproducible_per_request():
         s.batch_sample_token_and_logprob(logits, cfgs[:5] + [SimpleNamespace(**{**vars(cfgs[5]), "seed": None})], pos)
     with pytest.raises(ValueError):
         s.batch_sample_token_and_logprob(logits, cfgs, None)
+
+
+def test_mixed_seed_batch_and_missing_positions_are_rejected_before_any_compute():
+    """Reference tests/test_inferencer_sampling.py:88-98: CPU logits are enough, the errors come first."""
+    from types import SimpleNamespace as NS
+
+    from vexact_b200.sampler import Sampler
+
+    cfgs = [NS(do_sample=True, temperature=1.0, top_k=4, top_p=1.0, seed=None) for _ in range(2)]
+    cfgs[0].seed = 1234
+    with pytest.raises(ValueError, match="every request in the batch"):
+        Sampler().batch_sample_token(torch.randn(2, 16), cfgs, torch.arange(2))
+    cfgs[1].seed = 99
+    with pytest.raises(ValueError, match="sampling_positions must be set"):
+        Sampler().batch_sample_token(torch.randn(2, 16), cfgs)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch_size", [1, 96])
+@pytest.mark.parametrize("top_k", [0, 50, None])
+@pytest.mark.parametrize("top_p", [0, 0.9])
+def test_batch_sample_token_matches_the_step_by_step_form(batch_size, top_k, top_p):
+    """The reference's own sampler test (tests/test_inferencer_sampling.py:23-85) at its vocabulary size: temperature,
+    `apply_top_k_top_p`, softmax, one exponential_() draw, arg-max of probs / noise, written out step by step with
+    this library's `apply_top_k_top_p`, against `batch_sample_token` under the same torch seed."""
+    from types import SimpleNamespace as NS
+
+    from vexact_b200.sampler import Sampler
+
+    sampler = Sampler()
+    vocab = 151936
+    torch.manual_seed(7)
+    logits = torch.empty((batch_size, vocab), device="cuda").uniform_(-1.0, 1.0)
+    cfgs = [NS(do_sample=True, temperature=1.0, top_k=top_k, top_p=top_p, seed=None)] * batch_size
+
+    def step_by_step(x):
+        k = None if (top_k is None or int(top_k) <= 0) else int(top_k)
+        if not (float(top_p) > 0):
+            return x.argmax(dim=-1).view(-1)
+        kt = None if k is None else torch.full((x.shape[0],), k, device=x.device)
+        pt = torch.full((x.shape[0],), float(top_p), device=x.device)
+        masked = sampler.apply_top_k_top_p(x, kt, pt)
+        probs = torch.softmax(masked, dim=-1)
+        noise = torch.empty_like(probs).exponential_(1)
+        return torch.argmax(probs / noise, dim=-1)
+
+    torch.manual_seed(42)
+    torch.cuda.manual_seed_all(42)
+    want = step_by_step(logits.clone())
+    torch.manual_seed(42)
+    torch.cuda.manual_seed_all(42)
+    got = sampler.batch_sample_token(logits.clone(), cfgs)
+    torch.testing.assert_close(got, want, rtol=0, atol=0)
+
+
+@pytest.mark.gpu
+def test_apply_top_k_top_p_matches_the_sort_based_restatement():
+    """Masked logits against the CPU restatement of sampler.py:146-186.  Elements may differ only at the top-p
+    boundary: the restatement's fp32 running sum over the sorted row and this kernel's 2^-40 fixed-point masses
+    can place the cut a few elements apart, and a run of equal logits at the cut is kept whole here."""
+    from vexact_b200.sampler import Sampler
+
+    g = torch.Generator().manual_seed(5)
+    for rows, vocab, dtype, temp, k, p in [(4, 4096, torch.float32, 1.0, 40, None), (4, 4096, torch.float32, 1.0, None, 0.9),
+                                           (3, 32000, torch.float32, 1.0, 100, 0.8), (2, 151936, torch.bfloat16, 1.0, 0, 0.95),
+                                           (2, 129, torch.float32, 1.0, 129, 1.0)]:
+        x = (torch.randn(rows, vocab, generator=g) * 2.0).to(dtype)
+        kk = None if (k is None or k <= 0 or k >= vocab) else k
+        want = oracle_sampler.apply_top_k_top_p(x.float().clone(), kk, p)
+        got = Sampler().apply_top_k_top_p(x.cuda(), k, p).cpu()
+        assert got.dtype == torch.float32 and got.shape == x.shape
+        kept_g, kept_w = got > -float("inf"), want > -float("inf")
+        assert torch.equal(got[kept_g], x.float()[kept_g])               # kept values pass through unchanged
+        for r in range(rows):       # distinct logit values on which the two disagree (bf16 rows hold long equal runs)
+            values = x[r][kept_g[r] != kept_w[r]].float().unique()
+            assert values.numel() <= (0 if p is None else 8), (vocab, k, p, values.tolist())
+        if p is None or p >= 1.0:
+            assert torch.equal(got, want)
+    only_k = Sampler().apply_top_k_only(x.cuda(), torch.full((rows,), 5, device="cuda")).cpu()
+    assert torch.equal(only_k, oracle_sampler.apply_top_k_top_p(x.float().clone(), 5, None))
+
+
+@pytest.mark.gpu
+def test_seeded_sample_helper_equals_the_seeded_batch_call():
+    from types import SimpleNamespace as NS
+
+    from vexact_b200.sampler import Sampler
+
+    g = torch.Generator().manual_seed(8)
+    x = (torch.randn(5, 4096, generator=g) * 2.0).cuda()
+    seeds = [11, 22, 33, 44, 55]
+    pos = torch.tensor([3, 9, 100, 7, 7])
+    cfgs = [NS(do_sample=True, temperature=0.7, top_k=20, top_p=0.9, seed=s) for s in seeds]
+    want = Sampler().batch_sample_token(x, cfgs, pos)
+    masked = Sampler().apply_top_k_top_p(x / 0.7, 20, 0.9)
+    got = Sampler()._seeded_sample(masked, seeds, pos, 0.7)
+    assert torch.equal(got, want)

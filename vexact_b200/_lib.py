@@ -33,6 +33,7 @@ SIGNATURES = {
     "b200_greedy_logprob": [P, P, P, LL, I, LL, I, P],
     "b200_lm_head_greedy": [P, P, P, P, P, LL, I, I, LL, LL, P],
     "b200_sample_token": [P, P, P, P, LL, I, LL, LL, I, F, I, F, P],
+    "b200_apply_top_k_top_p": [P, P, LL, I, LL, LL, I, F, I, F, P],
     "b200_seeded_exponential": [P, P, P, LL, I, LL, P],
     "b200_gather_rows": [P, LL, LL, P, P, P, LL, I, P],
     "b200_moe_route_plan_softmax_topk": [P, I, LL, P, P, P, P, P, P, P, LL, I, I, I, I, I, P],

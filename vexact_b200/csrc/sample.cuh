@@ -37,13 +37,17 @@ struct SampleParams {
   float temperature, top_p;
   int top_k;
   bool vec;
+  float* masked_out;       // MASK form: fp32 [rows, n], the scaled logits with everything cut by top-k / top-p at -inf
+  long long out_stride;
 };
 
 // Digit layout of the three radix levels: bits 31..21, 20..10, 9..0.
 __device__ __forceinline__ int smp_shift(int level) { return level == 0 ? 21 : (level == 1 ? 10 : 0); }
 __device__ __forceinline__ int smp_bins(int level) { return level == 2 ? 1024 : 2048; }
 
-template <typename T>
+// MASK = true stops after the two thresholds and writes the masked logits (the reference's apply_top_k_top_p as
+// an operator of its own, sampler.py:146-186) instead of drawing a token.
+template <typename T, bool MASK = false>
 __global__ void __launch_bounds__(SMP_THREADS) sample_token_kernel(const SampleParams p) {
   pdl_trigger();
   pdl_wait();
@@ -56,7 +60,7 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_token_kernel(const SampleP
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n = p.n;
   const T* row = reinterpret_cast<const T*>(p.logits) + (long long)blockIdx.x * p.row_stride;
-  const float* qrow = p.q + (long long)blockIdx.x * p.q_stride;
+  const float* qrow = MASK ? nullptr : p.q + (long long)blockIdx.x * p.q_stride;
   const bool has_temp = p.temperature != 1.0f;
   auto scaled = [&](int i) {
     const float x = (float)row[i];
@@ -209,6 +213,15 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_token_kernel(const SampleP
   }
   const uint32_t key_min = key_k > key_p ? key_k : key_p;
 
+  if constexpr (MASK) {
+    float* orow = p.masked_out + (long long)blockIdx.x * p.out_stride;
+    for (int i = tid; i < n; i += SMP_THREADS) {
+      const float y = scaled(i);
+      orow[i] = smp_key(y) >= key_min ? y : -INFINITY;
+    }
+    return;
+  }
+
   // ---- argmax of exp(y - max) / q over the kept tokens (lowest index on ties)
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -285,12 +298,33 @@ extern "C" int b200_sample_token(const void* logits, const void* noise_q_f32, vo
   if (dtype != 0 && dtype != 1) return B200_ERR_ARG;
   const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
   SampleParams p{logits, (const float*)noise_q_f32, (long long*)tokens_i64, (float*)logprobs_f32, n, row_stride,
-                 q_row_stride, temperature, top_p, top_k, aligned && row_stride % (dtype == 0 ? 4 : 8) == 0};
+                 q_row_stride, temperature, top_p, top_k, aligned && row_stride % (dtype == 0 ? 4 : 8) == 0, nullptr, 0};
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == 0)
     launch_k(sample_token_kernel<float>, dim3((unsigned)rows), dim3(SMP_THREADS), 0, st, p);
   else
     launch_k(sample_token_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(SMP_THREADS), 0, st, p);
+  return launch_status();
+}
+
+// The masking step alone: out[r, i] = x[r, i] / temperature where the token survives top-k and top-p, -inf
+// elsewhere (fp32 [rows, n]); the thresholds are the ones b200_sample_token uses.  top_k <= 0 and top_p >= 1
+// switch the respective cut off.
+extern "C" int b200_apply_top_k_top_p(const void* logits, void* out_f32, long long rows, int n, long long row_stride,
+                                      long long out_row_stride, int dtype, float temperature, int top_k, float top_p,
+                                      void* stream) {
+  using namespace b200;
+  if (!logits || !out_f32 || rows < 0 || n <= 0 || !(temperature > 0.f) || (dtype != 0 && dtype != 1))
+    return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  SampleParams p{logits, nullptr, nullptr, nullptr, n, row_stride, 0, temperature, top_p, top_k,
+                 aligned && row_stride % (dtype == 0 ? 4 : 8) == 0, (float*)out_f32, out_row_stride};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == 0)
+    launch_k(sample_token_kernel<float, true>, dim3((unsigned)rows), dim3(SMP_THREADS), 0, st, p);
+  else
+    launch_k(sample_token_kernel<__nv_bfloat16, true>, dim3((unsigned)rows), dim3(SMP_THREADS), 0, st, p);
   return launch_status();
 }
 
