@@ -161,3 +161,51 @@ def test_fp16_matmul_and_batch_invariance(vb):
         assert torch.equal(vb.matmul_persistent(ad[:1], wd.t(), bd), outb[:1])
         if M > 8:
             assert torch.equal(vb.matmul_persistent(ad[5:8], wd.t(), bd), outb[5:8])
+
+
+def test_mm_under_the_mode_takes_any_layout(vb):
+    """Under the mode switch every aten::mm / addmm on CUDA tensors lands here, not only nn.Linear: a reduction
+    length that is no multiple of 8, a row-major right operand, operands sliced at an odd element offset.  The
+    reference's Triton kernel takes any strides (batch_invariant_ops.py:54-156); here such operands go through
+    zero-padded copies, which leaves every fp32 accumulation as it was: the padded-K result equals the result
+    for the same numbers laid out at K + pad with explicit zeros, and rows stay batch-invariant."""
+    a = _seeded(33, 77, seed=21).cuda()
+    b = _seeded(77, 50, seed=22).cuda()                     # row-major [K, N], K = 77
+    with vb.set_batch_invariant_mode(True):
+        c = torch.mm(a, b)
+        c1 = torch.mm(a[:1], b)
+        cb = torch.addmm(_seeded(50, seed=23).cuda(), a, b)
+    assert torch.equal(c[:1], c1)
+    a_pad = torch.nn.functional.pad(a, (0, 3))
+    b_pad = torch.nn.functional.pad(b, (0, 0, 0, 3))
+    assert torch.equal(c, vb.matmul_persistent(a_pad, b_pad))
+    _close_bf16(c.cpu(), ops.matmul(a.cpu(), b.cpu()), 77)
+    _close_bf16(cb.cpu(), ops.matmul(a.cpu(), b.cpu(), _seeded(50, seed=23)), 77)
+    big = _seeded(9 * 64 + 1, seed=24).cuda()
+    odd = big[1:].view(9, 64)                               # K fine, data pointer off by one element
+    w = _seeded(64, 32, seed=25).cuda()
+    assert torch.equal(vb.matmul_persistent(odd, w), vb.matmul_persistent(odd.clone(), w))
+
+
+def test_conv3d_under_the_mode_is_deterministic_and_batch_invariant(vb):
+    """Reference tests/batch_invariant_ops/test_torch_conv3d.py:50-115 (the Qwen3-VL patch embedding, cuDNN off):
+    ten identical runs, and sample 0 alone equal to sample 0 of the batch."""
+    import torch.nn.functional as F
+
+    cout, cin, kt, kh, kw, batch = 1024, 3, 2, 16, 16, 8
+    d, h, w = kt * 2, kh * 2, kw * 2
+    a = torch.linspace(-1.0, 1.0, batch * cin * d * h * w, dtype=BF, device="cuda").reshape(batch, cin, d, h, w)
+    weight = torch.linspace(-1.0, 1.0, cout * cin * kt * kh * kw, dtype=BF, device="cuda").reshape(cout, cin, kt, kh, kw)
+    bias = torch.linspace(-1.0, 1.0, cout, dtype=BF, device="cuda")
+    cudnn_was = torch.backends.cudnn.enabled
+    torch.backends.cudnn.enabled = False
+    try:
+        with vb.set_batch_invariant_mode(True):
+            out1 = F.conv3d(a, weight, bias=bias, stride=(kt, kh, kw))
+            for _ in range(10):
+                assert torch.equal(out1, F.conv3d(a, weight, bias=bias, stride=(kt, kh, kw)))
+            single = F.conv3d(a[:1], weight, bias=bias, stride=(kt, kh, kw))
+        assert torch.equal(single, out1[:1])
+    finally:
+        torch.backends.cudnn.enabled = cudnn_was
+        torch.use_deterministic_algorithms(False)

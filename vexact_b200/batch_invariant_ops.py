@@ -63,7 +63,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         if out_dtype not in (x.dtype, torch.float32):
             raise ValueError(f"unsupported output dtype {out_dtype}")
         if K % 8 or x2.stride(0) % 8 or weight.stride(0) % 8 or x2.data_ptr() % 16 or weight.data_ptr() % 16:
-            raise ValueError("16-bit matmul needs K and row strides that are multiples of 8 and 16-byte aligned data")
+            # The tensor maps want 16-byte rows.  Any other layout (an odd K from some aten::mm caller under the
+            # mode switch, a sliced view) goes through zero-padded copies: K grows to the next multiple of 8 and
+            # the extra products are exact zeros, so the fp32 accumulation of every output is unchanged.
+            K8 = (K + 7) // 8 * 8
+            x2 = torch.nn.functional.pad(x2, (0, K8 - K)) if K8 != K else x2.clone(memory_format=torch.contiguous_format)
+            weight = torch.nn.functional.pad(weight, (0, K8 - K)) if K8 != K else weight.clone(memory_format=torch.contiguous_format)
+            K = K8
         if bias is not None:
             assert bias.dim() == 1, "bias must be 1-D"
             bias = bias.to(x.dtype).contiguous()
