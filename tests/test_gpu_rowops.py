@@ -71,6 +71,13 @@ def test_mean_lastdim(vb):
     assert full.shape == (50, 4, 1)
     assert torch.equal(vb.mean_dim(x[:3], -1, keepdim=True), full[:3])
     torch.testing.assert_close(vb.mean_dim(x, 1).cpu(), x.cpu().mean(1), rtol=1e-6, atol=1e-6)
+    # other float types accumulate in fp32 and round once, as the reference's kernel does for every dtype
+    h = x.float().half()
+    assert torch.equal(vb.mean_dim(h, -1), vb.mean_dim(h.float(), -1).half())
+    with vb.set_batch_invariant_mode(True):
+        under_mode = h.mean(-1)
+        torch.use_deterministic_algorithms(False)
+    assert torch.equal(under_mode, vb.mean_dim(h, -1))
 
 
 def test_log_softmax_golden_and_invariance(vb):

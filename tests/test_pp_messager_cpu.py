@@ -66,6 +66,11 @@ def _worker(rank, world, port, fail_q, use_cuda=False, shared_cpu=None):
         # the reference's constructor: (pp_info, parallel_config, device)
         m = PPMessager(PPInfo(world, rank), ParallelConfig(world, "127.0.0.1", str(port)), device,
                        shared_cpu_group=shared_cpu)
+        # ring topology under the reference's attribute names (tests/test_pp_messager.py:128-143); the world's own
+        # ranks here, since this process group holds one replica
+        assert m._next_msger_rank == (rank + 1) % world and m._prev_msger_rank == (rank - 1) % world
+        for pair in (m._next_msger_cpu_pair, m._next_msger_gpu_pair, m._prev_msger_cpu_pair, m._prev_msger_gpu_pair):
+            assert pair is not None
         for step, (T, S, W) in enumerate([(8, 4, 5), (64, 8, 3), (2, 1, 1)]):
             req = step != 2          # the last step carries neither sampling configs nor tokens_generated
             # ring: rank r sends to r + 1; rank 0 sends token ids, the others hidden states

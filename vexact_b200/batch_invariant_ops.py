@@ -165,7 +165,11 @@ def mean_dim(input: torch.Tensor, dim: int, keepdim: bool = False, dtype: torch.
     if input.dtype != dtype:
         input = input.to(dtype)
     if dtype not in (torch.float32, torch.bfloat16):
-        raise NotImplementedError(f"mean_dim for dtype {dtype} is not implemented")
+        if not dtype.is_floating_point:
+            raise NotImplementedError(f"mean_dim for dtype {dtype} is not implemented")
+        # fp16 / fp64: the reference's kernel accumulates every dtype in fp32 and rounds once
+        # (batch_invariant_ops.py:333-381); an exact upcast (fp16) or the fp32 view (fp64) through the fp32 kernel
+        return mean_dim(input.float(), dim, keepdim=keepdim, dtype=torch.float32).to(dtype)
     moved = dim != input.ndim - 1
     x = input.movedim(dim, -1) if moved else input
     n = x.shape[-1]

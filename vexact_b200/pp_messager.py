@@ -131,6 +131,14 @@ class PPMessager:
             if store and self.pp_rank == nxt:
                 self._prev_rank, self._prev_cpu, self._prev_dev = pair[0], cpu, dev
 
+    # the reference's attribute names (pp_messager.py:97-114; tests/test_pp_messager.py:128-143 read them)
+    _next_msger_rank = property(lambda self: self._next_rank)
+    _prev_msger_rank = property(lambda self: self._prev_rank)
+    _next_msger_cpu_pair = property(lambda self: self._next_cpu)
+    _next_msger_gpu_pair = property(lambda self: self._next_dev)
+    _prev_msger_cpu_pair = property(lambda self: self._prev_cpu)
+    _prev_msger_gpu_pair = property(lambda self: self._prev_dev)
+
     # ---------------------------------------------------------------- staging
     def reserve(self, hidden_size: int, max_tokens: int, max_seqs: int, max_blocks_per_seq: int,
                 vocab_size: int = 0) -> None:
