@@ -404,3 +404,30 @@ def test_flex_key_paged_gives_the_other_keys_bits_and_packed_one_sequence(vb):
                             query_start_loc=torch.tensor([0, 10, 19], dtype=torch.int32).cuda())
     with pytest.raises(NotImplementedError):
         vb.flex_attention_forward(mod, q, k_all[:, :, :new], v_all[:, :, :new], None, scaling=d ** -0.5)
+
+
+@pytest.mark.parametrize("head_dim", [32, 40, 96])
+def test_packed_varlen_forward_takes_other_head_dims(vb, head_dim):
+    """The packed (training-side) call with head dims the kernels do not tile (reference
+    tests/batch_invariant_ops/test_triton_attention_varlen.py:289-301 uses 40 and 96): against fp32 eager attention
+    (`_eager_attention`, :52-72 there), causal with the queries at the end of the keys."""
+    g = torch.Generator().manual_seed(202)
+    hq, hkv = 6, 3
+    q_lens, kv_lens = [9, 23], [41, 57]
+    q = torch.randn(sum(q_lens), hq, head_dim, generator=g).to(BF).cuda()
+    k = torch.randn(sum(kv_lens), hkv, head_dim, generator=g).to(BF).cuda()
+    v = torch.randn(sum(kv_lens), hkv, head_dim, generator=g).to(BF).cuda()
+    cu_q = torch.tensor([0, 9, 32], dtype=torch.int32).cuda()
+    cu_k = torch.tensor([0, 41, 98], dtype=torch.int32).cuda()
+    out, _ = vb.flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_seqlen_q=max(q_lens), max_seqlen_k=max(kv_lens),
+                                       softmax_scale=head_dim ** -0.5, causal=True)
+    assert out.shape == q.shape
+    qo = ko = 0
+    for ql, kl in zip(q_lens, kv_lens):
+        qs, ks, vs = q[qo:qo + ql].float(), k[ko:ko + kl].float(), v[ko:ko + kl].float()
+        s = torch.einsum("qhd,khd->hqk", qs, ks.repeat_interleave(hq // hkv, 1)) * head_dim ** -0.5
+        qi = torch.arange(ql).cuda()[:, None] + (kl - ql)
+        s = s.masked_fill(~(torch.arange(kl).cuda()[None, :] <= qi), float("-inf"))
+        ref = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vs.repeat_interleave(hq // hkv, 1))
+        torch.testing.assert_close(out[qo:qo + ql].float(), ref, rtol=2 ** -7, atol=7e-3)
+        qo, ko = qo + ql, ko + kl

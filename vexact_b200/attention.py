@@ -154,6 +154,7 @@ def flash_attn_varlen_func(
 
 
 PACKED_PAGE = 16   # page size of the temporary cache behind the packed path
+_KERNEL_HEAD_DIMS = ((128, 128), (192, 128), (64, 64))   # (key dim, value dim) the attention kernels tile
 
 
 def packed_to_paged(k: torch.Tensor, v: torch.Tensor, cu_seqlens_k: torch.Tensor, max_seqlen_k: int,
@@ -188,6 +189,20 @@ class _PackedVarlenForward(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, scale, max_seqlen_q, max_seqlen_k):
+        dk, dv = q.shape[-1], v.shape[-1]
+        if (dk, dv) not in _KERNEL_HEAD_DIMS:
+            # Head dims the kernels do not tile (the reference's packed path takes any, e.g. 40 or 96:
+            # tests/batch_invariant_ops/test_triton_attention_varlen.py:289): zero columns up to the next
+            # tiled width add exact zeros to every dot product and are cut from the output again.  `scale` is
+            # explicit, so it is not touched by the wider head.
+            wide = next((d for d in (64, 128) if d >= max(dk, dv)), None)
+            if wide is None:
+                raise NotImplementedError(f"head dims ({dk}, {dv}) above 128 other than (192, 128)")
+            pad = torch.nn.functional.pad
+            out = _PackedVarlenForward.forward(ctx, pad(q, (0, wide - dk)), pad(k, (0, wide - dk)),
+                                               pad(v, (0, wide - dv)), cu_seqlens_q, cu_seqlens_k, scale,
+                                               max_seqlen_q, max_seqlen_k)
+            return out[..., :dv].contiguous()
         k_cache, v_cache, table, lens = packed_to_paged(k, v, cu_seqlens_k, max_seqlen_k)
         cu_q = cu_seqlens_q if cu_seqlens_q.dtype == torch.int32 else cu_seqlens_q.to(torch.int32)
         return paged_attention(q, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q)
