@@ -334,6 +334,14 @@ int b200_moe_scatter(const void* x, long long x_row_stride, const void* index_i3
 int b200_moe_gather(const void* x, long long x_rows, const void* index_i32, long long index_stride_t,
                     long long index_stride_k, void* out, long long T, int topk, int H, void* stream);
 
+/* ---- vexact/batch_invariant_ops/group_gemm/kernel/group_gemm.py:360 group_gemm_same_mn(transpose_a=True): the
+ *      weight gradient of a grouped GEMM, c[g] = a[rows of g]^T @ b[rows of g] with the rows of group g being
+ *      [cu_seqlens[g], cu_seqlens[g + 1]).  a [rows, M], b [rows, N], c [num_groups, M, N], all bf16 contiguous;
+ *      fp32 accumulation in ascending row order, one rounding; an empty group gets zeros.  M, N multiples of 4.
+ *      A training-side operator on the CUDA cores (no tensor-core form): bound by writing c. */
+int b200_moe_grouped_wgrad(const void* a, const void* b, void* c, const void* cu_seqlens, long long rows,
+                           int num_groups, int M, int N, void* stream);
+
 /* b200_moe_unpermute_reduce followed by b200_add_rmsnorm (the residual add and input RMSNorm the next
  * decoder layer starts with) in one launch, with that pair's arithmetic element for element:
  * sum_out[t] = bf16(residual[t] + moe[t]), out[t] = rmsnorm(sum_out[t]) * weight (mode as b200_rmsnorm).

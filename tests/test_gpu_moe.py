@@ -311,6 +311,9 @@ def test_group_gemm_operators_under_the_reference_names(vb):
     cu, a_idx, scatter_ours = vb.fused_moe.build_moe_indices(sel_d, E)
     assert torch.equal(scatter_ours, scatter_index)
 
+    rows = gg.moe_index_compute(sel_d, torch.cumsum(splits, dim=0))     # moe.py:382: any order inside an expert;
+    assert rows.dtype == torch.int64 and torch.equal(rows, scatter_index.long())   # here the stable one
+
     scattered = gg.moe_scatter(x, scatter_index)
     assert torch.equal(scattered, x[a_idx.long()])
     assert torch.equal(gg.moe_scatter(x.half(), scatter_index.long()), x.half()[a_idx.long()])   # fp16 rows, int64 index
@@ -342,8 +345,32 @@ def test_group_gemm_operators_under_the_reference_names(vb):
     torch.testing.assert_close(out.float(), fused.float(), rtol=0, atol=tol)
     assert (out == fused).float().mean() > 0.95
 
-    for call in (lambda: gg.group_gemm_same_nk(scattered, w1, cumsum_t, T * k, transpose_b=False),
-                 lambda: gg.group_gemm_same_mn(scattered, scattered, w1, cumsum_t, T * k),
+    # the two GEMM forms of the backward (group_gemm.py:156 with transpose_b=False, :360 group_gemm_same_mn)
+    dgrad = gg.group_gemm_same_nk(fc1_1, w1, cumsum_t, T * k, transpose_b=False)        # [R, I] x [E, I, H] -> [R, H]
+    assert torch.equal(dgrad, gg.group_gemm_same_nk(fc1_1, w1.transpose(1, 2).contiguous(), cumsum_t, T * k,
+                                                    transpose_b=True))
+    ref32 = torch.cat([fc1_1[bounds[e]:bounds[e + 1]].float() @ w1[e].float() for e in range(E)])
+    torch.testing.assert_close(dgrad.float(), ref32, rtol=2 ** -7, atol=2 ** -7 * ref32.abs().max().item())
+    wgrad = gg.group_gemm_same_mn(fc1_1, scattered, torch.full_like(w1, 7.0), cumsum_t, T * k, transpose_a=True,
+                                  transpose_b=False)                                  # [E, I, H]
+    ref32 = torch.stack([fc1_1[bounds[e]:bounds[e + 1]].float().t() @ scattered[bounds[e]:bounds[e + 1]].float()
+                         for e in range(E)])
+    torch.testing.assert_close(wgrad.float(), ref32, rtol=2 ** -7, atol=2 ** -8 * ref32.abs().max().item())
+    lonely = torch.cumsum(torch.tensor([3, 0, T * k - 3] + [0] * (E - 3), device="cuda"), 0)   # empty groups: zeros
+    wz = gg.group_gemm_same_mn(fc1_1, scattered, torch.full_like(w1, 7.0), lonely, T * k, transpose_a=True,
+                               transpose_b=False)
+    assert not wz[1].any() and not wz[3:].any() and wz[0].any() and wz[2].any()
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0
+    overrun = lonely.clone()
+    overrun[-1] = T * k + 9                                  # past the last row: clipped and reported
+    wo = gg.group_gemm_same_mn(fc1_1, scattered, torch.full_like(w1, 7.0), overrun, T * k, transpose_a=True,
+                               transpose_b=False)
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[:2] == (2, E - 1)
+    assert torch.equal(wo[2], wz[2]) and not wo[E - 1].any()
+
+    for call in (lambda: gg.group_gemm_same_mn(scattered, scattered, w1, cumsum_t, T * k),
                  lambda: gg.moe_add_gather(fc2, fc2, scatter_index)):
         with pytest.raises(NotImplementedError):
             call()
@@ -378,7 +405,7 @@ def test_scatter_and_gather_skip_and_report_an_index_out_of_range(vb):
 
 def test_expert_function_classes_take_the_reference_arguments(vb):
     """`FusedMoeExpertFunction.apply` / `QuackFusedMoeExpertFunction.apply` (fused_moe.py:22, :295) with the
-    reference's seven positional arguments: the fused forward's bits; differentiating through them raises."""
+    reference's seven positional arguments: the fused forward's bits."""
     from vexact_b200.fused_moe import FusedMoeExpertFunction, QuackFusedMoeExpertFunction
 
     T, E, k, H, I = 33, 8, 2, 128, 64
@@ -388,7 +415,50 @@ def test_expert_function_classes_take_the_reference_arguments(vb):
     fused = vb.fused_moe_forward(*args)
     assert torch.equal(FusedMoeExpertFunction.apply(*args), fused)
     assert torch.equal(QuackFusedMoeExpertFunction.apply(*args), fused)
-    x = args[3].clone().requires_grad_(True)
-    out = FusedMoeExpertFunction.apply(E, args[1], args[2], x, *args[4:])
-    with pytest.raises(NotImplementedError):
-        out.float().sum().backward()
+
+
+@pytest.mark.parametrize("fused_weights", [False, True])
+def test_fused_moe_backward_against_autograd_of_the_fp32_formula(vb, fused_weights):
+    """Gradients of `fused_moe_forward` (reference backward: fused_moe.py:113-265) for the hidden states, the routing
+    weights and the three weight tensors, against torch autograd on the fp32 statement of the same function
+    (sum over k of w_k * fc2_e(silu(fc1_1_e x) * fc1_2_e x)).  The chain rounds to bf16 after every step, as the
+    reference's does: stated tolerance 2^-5 of each gradient's largest magnitude, and cosine similarity > 0.999.
+    One expert is never selected: its weight gradients are exact zeros."""
+    T, E, k, H, I = 48, 8, 2, 128, 64
+    hidden, gate_up, down, sel, rw = _moe_case(T, E, k, H, I, seed=31)
+    sel = torch.where(sel == E - 1, torch.zeros_like(sel), sel)          # expert E-1 unused
+    dup = sel[:, 0] == sel[:, 1]
+    sel[dup, 1] = (sel[dup, 0] + 1) % (E - 1)
+    g_out = _seeded(T, H, seed=32)
+    leaves = dict(x=hidden.cuda(), rw=rw.cuda(), w1=gate_up[:, :I].contiguous().cuda(),
+                  w2=gate_up[:, I:].contiguous().cuda(), w3=down.cuda())
+    ours = {n: t.clone().requires_grad_(True) for n, t in leaves.items()}
+    if fused_weights:       # the model files' keyword form: one [E, 2I, H] tensor, gate rows first
+        gu = torch.cat([ours["w1"], ours["w2"]], dim=1)
+        out = vb.fused_moe_forward(E, ours["rw"], sel.cuda(), ours["x"], fc2_weight=ours["w3"], fc1_1_2_weight=gu)
+    else:
+        out = vb.fused_moe_forward(E, ours["rw"], sel.cuda(), ours["x"], ours["w1"], ours["w2"], ours["w3"])
+    assert torch.equal(out, vb.fused_moe_forward(E, leaves["rw"], sel.cuda(), leaves["x"], leaves["w1"], leaves["w2"],
+                                                 leaves["w3"]))
+    out.backward(g_out.cuda())
+
+    ref = {n: t.float().clone().requires_grad_(True) for n, t in leaves.items()}
+    s = sel.cuda()
+    acc = torch.zeros(T, H, device="cuda")
+    for j in range(k):
+        e = s[:, j]
+        a = torch.einsum("th,tih->ti", ref["x"], ref["w1"][e])
+        b = torch.einsum("th,tih->ti", ref["x"], ref["w2"][e])
+        acc = acc + torch.einsum("ti,thi->th", torch.nn.functional.silu(a) * b * ref["rw"][:, j:j + 1], ref["w3"][e])
+    acc.backward(g_out.cuda().float())
+    for n in leaves:
+        got, want = ours[n].grad.float(), ref[n].grad
+        assert got.shape == want.shape and ours[n].grad.dtype == leaves[n].dtype
+        tol = 2 ** -5 * want.abs().max().item()
+        torch.testing.assert_close(got, want, rtol=0, atol=tol, msg=lambda m, n=n: f"grad of {n}: {m}")
+        cos = torch.nn.functional.cosine_similarity(got.flatten(), want.flatten(), dim=0).item()
+        assert cos > 0.999, (n, cos)
+    for n in ("w1", "w2", "w3"):
+        assert not ours[n].grad[E - 1].any()
+
+

@@ -588,6 +588,83 @@ moe_gather_checked_kernel(const __nv_bfloat16* __restrict__ x, long long x_rows,
   }
 }
 
+// Weight gradient of a grouped GEMM, the contraction running over each group's own rows ("ragged K"):
+//   c[g, m, n] = sum over rows r of group g, ascending, of a[r, m] * b[r, n]      (fp32 fmaf chain, one rounding)
+// (group_gemm/kernel/group_gemm.py:255-400 group_gemm_same_mn with transpose_a).  A training-side operator kept
+// simple: one CTA per 64 x 64 tile of one group's output, rows staged 16 at a time through shared memory, fp32
+// FMAs on the CUDA cores.  With ~rows/groups rows per group the work is a few GFLOP and the kernel is bound by
+// writing c (groups * M * N * 2 bytes); an empty group gets zeros.  A group whose bounds leave [0, rows] or
+// decrease is clipped and reported through the status word.
+constexpr int WG_TILE = 64, WG_ROWS = 16;
+__global__ void __launch_bounds__(256)
+moe_wgrad_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                 __nv_bfloat16* __restrict__ c, const int* __restrict__ cu_seqlens, long long rows, int M, int N) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float sa[WG_ROWS][WG_TILE], sb[WG_ROWS][WG_TILE];
+  const int g = blockIdx.z, m0 = blockIdx.y * WG_TILE, n0 = blockIdx.x * WG_TILE;
+  long long r0 = cu_seqlens[g], r1 = cu_seqlens[g + 1];
+  if (r0 < 0 || r1 > rows || r1 < r0) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) report_status(B200_STATUS_BAD_INDEX, g);
+    r0 = r0 < 0 ? 0 : (r0 > rows ? rows : r0);
+    r1 = r1 > rows ? rows : r1;
+    if (r1 < r0) r1 = r0;
+  }
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int lr = tid >> 4, lc = (tid & 15) * 4;       // this thread stages row lr, columns lc..lc+3 of both tiles
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (long long r = r0; r < r1; r += WG_ROWS) {
+    const long long row = r + lr;
+    float va[4] = {0.f, 0.f, 0.f, 0.f}, vb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (row < r1) {
+      if (m0 + lc < M) {            // M and N are multiples of 4: a group of four columns is inside or outside
+        const uint2 q = *reinterpret_cast<const uint2*>(a + row * M + m0 + lc);
+        unpack_bf2(q.x, va[0], va[1]);
+        unpack_bf2(q.y, va[2], va[3]);
+      }
+      if (n0 + lc < N) {
+        const uint2 q = *reinterpret_cast<const uint2*>(b + row * N + n0 + lc);
+        unpack_bf2(q.x, vb[0], vb[1]);
+        unpack_bf2(q.y, vb[2], vb[3]);
+      }
+    }
+    __syncthreads();                // the previous chunk has been consumed
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sa[lr][lc + j] = va[j];
+      sb[lr][lc + j] = vb[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < WG_ROWS; ++k) {
+      float xa[4], xb[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) xa[i] = sa[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) xb[j] = sb[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xa[i], xb[j], acc[i][j]);
+    }
+  }
+  __nv_bfloat16* cg = c + (long long)g * M * N;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i, n = n0 + tx * 4;
+    if (m < M && n < N) {
+      uint2 o;
+      o.x = pack_bf2(acc[i][0], acc[i][1]);
+      o.y = pack_bf2(acc[i][2], acc[i][3]);
+      *reinterpret_cast<uint2*>(cg + (long long)m * N + n) = o;
+    }
+  }
+}
+
 // h = bf16(bf16(bf16(silu(g)) * u) * s): the unfused tail of fc1 for split gate / up weights.
 __global__ void __launch_bounds__(256)
 swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
@@ -920,6 +997,20 @@ extern "C" int b200_moe_gather(const void* x, long long x_rows, const void* inde
   launch_k(moe_gather_checked_kernel, dim3((unsigned)T), dim3(256), 0, (cudaStream_t)stream,
            (const __nv_bfloat16*)x, x_rows, (const int*)index_i32, index_stride_t, index_stride_k,
            (__nv_bfloat16*)out, H, topk);
+  return launch_status();
+}
+
+// c[g] = a[rows of g]^T @ b[rows of g]: a [rows, M], b [rows, N], c [G, M, N] bf16 contiguous, cu_seqlens
+// [G + 1] i32 (rows of group g are [cu[g], cu[g + 1])).  M and N multiples of 4, 8-byte aligned pointers.
+extern "C" int b200_moe_grouped_wgrad(const void* a, const void* b, void* c, const void* cu_seqlens, long long rows,
+                                      int num_groups, int M, int N, void* stream) {
+  using namespace b200;
+  if (!a || !b || !c || !cu_seqlens || rows < 0 || num_groups <= 0 || M <= 0 || N <= 0) return B200_ERR_ARG;
+  if (M % 4 != 0 || N % 4 != 0 || num_groups > 65535 || (M + WG_TILE - 1) / WG_TILE > 65535) return B200_ERR_SHAPE;
+  launch_k(moe_wgrad_kernel, dim3((unsigned)((N + WG_TILE - 1) / WG_TILE), (unsigned)((M + WG_TILE - 1) / WG_TILE),
+                                  (unsigned)num_groups),
+           dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)c,
+           (const int*)cu_seqlens, rows, M, N);
   return launch_status();
 }
 

@@ -315,6 +315,17 @@ def fused_moe_forward(
         raise ValueError("hidden_states must be a CUDA tensor")
     if fc2_weight is None:
         raise ValueError("fc2_weight is required")
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (
+            routing_weights, hidden_states, fc1_1_weight, fc1_2_weight, fc2_weight, fc1_1_2_weight, addend)):
+        # the training side: through the autograd Function, as the reference's fused_moe_forward does (fused_moe.py:459)
+        if defer_reduce or plan is not None:
+            raise NotImplementedError("defer_reduce / plan are inference-only forms")
+        if fc1_1_2_weight is not None:
+            I = fc1_1_2_weight.shape[1] // 2
+            fc1_1_weight, fc1_2_weight = fc1_1_2_weight[:, :I].contiguous(), fc1_1_2_weight[:, I:].contiguous()
+        out = FusedMoeExpertFunction.apply(num_experts, routing_weights.bfloat16(), selected_experts,
+                                           hidden_states.bfloat16(), fc1_1_weight, fc1_2_weight, fc2_weight)
+        return out if addend is None else out + addend.to(torch.bfloat16).reshape(out.shape)
     routing_weights = routing_weights.to(torch.bfloat16).contiguous()
     orig_shape = hidden_states.shape
     x = hidden_states.to(torch.bfloat16).reshape(-1, orig_shape[-1])
@@ -371,17 +382,83 @@ def fused_moe_forward(
 
 class FusedMoeExpertFunction(torch.autograd.Function):
     """The reference's entry class (fused_moe.py:22; `QuackFusedMoeExpertFunction` :295 on sm_90 and newer) with
-    its positional arguments.  Forward only: the backward (dgrad / ragged-K wgrad grouped GEMMs) is the training
-    side's and raises."""
+    its positional arguments.
+
+    Forward: the fused pipeline above.  Backward: the reference's chain (fused_moe.py:113-265) over this
+    library's operators: the forward's intermediates are recomputed step by step from the saved inputs (scatter,
+    two plain grouped GEMMs, SwiGLU in torch as there), then scatter of the output gradient, three dgrad grouped
+    GEMMs, three ragged-K weight gradients, the elementwise steps in torch exactly as the reference writes them, and
+    the top-k sum back to tokens.  Correct against autograd of the fp32 formula; the two backward GEMM forms are
+    not tuned (`group_gemm.py`)."""
 
     @staticmethod
     def forward(ctx, num_experts, gate_weights, expert_index, hidden_states, fc1_1_weight, fc1_2_weight, fc2_weight):
+        ctx.num_experts = num_experts
+        ctx.save_for_backward(gate_weights, expert_index, hidden_states, fc1_1_weight, fc1_2_weight, fc2_weight)
         return fused_moe_forward(num_experts, gate_weights, expert_index, hidden_states, fc1_1_weight, fc1_2_weight,
                                  fc2_weight)
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("the fused-MoE backward is not part of this library")
+        from . import group_gemm as gg
+
+        gate_weights, expert_index, hidden_states, w1, w2, w3 = ctx.saved_tensors
+        E = ctx.num_experts
+        bf = torch.bfloat16
+        H = grad_output.shape[-1]
+        grad_output = grad_output.reshape(-1, H).to(bf).contiguous()
+        x = hidden_states.reshape(-1, H).to(bf).contiguous()
+        T = x.shape[0]
+        experts = expert_index.reshape(T, -1)
+        k = experts.shape[1]
+        w1b, w2b, w3b = (w.to(bf).contiguous() for w in (w1, w2, w3))
+
+        # forward intermediates again, one operator at a time (fused_moe.py:36-99)
+        cu, _, scatter_index = build_moe_indices(experts, E)
+        cumsum_t = cu[1:]
+        flat = scatter_index.flatten().long()
+        scatter_output = gg.moe_scatter(x, scatter_index)
+        fc1_1_output = gg.group_gemm_same_nk(scatter_output, w1b, cumsum_t, T * k, transpose_b=True)
+        fc1_2_output = gg.group_gemm_same_nk(scatter_output, w2b, cumsum_t, T * k, transpose_b=True)
+        fc1_1_activation = torch.ops.aten.silu(fc1_1_output)
+        fc1_activation = fc1_1_activation * fc1_2_output
+        scattered_gate_weight = torch.empty((T * k, 1), dtype=bf, device=x.device)
+        scattered_gate_weight[flat] = gate_weights.to(bf).reshape(-1, 1)
+        fc1_weighted_output = fc1_activation * scattered_gate_weight
+
+        need = ctx.needs_input_grad
+        # top-k sum, then fc2
+        grad_fc2_output = gg.moe_scatter(grad_output, scatter_index)
+        grad_fc1_weighted_output = gg.group_gemm_same_nk(grad_fc2_output, w3b, cumsum_t, T * k, transpose_b=False)
+        grad_w3 = None
+        if need[6]:
+            grad_w3 = gg.group_gemm_same_mn(grad_fc2_output, fc1_weighted_output, torch.empty_like(w3b), cumsum_t,
+                                            T * k, transpose_a=True, transpose_b=False).to(w3.dtype)
+        # routing weight
+        grad_fc1_activation = grad_fc1_weighted_output * scattered_gate_weight
+        grad_gate = None
+        if need[1]:
+            grad_scattered = torch.sum(fc1_activation * grad_fc1_weighted_output, dim=-1)
+            grad_gate = grad_scattered[flat].reshape(gate_weights.shape).to(gate_weights.dtype)
+        # SwiGLU
+        grad_fc1_1_activation = grad_fc1_activation * fc1_2_output
+        grad_fc1_2_output = fc1_1_activation * grad_fc1_activation
+        grad_fc1_1_output = torch.ops.aten.silu_backward(grad_fc1_1_activation, fc1_1_output)
+        # fc1, both halves
+        grad_w1 = grad_w2 = None
+        if need[4]:
+            grad_w1 = gg.group_gemm_same_mn(grad_fc1_1_output, scatter_output, torch.empty_like(w1b), cumsum_t, T * k,
+                                            transpose_a=True, transpose_b=False).to(w1.dtype)
+        if need[5]:
+            grad_w2 = gg.group_gemm_same_mn(grad_fc1_2_output, scatter_output, torch.empty_like(w2b), cumsum_t, T * k,
+                                            transpose_a=True, transpose_b=False).to(w2.dtype)
+        grad_hidden = None
+        if need[3]:
+            grad_scatter_output = (gg.group_gemm_same_nk(grad_fc1_1_output, w1b, cumsum_t, T * k, transpose_b=False)
+                                   + gg.group_gemm_same_nk(grad_fc1_2_output, w2b, cumsum_t, T * k, transpose_b=False))
+            grad_hidden = gg.moe_gather(grad_scatter_output, scatter_index).reshape(hidden_states.shape)
+            grad_hidden = grad_hidden.to(hidden_states.dtype)
+        return None, grad_gate, None, grad_hidden, grad_w1, grad_w2, grad_w3
 
 
 QuackFusedMoeExpertFunction = FusedMoeExpertFunction

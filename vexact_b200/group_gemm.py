@@ -1,15 +1,15 @@
 """The forward operators of the reference's grouped-GEMM package under their own names.
 
 Mirror of vexact/batch_invariant_ops/group_gemm/kernel/moe.py (`expert_histogram` :52, `moe_gather`
-:131, `moe_scatter` :304) and group_gemm/kernel/group_gemm.py (`group_gemm_same_nk` :156), which
+:131, `moe_scatter` :304, `moe_index_compute` :382) and group_gemm/kernel/group_gemm.py (`group_gemm_same_nk` :156), which
 `FusedMoeExpertFunction.forward` (fused_moe.py:24-111) chains one after the other and which the
 reference's tests call directly.  `fused_moe_forward` in this package runs the same steps with fewer
 launches; these are for callers that hold the reference's intermediate tensors (a scatter index, an
 inclusive cumulative sum of rows per expert) and want one step at a time.
 
-Forward only: `transpose_b=False` (the dgrad form), `group_gemm_same_mn` (the ragged-K wgrad),
-`moe_add_gather` and accumulation into `c` belong to the training side's backward and raise
-NotImplementedError.
+The two GEMM forms of the backward are here too, correct but not tuned: `transpose_b=False` (dgrad) runs
+the forward kernel over a transposed copy of the weights, `group_gemm_same_mn` (the ragged-K weight gradient)
+is a CUDA-core kernel.  `moe_add_gather`, fused activations and accumulation into `c` raise NotImplementedError.
 """
 from __future__ import annotations
 
@@ -40,6 +40,22 @@ def expert_histogram(input: torch.Tensor, num_bins: int) -> torch.Tensor:
     # the index kernel's exclusive prefix sum over the bins, differenced
     cu = _permute(flat.view(-1, 1), None, None, num_bins)["cu_seqlens"]
     return cu[1:] - cu[:-1]
+
+
+def moe_index_compute(experts_for_tokens: torch.Tensor, expert_histogram_cumsum: torch.Tensor) -> torch.Tensor:
+    """Row of the expert-sorted activation for every (token, k): [n_tokens, topk] int64 (moe.py:382-433).
+
+    The reference reserves each expert's rows with atomics, so its order inside an expert varies from run to
+    run; here it is the stable order (token, k ascending), i.e. the `scatter_index` of fused_moe.py:43, which
+    satisfies the same contract.  `expert_histogram_cumsum` ([n_experts], inclusive) only tells the number of
+    experts: the counts are recomputed in the same launch."""
+    assert experts_for_tokens.is_contiguous()
+    assert experts_for_tokens.numel() < (1 << 31) - 1
+    assert expert_histogram_cumsum.is_contiguous()
+    assert experts_for_tokens.device == expert_histogram_cumsum.device
+    e = experts_for_tokens if experts_for_tokens.dim() == 2 else experts_for_tokens.reshape(-1, 1)
+    plan = _permute(e, None, None, expert_histogram_cumsum.numel())
+    return plan["scatter_index"].view(experts_for_tokens.shape).to(torch.int64)
 
 
 def moe_scatter(x: torch.Tensor, index: torch.Tensor, out_dtype=None) -> torch.Tensor:
@@ -115,8 +131,11 @@ def group_gemm_same_nk(
     del max_M
     assert not transpose_a, "Transpose A not tested yet."
     if not transpose_b:
-        raise NotImplementedError("transpose_b=False is the dgrad form of the fused-MoE backward, which is not "
-                                  "part of this library")
+        # dgrad: b is [G, K, N] with N contiguous.  The tensor-core kernel reads weights K-major, so the weights
+        # are transposed into scratch first (one extra pass over them); the products and their order are those
+        # of the forward form on the transposed tensor.
+        assert b.dim() == 3 and a.shape[1] == b.shape[1]
+        return group_gemm_same_nk(a, b.transpose(1, 2).contiguous(), cumsum_M, 0, transpose_b=True)
     if activation is not None or save_activation:
         raise NotImplementedError("a fused activation is not offered here; fused_moe_forward fuses SwiGLU itself")
     if c is not None:
@@ -141,6 +160,32 @@ def group_gemm_same_nk(
     return out
 
 
-def group_gemm_same_mn(*args, **kwargs):
-    raise NotImplementedError("group_gemm_same_mn (group_gemm.py:360, the ragged-K weight gradient) serves the "
-                              "fused-MoE backward, which is not part of this library")
+def group_gemm_same_mn(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cumsum_K: torch.Tensor, max_K: int,
+                       transpose_a: bool = False, transpose_b: bool = False) -> torch.Tensor:
+    """c[g] = a[rows of g]^T @ b[rows of g], written into the caller's `c` [G, M, N] (group_gemm.py:360-400 with
+    `transpose_a=True, transpose_b=False`, the only form fused_moe.py:154-236 uses): a [total_K, M], b [total_K, N],
+    `cumsum_K` the INCLUSIVE cumulative sum of rows per group.  fp32 accumulation over a group's rows in ascending
+    order, one rounding; an empty group gets zeros."""
+    del max_K
+    if not transpose_a or transpose_b:
+        raise NotImplementedError("group_gemm_same_mn is implemented for transpose_a=True, transpose_b=False")
+    G, M, N = c.shape
+    assert a.dtype in [torch.bfloat16, torch.float16], a.dtype
+    assert b.dtype in [torch.bfloat16, torch.float16], b.dtype
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or c.dtype != torch.bfloat16:
+        raise NotImplementedError("group_gemm_same_mn is implemented for bf16")
+    assert a.is_cuda and a.device == b.device, f"a.device = {a.device}, b.device = {b.device}"
+    assert a.device == c.device, f"a.device = {a.device}, c.device = {c.device}"
+    assert len(cumsum_K) == G, f"{len(cumsum_K), c.shape}"
+    assert a.is_contiguous() and b.is_contiguous() and c.is_contiguous(), "Not implemented: Noncontiguous input."
+    assert a.shape == (b.shape[0], M) and b.shape[1] == N
+    if M % 4 or N % 4 or a.data_ptr() % 8 or b.data_ptr() % 8 or c.data_ptr() % 8:
+        raise NotImplementedError("group_gemm_same_mn needs M and N that are multiples of 4 and 8-byte aligned data")
+    cu = torch.zeros(G + 1, dtype=torch.int32, device=a.device)
+    cu[1:] = cumsum_K
+    _lib.check(
+        _lib.load().b200_moe_grouped_wgrad(a.data_ptr(), b.data_ptr(), c.data_ptr(), cu.data_ptr(), a.shape[0], G, M,
+                                           N, _lib.current_stream()),
+        "b200_moe_grouped_wgrad",
+    )
+    return c
