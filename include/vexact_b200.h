@@ -246,6 +246,21 @@ int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* 
                                 long long vc_head_stride, float softmax_scale, const void* seq_order,
                                 long long total_q, void* stream);
 
+/* ---- vexact/batch_invariant_ops/triton_invariant_attention.py:194-431 (_varlen_attn_bwd_dq_kernel,
+ *      _varlen_attn_bwd_dkv_kernel): dq, dk, dv of the packed (non-paged) causal varlen attention.  All tensors
+ *      bf16 and contiguous: q / dq [total_q, hq, dk_dim], k / dk [total_k, hkv, dk_dim], v / dv [total_k, hkv,
+ *      dv_dim], out / dout [total_q, hq, dv_dim]; cu_seqlens_q / _k [num_seqs + 1] int32; lse / delta: fp32
+ *      scratch [total_q, hq] each (the log-sum-exp is recomputed here, the forward does not save it).
+ *      (dk_dim, dv_dim) in {(64, 64), (128, 128), (192, 128)}.  p and ds are rounded to bf16 before their
+ *      products as in the reference; fp32 accumulation in a fixed order, no atomics.  A training-side operator
+ *      on the CUDA cores (no tensor-core form).  Pass zero-filled dq / dk / dv: rows of no sequence are not
+ *      written. */
+int b200_varlen_attn_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                              const void* cu_seqlens_q, const void* cu_seqlens_k, void* dq, void* dk, void* dv,
+                              void* lse_scratch_f32, void* delta_scratch_f32, int num_seqs, int max_seqlen_q,
+                              int max_seqlen_k, long long total_q, long long total_k, int num_q_heads,
+                              int num_kv_heads, int dk_dim, int dv_dim, float softmax_scale, void* stream);
+
 /* ---- vexact/models/qwen3_moe/modeling_qwen3_moe.py:128-134 (softmax, top-k, renormalise, cast).
  * logits_dtype: 0 = fp32, 1 = bf16.  Any of the four outputs may be NULL except that one weight
  * and one expert output are required. */

@@ -344,10 +344,13 @@ def test_packed_varlen_forward_equals_paged_prefill_bitwise(vb):
                                          seqused_k=torch.tensor(lens, dtype=torch.int32).cuda(),
                                          page_table=table.cuda(), causal=True)
     assert torch.equal(packed, paged)
-    with pytest.raises(NotImplementedError):
-        qq = q.clone().requires_grad_(True)
-        out, _ = vb.flash_attn_varlen_func(qq, k, v, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=max(lens),
-                                           max_seqlen_k=max(lens), causal=True)
+    # the paged call is forward-only under autograd, as the reference's (test_triton_attention_varlen.py:561-569)
+    qq = q.clone().requires_grad_(True)
+    out, _ = vb.flash_attn_varlen_func(qq, kc, vc, cu_seqlens_q=cu, max_seqlen_q=max(lens),
+                                       seqused_k=torch.tensor(lens, dtype=torch.int32).cuda(),
+                                       page_table=table.cuda(), causal=True)
+    assert torch.equal(out, paged)
+    with pytest.raises(NotImplementedError, match="paged triton flash_attn_varlen_func backward"):
         out.float().sum().backward()
 
 
@@ -431,3 +434,64 @@ def test_packed_varlen_forward_takes_other_head_dims(vb, head_dim):
         ref = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vs.repeat_interleave(hq // hkv, 1))
         torch.testing.assert_close(out[qo:qo + ql].float(), ref, rtol=2 ** -7, atol=7e-3)
         qo, ko = qo + ql, ko + kl
+
+
+def _eager_packed(q, k, v, scale):
+    """fp32 causal attention of one sequence, queries at the end of the keys (the reference tests' `_eager_attention`,
+    test_triton_attention_varlen.py:52-72, without its bf16 cast of the probabilities)."""
+    ql, kl, g = q.shape[0], k.shape[0], q.shape[1] // k.shape[1]
+    s = torch.einsum("qhd,khd->hqk", q, k.repeat_interleave(g, 1)) * scale
+    seen = torch.arange(kl, device=q.device)[None, :] <= torch.arange(ql, device=q.device)[:, None] + (kl - ql)
+    s = s.masked_fill(~seen, float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), v.repeat_interleave(g, 1))
+
+
+@pytest.mark.parametrize("q_lens,kv_lens,hq,hkv,dk,dv", [
+    ([9, 23], [41, 57], 6, 3, 64, 64),          # decode-like chunks at the end of longer contexts, GQA
+    ([65, 129], [65, 129], 4, 2, 128, 128),     # full causal prefill, tiles with ragged edges
+    ([9, 23], [41, 57], 6, 3, 40, 40),          # a head dim the kernels do not tile (zero columns)
+    ([5, 40], [33, 40], 4, 4, 192, 128),        # MLA dims
+])
+def test_packed_varlen_backward_matches_autograd_of_fp32_attention(vb, q_lens, kv_lens, hq, hkv, dk, dv):
+    """dq, dk, dv of the packed call (reference kernels: triton_invariant_attention.py:194-431; reference tests:
+    test_triton_attention_varlen.py:75-150, :254-335) against torch autograd on fp32 eager attention.  bf16 inputs and
+    bf16 roundings of p and ds inside: the reference's own bf16 tolerance, 3e-2 of each gradient's largest
+    magnitude, and cosine similarity > 0.999.  A sequence's gradients are the same bits alone and in the batch."""
+    g = torch.Generator().manual_seed(77)
+    q = torch.randn(sum(q_lens), hq, dk, generator=g).to(BF).cuda()
+    k = torch.randn(sum(kv_lens), hkv, dk, generator=g).to(BF).cuda()
+    v = torch.randn(sum(kv_lens), hkv, dv, generator=g).to(BF).cuda()
+    dout = torch.randn(sum(q_lens), hq, dv, generator=g).to(BF).cuda()
+    cu_q = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32).cuda()
+    cu_k = torch.tensor([0] + torch.tensor(kv_lens).cumsum(0).tolist(), dtype=torch.int32).cuda()
+    scale = dk ** -0.5
+
+    def run(q, k, v, dout, cu_q, cu_k, mq, mk):
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v)]
+        out, _ = vb.flash_attn_varlen_func(*leaves, cu_q, cu_k, max_seqlen_q=mq, max_seqlen_k=mk, softmax_scale=scale,
+                                           causal=True)
+        out.backward(dout)
+        return [t.grad for t in leaves]
+
+    got = run(q, k, v, dout, cu_q, cu_k, max(q_lens), max(kv_lens))
+    ref_leaves = [t.float().clone().requires_grad_(True) for t in (q, k, v)]
+    qo = ko = 0
+    outs = []
+    for ql, kl in zip(q_lens, kv_lens):
+        outs.append(_eager_packed(ref_leaves[0][qo:qo + ql], ref_leaves[1][ko:ko + kl], ref_leaves[2][ko:ko + kl], scale))
+        qo, ko = qo + ql, ko + kl
+    torch.cat(outs).backward(dout.float())
+    for name, a, b in zip("qkv", got, ref_leaves):
+        want = b.grad
+        assert a.shape == want.shape and a.dtype == BF
+        torch.testing.assert_close(a.float(), want, rtol=0, atol=3e-2 * want.abs().max().item(),
+                                   msg=lambda m, name=name: f"d{name}: {m}")
+        cos = torch.nn.functional.cosine_similarity(a.float().flatten(), want.flatten(), dim=0).item()
+        assert cos > 0.999, (name, cos)
+    # sequence 1 alone: the same bits
+    a, b = q_lens[0], kv_lens[0]
+    alone = run(q[a:], k[b:], v[b:], dout[a:], torch.tensor([0, q_lens[1]], dtype=torch.int32).cuda(),
+                torch.tensor([0, kv_lens[1]], dtype=torch.int32).cuda(), q_lens[1], kv_lens[1])
+    assert torch.equal(alone[0], got[0][a:]) and torch.equal(alone[1], got[1][b:]) and torch.equal(alone[2], got[2][b:])
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0

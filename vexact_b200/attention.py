@@ -116,7 +116,7 @@ def flash_attn_varlen_func(
     With `page_table` / `block_table`: the paged rollout path.  Without: the packed path the training side
     uses (triton_invariant_attention.py:48-192, forward only): K / V are laid into a temporary paged cache
     and run through the same kernel, so a token gets the same bits from the packed call as from the rollout's
-    paged prefill.  The packed backward kernels (:194-431) are not part of this library: gradients raise."""
+    paged prefill.  Gradients of q, k and v come from `b200_varlen_attn_backward` (:194-431 there)."""
     del alibi_slopes, deterministic, return_attn_probs, kwargs
     if dropout_p != 0.0:
         raise NotImplementedError("dropout is not supported")
@@ -150,6 +150,8 @@ def flash_attn_varlen_func(
     if max_seqlen_q is None or int(max_seqlen_q) <= 0:
         # The reference kernel ignores max_seqlen_q; this one sizes its grid with it.
         max_seqlen_q = q.shape[0]
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _PagedForward.apply(q, k, v, cu_seqlens_q, lens, table, float(scale), int(max_seqlen_q)), None
     return paged_attention(q, k, v, cu_seqlens_q, lens, table, scale, int(max_seqlen_q)), None
 
 
@@ -184,32 +186,71 @@ def packed_to_paged(k: torch.Tensor, v: torch.Tensor, cu_seqlens_k: torch.Tensor
     return k_cache, v_cache, table, lens.to(torch.int32)
 
 
+def _pad_head_dims(q, k, v):
+    """Head dims the kernels do not tile (the reference's packed path takes any, e.g. 40 or 96:
+    tests/batch_invariant_ops/test_triton_attention_varlen.py:289) get zero columns up to the next tiled width:
+    exact zeros in every dot product, cut from the outputs again.  The softmax scale is explicit, so the wider
+    head does not touch it."""
+    dk, dv = q.shape[-1], v.shape[-1]
+    if (dk, dv) in _KERNEL_HEAD_DIMS:
+        return q, k, v
+    wide = next((d for d in (64, 128) if d >= max(dk, dv)), None)
+    if wide is None:
+        raise NotImplementedError(f"head dims ({dk}, {dv}) above 128 other than (192, 128)")
+    pad = torch.nn.functional.pad
+    return pad(q, (0, wide - dk)), pad(k, (0, wide - dk)), pad(v, (0, wide - dv))
+
+
 class _PackedVarlenForward(torch.autograd.Function):
-    """Forward of the packed path; its backward kernels are the training side's and are not built here."""
+    """The packed path: forward through a temporary paged cache and the paged kernels, backward through
+    `b200_varlen_attn_backward` (triton_invariant_attention.py:48-431)."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu_seqlens_q, cu_seqlens_k, scale, max_seqlen_q, max_seqlen_k):
         dk, dv = q.shape[-1], v.shape[-1]
-        if (dk, dv) not in _KERNEL_HEAD_DIMS:
-            # Head dims the kernels do not tile (the reference's packed path takes any, e.g. 40 or 96:
-            # tests/batch_invariant_ops/test_triton_attention_varlen.py:289): zero columns up to the next
-            # tiled width add exact zeros to every dot product and are cut from the output again.  `scale` is
-            # explicit, so it is not touched by the wider head.
-            wide = next((d for d in (64, 128) if d >= max(dk, dv)), None)
-            if wide is None:
-                raise NotImplementedError(f"head dims ({dk}, {dv}) above 128 other than (192, 128)")
-            pad = torch.nn.functional.pad
-            out = _PackedVarlenForward.forward(ctx, pad(q, (0, wide - dk)), pad(k, (0, wide - dk)),
-                                               pad(v, (0, wide - dv)), cu_seqlens_q, cu_seqlens_k, scale,
-                                               max_seqlen_q, max_seqlen_k)
-            return out[..., :dv].contiguous()
-        k_cache, v_cache, table, lens = packed_to_paged(k, v, cu_seqlens_k, max_seqlen_k)
+        qp, kp, vp = _pad_head_dims(q, k, v)
+        k_cache, v_cache, table, lens = packed_to_paged(kp, vp, cu_seqlens_k, max_seqlen_k)
         cu_q = cu_seqlens_q if cu_seqlens_q.dtype == torch.int32 else cu_seqlens_q.to(torch.int32)
-        return paged_attention(q, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q)
+        out = paged_attention(qp, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q)
+        if any(ctx.needs_input_grad[:3]):
+            cu_k = cu_seqlens_k if cu_seqlens_k.dtype == torch.int32 else cu_seqlens_k.to(torch.int32)
+            ctx.save_for_backward(qp.contiguous(), kp.contiguous(), vp.contiguous(), out, cu_q.contiguous(),
+                                  cu_k.contiguous())
+            ctx.scale, ctx.max_q, ctx.max_k, ctx.dims = float(scale), int(max_seqlen_q), int(max_seqlen_k), (dk, dv)
+        return out if out.shape[-1] == dv else out[..., :dv].contiguous()
 
     @staticmethod
     def backward(ctx, grad_out):
-        raise NotImplementedError("the packed varlen backward (dq / dkv kernels) is not part of this library")
+        q, k, v, out, cu_q, cu_k = ctx.saved_tensors
+        dk_dim, dv_dim = ctx.dims
+        dout = grad_out.to(torch.bfloat16)
+        if dout.shape[-1] != out.shape[-1]:
+            dout = torch.nn.functional.pad(dout, (0, out.shape[-1] - dout.shape[-1]))
+        dout = dout.contiguous()
+        dq, dkk, dvv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+        lse = torch.empty(q.shape[:2], dtype=torch.float32, device=q.device)
+        delta = torch.empty_like(lse)
+        _lib.check(
+            _lib.load().b200_varlen_attn_backward(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), cu_q.data_ptr(),
+                cu_k.data_ptr(), dq.data_ptr(), dkk.data_ptr(), dvv.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                cu_q.numel() - 1, ctx.max_q, ctx.max_k, q.shape[0], k.shape[0], q.shape[1], k.shape[1], q.shape[2],
+                v.shape[2], ctx.scale, _lib.current_stream()),
+            "b200_varlen_attn_backward",
+        )
+        return dq[..., :dk_dim], dkk[..., :dk_dim], dvv[..., :dv_dim], None, None, None, None, None
+
+
+class _PagedForward(torch.autograd.Function):
+    """The paged call under autograd: forward only, as in the reference (triton_invariant_attention.py:889-902)."""
+
+    @staticmethod
+    def forward(ctx, q, k_cache, v_cache, cu_seqlens_q, lens, table, scale, max_seqlen_q):
+        return paged_attention(q, k_cache, v_cache, cu_seqlens_q, lens, table, scale, max_seqlen_q)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        raise NotImplementedError("paged triton flash_attn_varlen_func backward is not implemented")
 
 
 def flash_attention_forward(

@@ -7,6 +7,7 @@
 #include "attn.cuh"
 #include "attn_tc.cuh"
 #include "attn_rows.cuh"
+#include "attn_bwd.cuh"
 #include "moe.cuh"
 #include "noalloc.cuh"
 #include "step.cuh"
