@@ -72,6 +72,9 @@ def parse_args():
     ap.add_argument("--row-kernels", action="store_true",
                     help="side measurement: the row kernels (RMSNorm, log_softmax, gather_logprob, kv_store) at the "
                          "operator-suite shapes, rotating over inputs larger than L2, GB/s per kernel")
+    ap.add_argument("--train-kernels", action="store_true",
+                    help="side measurement: forward + backward of the packed attention call and of one fused-MoE "
+                         "layer at the model's widths (the training-side operators; correctness-first kernels)")
     ap.add_argument("--prefill-attention", type=int, default=0, metavar="QLEN",
                     help="side measurement: time one causal prefill attention call of QLEN queries on the "
                          "model's head shape (context --ctx if larger) and print its own JSON line")
@@ -534,6 +537,69 @@ def run_row_kernels(args, shape):
     print(json.dumps({"measurement": "row_kernels", "hbm_peak_GBps": peak, "kernels": out}))
 
 
+def run_train_kernels(args, shape):
+    """Side measurement (not the contract line): forward and forward + backward of the training-side calls, CUDA
+    events: packed causal attention over 4 sequences of 2048 tokens, and one fused-MoE layer over 4096 tokens."""
+    import vexact_b200 as vb
+
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    BF = torch.bfloat16
+    res = {}
+
+    def timed(name, fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        res[name] = round(a.elapsed_time(b) / reps, 3)
+
+    hq, hkv, d = shape.num_q_heads, shape.num_kv_heads, shape.head_dim
+    lens = [2048] * 4
+    T = sum(lens)
+    q = torch.randn(T, hq, d, device=dev, generator=g).to(BF).requires_grad_(True)
+    k = torch.randn(T, hkv, d, device=dev, generator=g).to(BF).requires_grad_(True)
+    v = torch.randn(T, hkv, d, device=dev, generator=g).to(BF).requires_grad_(True)
+    dout = torch.randn(T, hq, d, device=dev, generator=g).to(BF)
+    cu = torch.tensor([0, 2048, 4096, 6144, 8192], dtype=torch.int32, device=dev)
+
+    def attn(backward):
+        out, _ = vb.flash_attn_varlen_func(q, k, v, cu, cu, max_seqlen_q=2048, max_seqlen_k=2048, causal=True)
+        if backward:
+            out.backward(dout)
+
+    with torch.no_grad():
+        timed("attention_forward_ms", lambda: attn(False))
+    timed("attention_forward_backward_ms", lambda: attn(True))
+    if shape.moe is not None:
+        E, kk, H, I = shape.moe.num_experts, shape.moe.top_k, shape.hidden, shape.moe.intermediate
+        Tm = 4096
+        x = torch.randn(Tm, H, device=dev, generator=g).to(BF).requires_grad_(True)
+        w1 = (torch.randn(E, I, H, device=dev, generator=g) * 0.02).to(BF).requires_grad_(True)
+        w2 = (torch.randn(E, I, H, device=dev, generator=g) * 0.02).to(BF).requires_grad_(True)
+        w3 = (torch.randn(E, H, I, device=dev, generator=g) * 0.02).to(BF).requires_grad_(True)
+        logits = torch.randn(Tm, E, device=dev, generator=g)
+        rw, sel = vb.route_softmax_topk(logits, kk, True)
+        rw = rw.requires_grad_(True)
+        gy = torch.randn(Tm, H, device=dev, generator=g).to(BF)
+
+        def moe(backward):
+            out = vb.fused_moe_forward(E, rw, sel, x, w1, w2, w3)
+            if backward:
+                out.backward(gy)
+
+        with torch.no_grad():
+            timed("moe_forward_ms", lambda: moe(False))
+        timed("moe_forward_backward_ms", lambda: moe(True))
+    print(json.dumps({"measurement": "train_kernels", "attention": {"tokens": T, "heads": [hq, hkv], "head_dim": d},
+                      "ms": res}))
+
+
 def run_prefill_attention(args, shape):
     """Side measurement (not the contract line): one sequence's causal prefill through paged attention."""
     import vexact_b200 as vb
@@ -606,6 +672,9 @@ def main():
         return
     if args.row_kernels:
         run_row_kernels(args, shape)
+        return
+    if args.train_kernels:
+        run_train_kernels(args, shape)
         return
     if args.prefill_attention:
         run_prefill_attention(args, shape)
