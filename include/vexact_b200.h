@@ -349,11 +349,17 @@ int b200_moe_scatter(const void* x, long long x_row_stride, const void* index_i3
 int b200_moe_gather(const void* x, long long x_rows, const void* index_i32, long long index_stride_t,
                     long long index_stride_k, void* out, long long T, int topk, int H, void* stream);
 
+/* No counterpart in the reference (its Triton GEMM reads either layout): out[g, c, r] = x[g, r, c] for 2-byte
+ * elements, x [G, R, C] and out [G, C, R] contiguous, R and C multiples of 8, 16-byte aligned.  Used to hand the
+ * expert weights to the dgrad form of the grouped GEMM (group_gemm.py:156 with transpose_b=False). */
+int b200_transpose_last2(const void* x, void* out, int G, int R, int C, void* stream);
+
 /* ---- vexact/batch_invariant_ops/group_gemm/kernel/group_gemm.py:360 group_gemm_same_mn(transpose_a=True): the
  *      weight gradient of a grouped GEMM, c[g] = a[rows of g]^T @ b[rows of g] with the rows of group g being
  *      [cu_seqlens[g], cu_seqlens[g + 1]).  a [rows, M], b [rows, N], c [num_groups, M, N], all bf16 contiguous;
  *      fp32 accumulation in ascending row order, one rounding; an empty group gets zeros.  M, N multiples of 4.
- *      A training-side operator on the CUDA cores (no tensor-core form): bound by writing c. */
+ *      A training-side operator: mma.sync tensor-core kernel when M and N are multiples of 8 and the pointers
+ *      16-byte aligned (sum over 16-row steps in ascending order), a CUDA-core kernel otherwise. */
 int b200_moe_grouped_wgrad(const void* a, const void* b, void* c, const void* cu_seqlens, long long rows,
                            int num_groups, int M, int N, void* stream);
 

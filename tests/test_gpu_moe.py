@@ -462,3 +462,25 @@ def test_fused_moe_backward_against_autograd_of_the_fp32_formula(vb, fused_weigh
         assert not ours[n].grad[E - 1].any()
 
 
+
+
+def test_weight_gradient_kernels_tensor_core_and_cuda_core_forms(vb):
+    """`group_gemm_same_mn` runs on the tensor cores when M and N are multiples of 8 and on the CUDA cores
+    otherwise; both against the fp32 product, with ragged and empty groups and tiles that overhang M and N."""
+    from vexact_b200 import group_gemm as gg
+
+    g = torch.Generator().manual_seed(41)
+    counts = [0, 37, 1, 200, 0, 16, 90]
+    R, G = sum(counts), len(counts)
+    cs = torch.cumsum(torch.tensor(counts), 0).cuda()
+    bounds = [0] + cs.tolist()
+    for M, N in [(200, 136), (128, 256), (36, 20)]:
+        a = torch.randn(R, M, generator=g).to(BF).cuda()
+        b = torch.randn(R, N, generator=g).to(BF).cuda()
+        c = gg.group_gemm_same_mn(a, b, torch.full((G, M, N), 7.0, dtype=BF, device="cuda"), cs, R, transpose_a=True,
+                                  transpose_b=False)
+        ref = torch.stack([a[bounds[e]:bounds[e + 1]].float().t() @ b[bounds[e]:bounds[e + 1]].float() for e in range(G)])
+        torch.testing.assert_close(c.float(), ref, rtol=2 ** -7, atol=2 ** -8 * ref.abs().max().item())
+        assert not c[0].any() and not c[4].any()
+    torch.cuda.synchronize()
+    assert vb._lib.read_status()[0] == 0

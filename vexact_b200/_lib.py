@@ -60,6 +60,7 @@ SIGNATURES = {
     "b200_moe_scatter": [P, LL, P, LL, LL, P, LL, LL, I, I, P],
     "b200_moe_gather": [P, LL, P, LL, LL, P, LL, I, I, P],
     "b200_moe_grouped_wgrad": [P, P, P, P, LL, I, I, I, P],
+    "b200_transpose_last2": [P, P, I, I, I, P],
     "b200_varlen_attn_backward": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, LL, LL, I, I, I, I, F, P],
     "b200_moe_unpermute_add_rmsnorm": [P, P, P, P, P, P, P, LL, I, I, F, I, P],
 }

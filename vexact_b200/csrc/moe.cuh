@@ -665,6 +665,121 @@ moe_wgrad_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __res
   }
 }
 
+// The same weight gradient on the tensor cores (mma.sync m16n8k16, bf16 x bf16 -> fp32): one CTA per 128 x 128
+// tile of one group's output, eight warps of 64 x 32 each, the group's rows staged 32 at a time as bf16 and read
+// with transposing ldmatrix (both operands have the contraction as their row dimension).  Products are exact,
+// the sum runs over 16-row steps in ascending order with the instruction's own order inside a step: deterministic,
+// and within fp32 rounding of the CUDA-core kernel above.  M and N multiples of 8, 16-byte aligned pointers.
+constexpr int WGM_TILE = 128, WGM_ROWS = 32, WGM_LD = WGM_TILE + 8;   // padded row: ldmatrix rows 272 bytes apart
+__global__ void __launch_bounds__(256)
+moe_wgrad_mma_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                     __nv_bfloat16* __restrict__ c, const int* __restrict__ cu_seqlens, long long rows, int M, int N) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ __align__(16) __nv_bfloat16 sa[WGM_ROWS][WGM_LD], sb[WGM_ROWS][WGM_LD];
+  const int g = blockIdx.z, m0 = blockIdx.y * WGM_TILE, n0 = blockIdx.x * WGM_TILE;
+  long long r0 = cu_seqlens[g], r1 = cu_seqlens[g + 1];
+  if (r0 < 0 || r1 > rows || r1 < r0) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) report_status(B200_STATUS_BAD_INDEX, g);
+    r0 = r0 < 0 ? 0 : (r0 > rows ? rows : r0);
+    r1 = r1 > rows ? rows : r1;
+    if (r1 < r0) r1 = r0;
+  }
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = (warp >> 2) * 64, wn = (warp & 3) * 32;        // this warp's 64 x 32 corner inside the tile
+  float acc[4][4][4];                                            // [m16 tile][n8 tile][fragment]
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+  const uint32_t sa_base = (uint32_t)__cvta_generic_to_shared(&sa[0][0]);
+  const uint32_t sb_base = (uint32_t)__cvta_generic_to_shared(&sb[0][0]);
+  for (long long r = r0; r < r1; r += WGM_ROWS) {
+    __syncthreads();                                             // the previous chunk has been consumed
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {                             // 32 rows x 16 vectors of 8 columns per operand
+      const int e = tid + it * 256, lr = e >> 4, lc = (e & 15) * 8;
+      uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+      if (r + lr < r1) {
+        if (m0 + lc < M) va = *reinterpret_cast<const uint4*>(a + (r + lr) * M + m0 + lc);
+        if (n0 + lc < N) vb = *reinterpret_cast<const uint4*>(b + (r + lr) * N + n0 + lc);
+      }
+      *reinterpret_cast<uint4*>(&sa[lr][lc]) = va;
+      *reinterpret_cast<uint4*>(&sb[lr][lc]) = vb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk0 = 0; kk0 < WGM_ROWS; kk0 += 16) {
+      uint32_t bf[4][2];
+#pragma unroll
+      for (int jp = 0; jp < 2; ++jp) {                           // two n8 tiles per ldmatrix
+        const int row = kk0 + (lane & 7) + ((lane >> 3) & 1) * 8, col = wn + jp * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(sb_base + (uint32_t)(row * WGM_LD + col) * 2, bf[2 * jp][0], bf[2 * jp][1],
+                          bf[2 * jp + 1][0], bf[2 * jp + 1][1]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = kk0 + (lane & 7) + (lane >> 4) * 8, col = wm + i * 16 + ((lane >> 3) & 1) * 8;
+        uint32_t a0, a1, a2, a3;
+        ldmatrix_x4_trans(sa_base + (uint32_t)(row * WGM_LD + col) * 2, a0, a1, a2, a3);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16_16816(acc[i][j], a0, a1, a2, a3, bf[j][0], bf[j][1]);
+      }
+    }
+  }
+  __nv_bfloat16* cg = c + (long long)g * M * N;
+  const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + wn + j * 8 + 2 * tig;
+      if (n >= N) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int m = m0 + wm + i * 16 + gid + half * 8;
+        if (m < M)
+          *reinterpret_cast<uint32_t*>(cg + (long long)m * N + n) = pack_bf2(acc[i][j][2 * half], acc[i][j][2 * half + 1]);
+      }
+    }
+}
+
+// out[g, c, r] = x[g, r, c] for 2-byte elements: 64 x 64 tiles through shared memory, 16-byte loads and stores.
+// R and C multiples of 8.  (The dgrad grouped GEMM reads the expert weights with the other dimension contiguous.)
+__global__ void __launch_bounds__(256)
+transpose_last2_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out, int R, int C) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ __align__(16) uint16_t t[64][72];
+  const long long base = (long long)blockIdx.z * R * C;
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64, tid = threadIdx.x;
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int e = tid + it * 256, lr = e >> 3, lc = (e & 7) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r0 + lr < R && c0 + lc < C) v = *reinterpret_cast<const uint4*>(x + base + (long long)(r0 + lr) * C + c0 + lc);
+    *reinterpret_cast<uint4*>(&t[lr][lc]) = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int it = 0; it < 2; ++it) {
+    const int e = tid + it * 256, oc = e >> 3, orr = (e & 7) * 8;     // output row oc (a source column), 8 source rows
+    if (c0 + oc < C && r0 + orr < R) {
+      uint16_t w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[k] = t[orr + k][oc];
+      uint4 v;
+      v.x = w[0] | ((uint32_t)w[1] << 16);
+      v.y = w[2] | ((uint32_t)w[3] << 16);
+      v.z = w[4] | ((uint32_t)w[5] << 16);
+      v.w = w[6] | ((uint32_t)w[7] << 16);
+      *reinterpret_cast<uint4*>(out + base + (long long)(c0 + oc) * R + r0 + orr) = v;
+    }
+  }
+}
+
 // h = bf16(bf16(bf16(silu(g)) * u) * s): the unfused tail of fc1 for split gate / up weights.
 __global__ void __launch_bounds__(256)
 swiglu_scale_kernel(const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
@@ -1000,6 +1115,19 @@ extern "C" int b200_moe_gather(const void* x, long long x_rows, const void* inde
   return launch_status();
 }
 
+// out[g, c, r] = x[g, r, c]: x [G, R, C], out [G, C, R], contiguous, 2-byte elements, R and C multiples of 8,
+// 16-byte aligned pointers.
+extern "C" int b200_transpose_last2(const void* x, void* out, int G, int R, int C, void* stream) {
+  using namespace b200;
+  if (!x || !out || G <= 0 || R <= 0 || C <= 0) return B200_ERR_ARG;
+  if (R % 8 != 0 || C % 8 != 0 || G > 65535 || (R + 63) / 64 > 65535 ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return B200_ERR_SHAPE;
+  launch_k(transpose_last2_kernel, dim3((unsigned)((C + 63) / 64), (unsigned)((R + 63) / 64), (unsigned)G), dim3(256), 0,
+           (cudaStream_t)stream, (const uint16_t*)x, (uint16_t*)out, R, C);
+  return launch_status();
+}
+
 // c[g] = a[rows of g]^T @ b[rows of g]: a [rows, M], b [rows, N], c [G, M, N] bf16 contiguous, cu_seqlens
 // [G + 1] i32 (rows of group g are [cu[g], cu[g + 1])).  M and N multiples of 4, 8-byte aligned pointers.
 extern "C" int b200_moe_grouped_wgrad(const void* a, const void* b, void* c, const void* cu_seqlens, long long rows,
@@ -1007,6 +1135,17 @@ extern "C" int b200_moe_grouped_wgrad(const void* a, const void* b, void* c, con
   using namespace b200;
   if (!a || !b || !c || !cu_seqlens || rows < 0 || num_groups <= 0 || M <= 0 || N <= 0) return B200_ERR_ARG;
   if (M % 4 != 0 || N % 4 != 0 || num_groups > 65535 || (M + WG_TILE - 1) / WG_TILE > 65535) return B200_ERR_SHAPE;
+  static const int simt = env_int("B200_WGRAD_SIMT", 0);        // development knob: the CUDA-core kernel
+  const bool vec16 = M % 8 == 0 && N % 8 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(c) & 3) == 0;
+  if (vec16 && !simt) {
+    launch_k(moe_wgrad_mma_kernel, dim3((unsigned)((N + WGM_TILE - 1) / WGM_TILE),
+                                        (unsigned)((M + WGM_TILE - 1) / WGM_TILE), (unsigned)num_groups),
+             dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
+             (__nv_bfloat16*)c, (const int*)cu_seqlens, rows, M, N);
+    return launch_status();
+  }
   launch_k(moe_wgrad_kernel, dim3((unsigned)((N + WG_TILE - 1) / WG_TILE), (unsigned)((M + WG_TILE - 1) / WG_TILE),
                                   (unsigned)num_groups),
            dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)c,

@@ -29,6 +29,17 @@ def _index_i32(index: torch.Tensor) -> torch.Tensor:
     return index if index.dtype == torch.int32 else index.to(torch.int32)
 
 
+def _transpose_last2(x: torch.Tensor) -> torch.Tensor:
+    """[G, R, C] -> contiguous [G, C, R] (tiled kernel for 2-byte elements with R, C multiples of 8)."""
+    G, R, C = x.shape
+    if x.element_size() != 2 or R % 8 or C % 8 or not x.is_contiguous() or x.data_ptr() % 16:
+        return x.transpose(1, 2).contiguous()
+    out = torch.empty((G, C, R), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.load().b200_transpose_last2(x.data_ptr(), out.data_ptr(), G, R, C, _lib.current_stream()),
+               "b200_transpose_last2")
+    return out
+
+
 def expert_histogram(input: torch.Tensor, num_bins: int) -> torch.Tensor:
     """Counts of the values 0..num_bins-1 in `input` -> int32 [num_bins] (moe.py:52-83)."""
     assert input.is_cuda
@@ -135,7 +146,7 @@ def group_gemm_same_nk(
         # are transposed into scratch first (one extra pass over them); the products and their order are those
         # of the forward form on the transposed tensor.
         assert b.dim() == 3 and a.shape[1] == b.shape[1]
-        return group_gemm_same_nk(a, b.transpose(1, 2).contiguous(), cumsum_M, 0, transpose_b=True)
+        return group_gemm_same_nk(a, _transpose_last2(b), cumsum_M, 0, transpose_b=True)
     if activation is not None or save_activation:
         raise NotImplementedError("a fused activation is not offered here; fused_moe_forward fuses SwiGLU itself")
     if c is not None:
