@@ -253,8 +253,8 @@ int b200_paged_attn_fwd_ordered(const void* q, const void* k_cache, const void* 
  *      scratch [total_q, hq] each (the log-sum-exp is recomputed here, the forward does not save it).
  *      (dk_dim, dv_dim) in {(64, 64), (128, 128), (192, 128)}.  p and ds are rounded to bf16 before their
  *      products as in the reference; fp32 accumulation in a fixed order, no atomics.  A training-side operator
- *      on the CUDA cores (no tensor-core form).  Pass zero-filled dq / dk / dv: rows of no sequence are not
- *      written. */
+ *      on mma.sync tensor-core instructions (B200_ATTN_BWD_SIMT=1: the CUDA-core form).  Pass zero-filled dq /
+ *      dk / dv: rows of no sequence are not written. */
 int b200_varlen_attn_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
                               const void* cu_seqlens_q, const void* cu_seqlens_k, void* dq, void* dk, void* dv,
                               void* lse_scratch_f32, void* delta_scratch_f32, int num_seqs, int max_seqlen_q,

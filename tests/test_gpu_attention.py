@@ -495,3 +495,41 @@ def test_packed_varlen_backward_matches_autograd_of_fp32_attention(vb, q_lens, k
     assert torch.equal(alone[0], got[0][a:]) and torch.equal(alone[1], got[1][b:]) and torch.equal(alone[2], got[2][b:])
     torch.cuda.synchronize()
     assert vb._lib.read_status()[0] == 0
+
+
+def test_packed_varlen_backward_tensor_core_and_cuda_core_forms_agree(vb, tmp_path):
+    """The default backward runs on the tensor cores (mma.sync); B200_ATTN_BWD_SIMT=1 selects the CUDA-core kernels
+    (read once per process, hence the child process).  Same rounding points, different summation order inside a
+    16-wide step: the two agree to 2^-6 of each gradient's largest magnitude."""
+    import subprocess
+    import sys
+
+    script = """
+import sys, torch
+import vexact_b200 as vb
+BF = torch.bfloat16
+g = torch.Generator().manual_seed(5)
+q_lens, kv_lens, hq, hkv, d = [70, 33], [100, 33], 4, 2, 128
+q = torch.randn(sum(q_lens), hq, d, generator=g).to(BF).cuda().requires_grad_(True)
+k = torch.randn(sum(kv_lens), hkv, d, generator=g).to(BF).cuda().requires_grad_(True)
+v = torch.randn(sum(kv_lens), hkv, d, generator=g).to(BF).cuda().requires_grad_(True)
+dout = torch.randn(sum(q_lens), hq, d, generator=g).to(BF).cuda()
+cu_q = torch.tensor([0, 70, 103], dtype=torch.int32).cuda()
+cu_k = torch.tensor([0, 100, 133], dtype=torch.int32).cuda()
+out, _ = vb.flash_attn_varlen_func(q, k, v, cu_q, cu_k, max_seqlen_q=70, max_seqlen_k=100, causal=True)
+out.backward(dout)
+torch.cuda.synchronize()
+assert vb._lib.read_status()[0] == 0
+torch.save([q.grad.cpu(), k.grad.cpu(), v.grad.cpu()], sys.argv[1])
+"""
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    grads = {}
+    for form, knob in (("mma", "0"), ("simt", "1")):
+        path = str(tmp_path / f"{form}.pt")
+        env = dict(os.environ, B200_ATTN_BWD_SIMT=knob, PYTHONPATH=root)
+        subprocess.run([sys.executable, "-c", script, path], check=True, env=env, cwd=root, timeout=180)
+        grads[form] = torch.load(path)
+    for a, b in zip(grads["mma"], grads["simt"]):
+        torch.testing.assert_close(a.float(), b.float(), rtol=0, atol=2 ** -6 * b.float().abs().max().item())

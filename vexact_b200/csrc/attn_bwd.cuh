@@ -10,10 +10,10 @@
 // The reference's forward saves the log-sum-exp; this library's forward kernels do not, so the first kernel
 // recomputes it (one more pass over the keys) and leaves lse and delta in caller-provided scratch for the second.
 //
-// A training-side operator kept simple: 32 x 32 tiles staged in shared memory as fp32, fp32 FMAs on the CUDA
-// cores, every sum in a fixed order (key blocks ascending for dq; query heads, then query blocks ascending for
-// dk / dv) and no atomics, so gradients are deterministic and a sequence's gradients do not depend on the batch.
-// No tensor-core form, no roofline claim.
+// This file holds the plain form: 32 x 32 tiles staged in shared memory as fp32, fp32 FMAs on the CUDA cores,
+// every sum in a fixed order (key blocks ascending for dq; query heads, then query blocks ascending for dk / dv)
+// and no atomics, so gradients are deterministic and a sequence's gradients do not depend on the batch.  It is
+// what B200_ATTN_BWD_SIMT=1 runs and what the tensor-core form (attn_bwd_mma.cuh, the default) is checked against.
 #pragma once
 #include "common.cuh"
 
@@ -329,33 +329,3 @@ inline int attn_bwd_launch(const AttnBwdParams& p, int num_seqs, int max_seqlen_
 }
 
 }  // namespace b200
-
-// dq, dk, dv of packed causal varlen attention (triton_invariant_attention.py:194-431).  All tensors bf16 and
-// contiguous: q / dq [total_q, hq, dk_dim], k / dk [total_k, hkv, dk_dim], v / dv [total_k, hkv, dv_dim], out /
-// dout [total_q, hq, dv_dim]; cu_seqlens_q / _k [num_seqs + 1] int32; lse / delta: fp32 scratch [total_q, hq].
-// (dk_dim, dv_dim) one of (64, 64), (128, 128), (192, 128).  Keys or queries of no sequence keep what dq / dk / dv
-// held (pass zero-filled tensors).  Sequences longer than max_seqlen_q / max_seqlen_k are reported (status code 2).
-extern "C" int b200_varlen_attn_backward(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                                         const void* cu_seqlens_q, const void* cu_seqlens_k, void* dq, void* dk,
-                                         void* dv, void* lse_scratch_f32, void* delta_scratch_f32, int num_seqs,
-                                         int max_seqlen_q, int max_seqlen_k, long long total_q, long long total_k,
-                                         int num_q_heads, int num_kv_heads, int dk_dim, int dv_dim,
-                                         float softmax_scale, void* stream) {
-  using namespace b200;
-  if (!q || !k || !v || !out || !dout || !cu_seqlens_q || !cu_seqlens_k || !dq || !dk || !dv || !lse_scratch_f32 ||
-      !delta_scratch_f32 || num_seqs < 0 || max_seqlen_q < 0 || max_seqlen_k < 0 || total_q < 0 || total_k < 0 ||
-      num_q_heads <= 0 || num_kv_heads <= 0)
-    return B200_ERR_ARG;
-  if (num_q_heads % num_kv_heads != 0 || num_seqs > 65535 || num_q_heads > 65535) return B200_ERR_SHAPE;
-  if (total_q > 0x7fffffffLL || total_k > 0x7fffffffLL) return B200_ERR_SHAPE;
-  if (num_seqs == 0 || max_seqlen_q == 0 || max_seqlen_k == 0) return B200_OK;
-  AttnBwdParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-                  (const __nv_bfloat16*)out, (const __nv_bfloat16*)dout, (__nv_bfloat16*)dq, (__nv_bfloat16*)dk,
-                  (__nv_bfloat16*)dv, (float*)lse_scratch_f32, (float*)delta_scratch_f32, (const int*)cu_seqlens_q,
-                  (const int*)cu_seqlens_k, num_q_heads, num_kv_heads, total_q, total_k, softmax_scale};
-  cudaStream_t st = (cudaStream_t)stream;
-  if (dk_dim == 64 && dv_dim == 64) return attn_bwd_launch<64, 64>(p, num_seqs, max_seqlen_q, max_seqlen_k, st);
-  if (dk_dim == 128 && dv_dim == 128) return attn_bwd_launch<128, 128>(p, num_seqs, max_seqlen_q, max_seqlen_k, st);
-  if (dk_dim == 192 && dv_dim == 128) return attn_bwd_launch<192, 128>(p, num_seqs, max_seqlen_q, max_seqlen_k, st);
-  return B200_ERR_SHAPE;
-}

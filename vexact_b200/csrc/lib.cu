@@ -7,7 +7,7 @@
 #include "attn.cuh"
 #include "attn_tc.cuh"
 #include "attn_rows.cuh"
-#include "attn_bwd.cuh"
+#include "attn_bwd_mma.cuh"
 #include "moe.cuh"
 #include "noalloc.cuh"
 #include "step.cuh"
