@@ -101,6 +101,14 @@ int b200_log_softmax_f32(const void* x, void* out, long long rows, int n, long l
 int b200_gather_logprob(const void* logits, const void* labels, void* out, long long rows, int n,
                         long long row_stride, int dtype, long long ignore_index, void* stream);
 
+/* Gradient of b200_gather_logprob with respect to the logits (the backward of flash-attn's cross_entropy_loss, which
+ * standalone_logprobs.py:28 wraps, with a log-probability's sign): dlogits[r, i] = grad_out[r] * ((i == label[r]) -
+ * softmax(logits[r])[i]), in the logits' dtype, a zero row for an ignored label.  dlogits may be logits itself
+ * (`inplace_backward=True`). */
+int b200_gather_logprob_backward(const void* logits, const void* labels, const void* grad_out_f32, void* dlogits,
+                                 long long rows, int n, long long row_stride, long long d_row_stride, int dtype,
+                                 long long ignore_index, void* stream);
+
 /* ---- vexact/inferencer/inferencer.py:393-449 _select_tokens for greedy decoding: the argmax of each
  *      row of logits (lowest index on ties) and that token's log-probability (the value
  *      logprobs_from_logits_flash_attn returns for it), in one pass.  tokens int64, logprobs fp32. */

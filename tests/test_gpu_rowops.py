@@ -255,3 +255,31 @@ def test_rms_norm_backward_matches_reference_formula_and_is_row_invariant():
     w1 = w.detach().clone().requires_grad_(True)
     vb.batch_invariant_rms_norm(x1, w1, eps).backward(go[7:8])
     assert torch.equal(x1.grad[0], x.grad[7])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_gather_logprob_backward_matches_autograd(vb, dtype):
+    """Gradient of `logprobs_from_logits_flash_attn` with respect to the logits (the reference wraps flash-attn's
+    cross_entropy_loss, whose backward is softmax - onehot; standalone_logprobs.py:28-55): against torch autograd on
+    log_softmax + gather in fp32; an ignored label gives a zero row; `inplace_backward=True` writes into the logits."""
+    g = torch.Generator().manual_seed(12)
+    rows, vocab = 7, 5003
+    x = (torch.randn(rows, vocab, generator=g) * 3).to(dtype).cuda()
+    labels = torch.randint(0, vocab, (rows,), generator=g).cuda()
+    labels[3] = -100
+    go = torch.randn(rows, generator=g).cuda()
+    leaf = x.clone().requires_grad_(True)
+    out = vb.logprobs_from_logits_flash_attn(leaf, labels)
+    assert torch.equal(out, vb.logprobs_from_logits_flash_attn(x, labels))
+    out.backward(go)
+    ref = x.float().clone().requires_grad_(True)
+    lp = torch.log_softmax(ref, -1).gather(-1, labels.clamp(min=0).unsqueeze(-1)).squeeze(-1)
+    (lp * (labels != -100)).backward(go)
+    assert leaf.grad.dtype == dtype and not leaf.grad[3].any()
+    tol = 2e-6 if dtype == torch.float32 else 2 ** -8
+    torch.testing.assert_close(leaf.grad.float(), ref.grad, rtol=tol, atol=tol * ref.grad.abs().max().item())
+    # in place: the gradient lands in the logits' own storage
+    buf = x.clone()
+    leaf2 = buf.detach().requires_grad_(True)
+    vb.logprobs_from_logits_flash_attn(leaf2, labels, inplace_backward=True).backward(go)
+    assert leaf2.grad.data_ptr() == leaf2.data_ptr() and torch.equal(leaf2.grad, leaf.grad)

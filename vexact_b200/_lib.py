@@ -30,6 +30,7 @@ SIGNATURES = {
     "b200_mean_lastdim": [P, P, LL, I, LL, I, P],
     "b200_log_softmax_f32": [P, P, LL, I, LL, LL, P],
     "b200_gather_logprob": [P, P, P, LL, I, LL, I, LL, P],
+    "b200_gather_logprob_backward": [P, P, P, P, LL, I, LL, LL, I, LL, P],
     "b200_greedy_logprob": [P, P, P, LL, I, LL, I, P],
     "b200_lm_head_greedy": [P, P, P, P, P, LL, I, I, LL, LL, P],
     "b200_sample_token": [P, P, P, P, LL, I, LL, LL, I, F, I, F, P],

@@ -176,6 +176,29 @@ gather_logprob_kernel(const T* __restrict__ x, const long long* __restrict__ lab
   }
 }
 
+// Gradient of gather_logprob_kernel with respect to the logits (flash-attn's cross-entropy backward with the sign
+// of a log-probability, flash_attn/ops/triton/cross_entropy.py): dx[i] = g * ((i == label) - exp(x[i] - lse)),
+// a zero row for an ignored label.  The (max, sum) walk is the forward's, so lse has the forward's bits.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+gather_logprob_backward_kernel(const T* __restrict__ x, const long long* __restrict__ labels,
+                               const float* __restrict__ grad_out, T* __restrict__ dx, int n, long long x_stride,
+                               long long dx_stride, long long ignore_index, bool vec) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float sm[32], ss[32];
+  const T* row = x + (long long)blockIdx.x * x_stride;
+  T* drow = dx + (long long)blockIdx.x * dx_stride;
+  const long long label = labels[blockIdx.x];
+  const MaxSum r = row_max_sum<T>(row, n, vec, sm, ss);
+  const bool live = label != ignore_index && label >= 0 && label < n;
+  const float lse = logf(r.s) + r.m, g = live ? grad_out[blockIdx.x] : 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float xi = (float)row[i];      // read before the write: dx may be x itself (inplace_backward)
+    drow[i] = (T)(live ? g * ((i == label ? 1.f : 0.f) - expf(xi - lse)) : 0.f);
+  }
+}
+
 // Greedy token and its log-probability in one pass over a row of logits: argmax (lowest index on
 // ties, as torch.argmax) and logprob = max - logsumexp = -log(sum exp(x - max)).  Replaces the
 // torch.argmax + cross-entropy pair of Inferencer._select_tokens (inferencer.py:393-449) for greedy
@@ -271,6 +294,30 @@ extern "C" int b200_gather_logprob(const void* logits, const void* labels, void*
   } else {
     return B200_ERR_ARG;
   }
+  return launch_status();
+}
+
+// d logprob / d logits for b200_gather_logprob: dlogits[r, i] = grad_out[r] * ((i == label[r]) - softmax(logits[r])[i])
+// in the logits' dtype; dlogits may alias logits (rows are processed after their statistics are known).
+extern "C" int b200_gather_logprob_backward(const void* logits, const void* labels, const void* grad_out_f32,
+                                            void* dlogits, long long rows, int n, long long row_stride,
+                                            long long d_row_stride, int dtype /*0 = f32, 1 = bf16*/,
+                                            long long ignore_index, void* stream) {
+  using namespace b200;
+  if (!logits || !labels || !grad_out_f32 || !dlogits || rows < 0 || n <= 0) return B200_ERR_ARG;
+  if (rows == 0) return B200_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  if (dtype == 0)
+    launch_k(gather_logprob_backward_kernel<float>, dim3((unsigned)rows), dim3(1024), 0, st, (const float*)logits,
+             (const long long*)labels, (const float*)grad_out_f32, (float*)dlogits, n, row_stride, d_row_stride,
+             ignore_index, aligned && row_stride % 4 == 0);
+  else if (dtype == 1)
+    launch_k(gather_logprob_backward_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(1024), 0, st,
+             (const __nv_bfloat16*)logits, (const long long*)labels, (const float*)grad_out_f32,
+             (__nv_bfloat16*)dlogits, n, row_stride, d_row_stride, ignore_index, aligned && row_stride % 8 == 0);
+  else
+    return B200_ERR_ARG;
   return launch_status();
 }
 

@@ -13,11 +13,46 @@ from . import _lib
 IGNORE_INDEX = -100
 
 
+class _GatherLogprob(torch.autograd.Function):
+    """Per-token log-probability with the gradient flash-attn's cross-entropy gives (sign flipped)."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, inplace_backward):
+        with torch.no_grad():
+            out = logprobs_from_logits_flash_attn(logits, labels)
+        ctx.save_for_backward(logits, labels)
+        ctx.inplace = bool(inplace_backward)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        logits, labels = ctx.saved_tensors
+        vocab = logits.shape[-1]
+        x = logits.reshape(-1, vocab)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        inplace = ctx.inplace and x.data_ptr() == logits.data_ptr()
+        dx = x if inplace else torch.empty_like(x)
+        lab = labels.reshape(-1).to(torch.int64).contiguous()
+        g = grad_out.reshape(-1).to(torch.float32).contiguous()
+        _lib.check(
+            _lib.load().b200_gather_logprob_backward(x.data_ptr(), lab.data_ptr(), g.data_ptr(), dx.data_ptr(),
+                                                     x.shape[0], vocab, x.stride(0), dx.stride(0),
+                                                     0 if x.dtype == torch.float32 else 1, IGNORE_INDEX,
+                                                     _lib.current_stream()),
+            "b200_gather_logprob_backward",
+        )
+        return dx.reshape(logits.shape), None, None
+
+
 def logprobs_from_logits_flash_attn(logits: torch.Tensor, labels: torch.Tensor,
                                     inplace_backward: bool = False) -> torch.Tensor:
-    del inplace_backward  # forward only
     if not logits.is_cuda:
         raise ValueError("logits must be a CUDA tensor")
+    if torch.is_grad_enabled() and logits.requires_grad:
+        if logits.dtype not in (torch.float32, torch.bfloat16):
+            raise NotImplementedError(f"logits dtype {logits.dtype} is not supported")
+        return _GatherLogprob.apply(logits, labels, inplace_backward)
     if logits.dtype not in (torch.float32, torch.bfloat16):
         raise NotImplementedError(f"logits dtype {logits.dtype} is not supported")
     batch_shape = logits.shape[:-1]
