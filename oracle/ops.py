@@ -17,8 +17,6 @@ functions (Triton and quack), which is what the model files' call to
 """
 from __future__ import annotations
 
-import math
-
 import numpy as np
 import torch
 
