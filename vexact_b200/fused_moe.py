@@ -413,51 +413,46 @@ class FusedMoeExpertFunction(torch.autograd.Function):
         k = experts.shape[1]
         w1b, w2b, w3b = (w.to(bf).contiguous() for w in (w1, w2, w3))
 
-        # forward intermediates again, one operator at a time (fused_moe.py:36-99)
+        # forward intermediates again, one operator at a time (same rounding points as fused_moe.py:36-99)
         cu, _, scatter_index = build_moe_indices(experts, E)
-        cumsum_t = cu[1:]
-        flat = scatter_index.flatten().long()
-        scatter_output = gg.moe_scatter(x, scatter_index)
-        fc1_1_output = gg.group_gemm_same_nk(scatter_output, w1b, cumsum_t, T * k, transpose_b=True)
-        fc1_2_output = gg.group_gemm_same_nk(scatter_output, w2b, cumsum_t, T * k, transpose_b=True)
-        fc1_1_activation = torch.ops.aten.silu(fc1_1_output)
-        fc1_activation = fc1_1_activation * fc1_2_output
-        scattered_gate_weight = torch.empty((T * k, 1), dtype=bf, device=x.device)
-        scattered_gate_weight[flat] = gate_weights.to(bf).reshape(-1, 1)
-        fc1_weighted_output = fc1_activation * scattered_gate_weight
+        ends = cu[1:]                                   # inclusive row count per expert
+        rows = T * k
+        sorted_pos = scatter_index.flatten().long()
+        xs = gg.moe_scatter(x, scatter_index)           # [rows, H], expert-sorted
+        gate = gg.group_gemm_same_nk(xs, w1b, ends, rows, transpose_b=True)
+        up = gg.group_gemm_same_nk(xs, w2b, ends, rows, transpose_b=True)
+        gate_act = torch.ops.aten.silu(gate)
+        act = gate_act * up
+        row_w = torch.empty((rows, 1), dtype=bf, device=x.device)
+        row_w[sorted_pos] = gate_weights.to(bf).reshape(-1, 1)
+        hidden_in = act * row_w                         # what fc2 consumed
 
         need = ctx.needs_input_grad
-        # top-k sum, then fc2
-        grad_fc2_output = gg.moe_scatter(grad_output, scatter_index)
-        grad_fc1_weighted_output = gg.group_gemm_same_nk(grad_fc2_output, w3b, cumsum_t, T * k, transpose_b=False)
-        grad_w3 = None
-        if need[6]:
-            grad_w3 = gg.group_gemm_same_mn(grad_fc2_output, fc1_weighted_output, torch.empty_like(w3b), cumsum_t,
-                                            T * k, transpose_a=True, transpose_b=False).to(w3.dtype)
-        # routing weight
-        grad_fc1_activation = grad_fc1_weighted_output * scattered_gate_weight
+
+        def wgrad(g_rows, inputs, like, original):
+            return gg.group_gemm_same_mn(g_rows, inputs, torch.empty_like(like), ends, rows, transpose_a=True,
+                                         transpose_b=False).to(original.dtype)
+
+        # through the top-k sum and fc2
+        g_y = gg.moe_scatter(grad_output, scatter_index)
+        g_hidden_in = gg.group_gemm_same_nk(g_y, w3b, ends, rows, transpose_b=False)
+        grad_w3 = wgrad(g_y, hidden_in, w3b, w3) if need[6] else None
+        # the routing weight multiplies act row by row
+        g_act = g_hidden_in * row_w
         grad_gate = None
         if need[1]:
-            grad_scattered = torch.sum(fc1_activation * grad_fc1_weighted_output, dim=-1)
-            grad_gate = grad_scattered[flat].reshape(gate_weights.shape).to(gate_weights.dtype)
-        # SwiGLU
-        grad_fc1_1_activation = grad_fc1_activation * fc1_2_output
-        grad_fc1_2_output = fc1_1_activation * grad_fc1_activation
-        grad_fc1_1_output = torch.ops.aten.silu_backward(grad_fc1_1_activation, fc1_1_output)
-        # fc1, both halves
-        grad_w1 = grad_w2 = None
-        if need[4]:
-            grad_w1 = gg.group_gemm_same_mn(grad_fc1_1_output, scatter_output, torch.empty_like(w1b), cumsum_t, T * k,
-                                            transpose_a=True, transpose_b=False).to(w1.dtype)
-        if need[5]:
-            grad_w2 = gg.group_gemm_same_mn(grad_fc1_2_output, scatter_output, torch.empty_like(w2b), cumsum_t, T * k,
-                                            transpose_a=True, transpose_b=False).to(w2.dtype)
+            per_row = torch.sum(act * g_hidden_in, dim=-1)
+            grad_gate = per_row[sorted_pos].reshape(gate_weights.shape).to(gate_weights.dtype)
+        # SwiGLU: act = silu(gate) * up
+        g_up = gate_act * g_act
+        g_gate = torch.ops.aten.silu_backward(g_act * up, gate)
+        grad_w1 = wgrad(g_gate, xs, w1b, w1) if need[4] else None
+        grad_w2 = wgrad(g_up, xs, w2b, w2) if need[5] else None
         grad_hidden = None
         if need[3]:
-            grad_scatter_output = (gg.group_gemm_same_nk(grad_fc1_1_output, w1b, cumsum_t, T * k, transpose_b=False)
-                                   + gg.group_gemm_same_nk(grad_fc1_2_output, w2b, cumsum_t, T * k, transpose_b=False))
-            grad_hidden = gg.moe_gather(grad_scatter_output, scatter_index).reshape(hidden_states.shape)
-            grad_hidden = grad_hidden.to(hidden_states.dtype)
+            g_xs = (gg.group_gemm_same_nk(g_gate, w1b, ends, rows, transpose_b=False)
+                    + gg.group_gemm_same_nk(g_up, w2b, ends, rows, transpose_b=False))
+            grad_hidden = gg.moe_gather(g_xs, scatter_index).reshape(hidden_states.shape).to(hidden_states.dtype)
         return None, grad_gate, None, grad_hidden, grad_w1, grad_w2, grad_w3
 
 
