@@ -211,7 +211,10 @@ class _PackedVarlenForward(torch.autograd.Function):
         qp, kp, vp = _pad_head_dims(q, k, v)
         k_cache, v_cache, table, lens = packed_to_paged(kp, vp, cu_seqlens_k, max_seqlen_k)
         cu_q = cu_seqlens_q if cu_seqlens_q.dtype == torch.int32 else cu_seqlens_q.to(torch.int32)
-        out = paged_attention(qp, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q)
+        # zero-filled: a sequence the kernel refuses (more queries than keys: reported through the status word)
+        # leaves zeros, not whatever the allocator handed out
+        out = torch.zeros((qp.shape[0], qp.shape[1], vp.shape[-1]), dtype=qp.dtype, device=qp.device)
+        paged_attention(qp, k_cache, v_cache, cu_q, lens, table, scale, max_seqlen_q, out=out)
         if any(ctx.needs_input_grad[:3]):
             cu_k = cu_seqlens_k if cu_seqlens_k.dtype == torch.int32 else cu_seqlens_k.to(torch.int32)
             ctx.save_for_backward(qp.contiguous(), kp.contiguous(), vp.contiguous(), out, cu_q.contiguous(),
