@@ -595,6 +595,21 @@ def run_train_kernels(args, shape):
         with torch.no_grad():
             timed("moe_forward_ms", lambda: moe(False))
         timed("moe_forward_backward_ms", lambda: moe(True))
+        # the backward's GEMM forms on their own (vexact_b200.group_gemm), same shapes
+        from vexact_b200 import group_gemm as gg
+        with torch.no_grad():
+            cu, _, si = vb.fused_moe.build_moe_indices(sel, E)
+            ends, xs = cu[1:], gg.moe_scatter(x.detach(), si)
+            h1 = gg.group_gemm_same_nk(xs, w1.detach(), ends, 0, transpose_b=True)
+            gy8 = torch.randn(Tm * kk, H, device=dev, generator=g).to(BF)
+            c1, c3 = torch.empty_like(w1), torch.empty_like(w3)
+            timed("moe_plain_fc1_gemm_ms", lambda: gg.group_gemm_same_nk(xs, w1.detach(), ends, 0, transpose_b=True))
+            timed("moe_dgrad_fc2_ms", lambda: gg.group_gemm_same_nk(gy8, w3.detach(), ends, 0, transpose_b=False))
+            timed("moe_dgrad_fc1_ms", lambda: gg.group_gemm_same_nk(h1, w1.detach(), ends, 0, transpose_b=False))
+            timed("moe_wgrad_fc2_ms", lambda: gg.group_gemm_same_mn(gy8, h1, c3, ends, 0, transpose_a=True,
+                                                                    transpose_b=False))
+            timed("moe_wgrad_fc1_ms", lambda: gg.group_gemm_same_mn(h1, xs, c1, ends, 0, transpose_a=True,
+                                                                    transpose_b=False))
     print(json.dumps({"measurement": "train_kernels", "attention": {"tokens": T, "heads": [hq, hkv], "head_dim": d},
                       "ms": res}))
 
