@@ -680,8 +680,57 @@ def sec_model_moe(out_dir):
     return res
 
 
+@section("backward")
+def sec_backward(out_dir):
+    """Training-side gradients: the reference's packed attention backward (triton_invariant_attention.py:194-431)
+    and its Triton fused-MoE backward (fused_moe.py:113-265) next to this library's, same bf16 inputs and
+    upstream gradients.  Numbers only (max-abs / mean-abs deltas per gradient); no fixtures are stored."""
+    from vexact.batch_invariant_ops.triton_invariant_attention import flash_attn_varlen_func as ref_attn
+    import vexact.batch_invariant_ops.fused_moe as rmoe
+    import vexact_b200 as vb
+
+    rep = {}
+    g = torch.Generator().manual_seed(7)
+    q_lens, kv_lens, hq, hkv, d = [65, 129], [65, 129], 4, 2, 128
+    base = [torch.randn(sum(q_lens), hq, d, generator=g).to(BF).to(DEV),
+            torch.randn(sum(kv_lens), hkv, d, generator=g).to(BF).to(DEV),
+            torch.randn(sum(kv_lens), hkv, d, generator=g).to(BF).to(DEV)]
+    dout = torch.randn(sum(q_lens), hq, d, generator=g).to(BF).to(DEV)
+    cu_q = torch.tensor([0, 65, 194], dtype=torch.int32, device=DEV)
+    grads = {}
+    for tag, fn in (("reference", ref_attn), ("ours", vb.flash_attn_varlen_func)):
+        leaves = [t.clone().requires_grad_(True) for t in base]
+        out, _ = fn(*leaves, cu_q, cu_q, max_seqlen_q=129, max_seqlen_k=129, softmax_scale=d ** -0.5, causal=True)
+        out.backward(dout)
+        grads[tag] = [out.detach()] + [t.grad for t in leaves]
+    rep["attention"] = {n: delta(o, r) for n, o, r in zip(("out", "dq", "dk", "dv"), grads["ours"], grads["reference"])}
+    REPORT["backward"] = dict(rep)                       # partial results survive a late failure
+    with open(os.path.join(out_dir, "reference_agreement.json"), "w") as f:
+        json.dump(REPORT, f, indent=1)
+
+    try:
+        case = gi.MOE_CASES[0]
+        hidden, gate_up, down, router = gi.moe_inputs(case)
+        E, k, I = case["E"], case["k"], case["I"]
+        hd, gud, dd, rd = (t.to(DEV) for t in (hidden, gate_up, down, router))
+        rw, sel = _ref_topk_route(vb.matmul_persistent(hd, rd.t()), k)
+        gy = torch.randn(hd.shape, generator=g).to(BF).to(DEV)
+        base = dict(rw=rw, x=hd, w1=gud[:, :I].contiguous(), w2=gud[:, I:].contiguous(), w3=dd)
+        grads = {}
+        for tag, fn in (("reference", rmoe.FusedMoeExpertFunction.apply),
+                        ("ours", vb.fused_moe.FusedMoeExpertFunction.apply)):
+            lv = {n: t.clone().requires_grad_(True) for n, t in base.items()}
+            out = fn(E, lv["rw"], sel, lv["x"], lv["w1"], lv["w2"], lv["w3"])
+            out.backward(gy)
+            grads[tag] = dict(out=out.detach(), **{n: t.grad for n, t in lv.items()})
+        rep["fused_moe"] = {n: delta(grads["ours"][n], grads["reference"][n]) for n in grads["ours"]}
+    except Exception as e:      # keep the attention numbers
+        rep["fused_moe"] = {"error": f"{type(e).__name__}: {e}"[:600]}
+    return rep
+
+
 SECTIONS = [sec_matmul, sec_rowops, sec_kv_store, sec_attention, sec_moe, sec_moe_timing, sec_router, sec_model_dense,
-            sec_model_moe]
+            sec_model_moe, sec_backward]
 
 
 def main():
