@@ -708,8 +708,16 @@ def sec_backward(out_dir):
     with open(os.path.join(out_dir, "reference_agreement.json"), "w") as f:
         json.dump(REPORT, f, indent=1)
 
+    for case in (gi.MOE_CASES[0], gi.MOE_CASES[2]):
+        _backward_moe_case(case, g, rep)
+    return rep
+
+
+def _backward_moe_case(case, g, rep):
+    import vexact.batch_invariant_ops.fused_moe as rmoe
+    import vexact_b200 as vb
+
     try:
-        case = gi.MOE_CASES[0]
         hidden, gate_up, down, router = gi.moe_inputs(case)
         E, k, I = case["E"], case["k"], case["I"]
         hd, gud, dd, rd = (t.to(DEV) for t in (hidden, gate_up, down, router))
@@ -723,10 +731,9 @@ def sec_backward(out_dir):
             out = fn(E, lv["rw"], sel, lv["x"], lv["w1"], lv["w2"], lv["w3"])
             out.backward(gy)
             grads[tag] = dict(out=out.detach(), **{n: t.grad for n, t in lv.items()})
-        rep["fused_moe"] = {n: delta(grads["ours"][n], grads["reference"][n]) for n in grads["ours"]}
-    except Exception as e:      # keep the attention numbers
-        rep["fused_moe"] = {"error": f"{type(e).__name__}: {e}"[:600]}
-    return rep
+        rep["fused_moe_" + case["name"]] = {n: delta(grads["ours"][n], grads["reference"][n]) for n in grads["ours"]}
+    except Exception as e:      # keep the other numbers
+        rep["fused_moe_" + case["name"]] = {"error": f"{type(e).__name__}: {e}"[:600]}
 
 
 SECTIONS = [sec_matmul, sec_rowops, sec_kv_store, sec_attention, sec_moe, sec_moe_timing, sec_router, sec_model_dense,
