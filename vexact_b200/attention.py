@@ -114,7 +114,7 @@ def flash_attn_varlen_func(
     """FlashAttention-style varlen call; returns (out, None).
 
     With `page_table` / `block_table`: the paged rollout path.  Without: the packed path the training side
-    uses (triton_invariant_attention.py:48-192, forward only): K / V are laid into a temporary paged cache
+    uses (forward: triton_invariant_attention.py:48-192): K / V are laid into a temporary paged cache
     and run through the same kernel, so a token gets the same bits from the packed call as from the rollout's
     paged prefill.  Gradients of q, k and v come from `b200_varlen_attn_backward` (:194-431 there)."""
     del alibi_slopes, deterministic, return_attn_probs, kwargs
