@@ -1,8 +1,9 @@
 """Paged causal attention behind the reference's two entry points.
 
 * `flash_attn_varlen_func`: the FlashAttention-compatible varlen interface of
-  vexact/batch_invariant_ops/triton_invariant_attention.py:905 (paged path only:
-  `page_table` / `block_table` and `seqused_k` / `cache_seqlens` aliases).
+  vexact/batch_invariant_ops/triton_invariant_attention.py:905: the paged rollout path
+  (`page_table` / `block_table` and `seqused_k` / `cache_seqlens` aliases, forward only) and the
+  packed training-side path (no page table; forward and backward).
 * `flash_attention_forward`: the HF `ALL_ATTENTION_FUNCTIONS` adapter of
   triton_invariant_attention.py:982 and flash_attention.py:26, which reads the
   thread-local KV-cache context, stores K/V and calls the paged kernel.
